@@ -1,0 +1,537 @@
+// Routing forward for sm_100a.
+//
+//   route_gate_topk   one warp per pair of tokens: gate GEMM (fp32 accumulate, bf16 round), scoring,
+//                     iterative-argmax top-k (lowest index wins ties), renormalisation, logsumexp,
+//                     per-block expert histogram and probability-mass partial sums.
+//   route_scan        one block: per-expert exclusive scan of the block histograms, expert counts,
+//                     128-row-aligned segment starts (tile_start) and the loss statistics, all summed in a
+//                     fixed order so results do not depend on scheduling.
+//   route_rank        stable rank of every routed slot inside its expert segment -> pos[] and src[].
+//
+// Tokens are assigned to blocks in contiguous chunks, so "block order, then warp order, then slot order"
+// equals the (token, slot) order of a stable sort by expert id.
+#include "ffm_common.cuh"
+
+namespace ffm {
+
+namespace {
+
+constexpr int ROUTE_THREADS = 256;
+constexpr int ROUTE_WARPS = ROUTE_THREADS / 32;
+constexpr int MAX_E = 256;
+constexpr int TPW = 2;  // tokens per warp pass
+
+struct RouteGrid {
+  int blocks;
+  int tokens_per_block;
+};
+
+RouteGrid route_grid(long long N) {
+  // Contiguous token chunks, a multiple of 16 tokens (8 warps x 2 tokens), about four blocks per SM.
+  long long target_blocks = 148 * 4;
+  long long tpb = (N + target_blocks - 1) / target_blocks;
+  tpb = ((tpb + 15) / 16) * 16;
+  if (tpb < 16) tpb = 16;
+  RouteGrid g;
+  g.tokens_per_block = static_cast<int>(tpb);
+  g.blocks = static_cast<int>((N + tpb - 1) / tpb);
+  if (g.blocks < 1) g.blocks = 1;
+  return g;
+}
+
+// Sum GW per-lane partial accumulators across the warp; on return lane l holds the total of
+// accumulator (l % GW) in a[0].
+template <int GW>
+__device__ __forceinline__ void transpose_reduce(float (&a)[GW], int lane) {
+#pragma unroll
+  for (int n = GW; n > 1; n >>= 1) {
+    const int o = n >> 1;
+    const bool upper = (lane & o) != 0;
+#pragma unroll
+    for (int i = 0; i < o; ++i) {
+      const float lo = a[i], hi = a[i + o];
+      const float send = upper ? lo : hi;
+      const float keep = upper ? hi : lo;
+      a[i] = keep + __shfl_xor_sync(0xffffffffu, send, o);
+    }
+  }
+#pragma unroll
+  for (int o = 16; o >= GW; o >>= 1) a[0] += __shfl_xor_sync(0xffffffffu, a[0], o);
+}
+
+__device__ __forceinline__ float dot8(const uint4& h, const uint4& w, float acc) {
+  const float2 h0 = unpack_bf16x2(h.x), h1 = unpack_bf16x2(h.y), h2 = unpack_bf16x2(h.z), h3 = unpack_bf16x2(h.w);
+  const float2 w0 = unpack_bf16x2(w.x), w1 = unpack_bf16x2(w.y), w2 = unpack_bf16x2(w.z), w3 = unpack_bf16x2(w.w);
+  acc = fmaf(h0.x, w0.x, acc);
+  acc = fmaf(h0.y, w0.y, acc);
+  acc = fmaf(h1.x, w1.x, acc);
+  acc = fmaf(h1.y, w1.y, acc);
+  acc = fmaf(h2.x, w2.x, acc);
+  acc = fmaf(h2.y, w2.y, acc);
+  acc = fmaf(h3.x, w3.x, acc);
+  acc = fmaf(h3.y, w3.y, acc);
+  return acc;
+}
+
+// Expert e = g * 32 + lane for NG > 1 (GW == 32); e = lane % GW for NG == 1.
+template <int GW, int NG>
+__global__ void __launch_bounds__(ROUTE_THREADS)
+route_gate_topk(const bf16* __restrict__ hidden, const bf16* __restrict__ gate_w, const float* __restrict__ bias,
+                long long N, int D, int E, int top_k, int gating, float weight_scale, int tokens_per_block,
+                bf16* __restrict__ logits_out, float* __restrict__ topk_w, int32_t* __restrict__ topk_idx,
+                float* __restrict__ lse_out, int32_t* __restrict__ block_hist, float* __restrict__ block_mass,
+                float* __restrict__ block_z) {
+  __shared__ float s_mass[ROUTE_WARPS][MAX_E];
+  __shared__ int s_cnt[ROUTE_WARPS][MAX_E];
+  __shared__ float s_z[ROUTE_WARPS];
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long tok_begin = static_cast<long long>(blockIdx.x) * tokens_per_block;
+  long long tok_end = tok_begin + tokens_per_block;
+  if (tok_end > N) tok_end = N;
+  const int chunks = D >> 3;  // 16-byte chunks per row
+
+  float mass[NG];
+  int cnt[NG];
+#pragma unroll
+  for (int g = 0; g < NG; ++g) {
+    mass[g] = 0.0f;
+    cnt[g] = 0;
+  }
+  float zsum = 0.0f;
+
+  for (long long t0 = tok_begin + warp * TPW; t0 < tok_end; t0 += ROUTE_WARPS * TPW) {
+    const bool has1 = (t0 + 1) < tok_end;
+    const uint4* h0p = reinterpret_cast<const uint4*>(hidden + t0 * D);
+    const uint4* h1p = reinterpret_cast<const uint4*>(hidden + (has1 ? t0 + 1 : t0) * D);
+
+    // ---- gate GEMM: logit[tk][g] for expert g * 32 + lane (or lane % GW) ----
+    float logit[TPW][NG];
+#pragma unroll
+    for (int g = 0; g < NG; ++g) {
+      float acc0[GW], acc1[GW];
+#pragma unroll
+      for (int e = 0; e < GW; ++e) {
+        acc0[e] = 0.0f;
+        acc1[e] = 0.0f;
+      }
+      for (int c = lane; c < chunks; c += 32) {
+        const uint4 a0 = __ldg(h0p + c);
+        const uint4 a1 = __ldg(h1p + c);
+#pragma unroll
+        for (int e = 0; e < GW; ++e) {
+          const int ee = g * GW + e;
+          if (ee < E) {
+            const uint4 w = __ldg(reinterpret_cast<const uint4*>(gate_w + static_cast<long long>(ee) * D) + c);
+            acc0[e] = dot8(a0, w, acc0[e]);
+            acc1[e] = dot8(a1, w, acc1[e]);
+          }
+        }
+      }
+      transpose_reduce<GW>(acc0, lane);
+      transpose_reduce<GW>(acc1, lane);
+      logit[0][g] = bf16_round(acc0[0]);
+      logit[1][g] = bf16_round(acc1[0]);
+    }
+
+#pragma unroll
+    for (int tk = 0; tk < TPW; ++tk) {
+      if (tk == 1 && !has1) break;
+      const long long n = t0 + tk;
+      // expert owned by this lane in group g, and whether this lane is the canonical holder
+      // (for GW < 32 the logits are replicated 32 / GW times; only lanes < GW act as holders)
+      const bool holder_lane = (NG > 1) || (lane < GW);
+
+      float sel[NG];   // value used for selection
+      float val[NG];   // unbiased value that becomes the weight (logit or sigmoid score)
+      float lmax = -INFINITY;
+#pragma unroll
+      for (int g = 0; g < NG; ++g) {
+        const int e = g * GW + (NG > 1 ? lane : (lane % GW));
+        const bool valid = holder_lane && e < E;
+        const float lg = logit[tk][g];
+        if (valid && logits_out != nullptr) logits_out[n * E + e] = __float2bfloat16_rn(lg);
+        float v = (gating == FFM_GATING_SIGMOID) ? sigmoidf_(lg) : lg;
+        float s = v;
+        if (bias != nullptr && valid) s = v + bias[e];
+        val[g] = valid ? v : 0.0f;
+        sel[g] = valid ? s : -INFINITY;
+        if (valid) lmax = fmaxf(lmax, lg);
+      }
+      // logsumexp over all experts (z-loss)
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) lmax = fmaxf(lmax, __shfl_xor_sync(0xffffffffu, lmax, o));
+      float esum = 0.0f;
+#pragma unroll
+      for (int g = 0; g < NG; ++g) {
+        const int e = g * GW + (NG > 1 ? lane : (lane % GW));
+        if (holder_lane && e < E) esum += __expf(logit[tk][g] - lmax);
+      }
+      esum = warp_sum(esum);
+      const float lse = lmax + __logf(esum);
+      if (lane == 0) {
+        lse_out[n] = lse;
+        zsum += lse * lse;
+      }
+      if (gating == FFM_GATING_SIGMOID) {
+#pragma unroll
+        for (int g = 0; g < NG; ++g) mass[g] += val[g];
+      }
+
+      // ---- top-k by iterative argmax, lowest index wins ties ----
+      float my_val = 0.0f;
+      int my_idx = 0;
+      for (int j = 0; j < top_k; ++j) {
+        float best = -INFINITY;
+        int best_e = 0x7fffffff;
+#pragma unroll
+        for (int g = 0; g < NG; ++g) {
+          const int e = g * GW + (NG > 1 ? lane : (lane % GW));
+          if (sel[g] > best) {
+            best = sel[g];
+            best_e = e;
+          }
+        }
+        if (best == -INFINITY) best_e = 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+          const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+          if (ov > best || (ov == best && oe < best_e)) {
+            best = ov;
+            best_e = oe;
+          }
+        }
+        // the holder of best_e publishes the unbiased value and retires the expert
+        float v_pub = 0.0f;
+#pragma unroll
+        for (int g = 0; g < NG; ++g) {
+          const int e = g * GW + (NG > 1 ? lane : (lane % GW));
+          if (holder_lane && e == best_e) {
+            v_pub = val[g];
+            sel[g] = -INFINITY;
+          }
+        }
+        const int holder = (NG > 1) ? (best_e & 31) : best_e;
+        v_pub = __shfl_sync(0xffffffffu, v_pub, holder & 31);
+        if (lane == j) {
+          my_val = v_pub;
+          my_idx = best_e;
+        }
+      }
+
+      // ---- weights over the k selected values (lanes 0..k-1) ----
+      float w;
+      if (gating == FFM_GATING_SOFTMAX) {
+        float m = (lane < top_k) ? my_val : -INFINITY;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        const float ex = (lane < top_k) ? __expf(my_val - m) : 0.0f;
+        const float den = warp_sum(ex);
+        w = ex / den;
+      } else {
+        const float sc = (lane < top_k) ? my_val : 0.0f;
+        const float den = warp_sum(sc) + 1e-6f;
+        w = sc / den;
+      }
+      w *= weight_scale;
+      if (lane < top_k) {
+        topk_w[n * top_k + lane] = w;
+        topk_idx[n * top_k + lane] = my_idx;
+      }
+      // ---- per-warp statistics: lane (e % 32) owns expert e ----
+      for (int j = 0; j < top_k; ++j) {
+        const int ej = __shfl_sync(0xffffffffu, my_idx, j);
+        const float wj = __shfl_sync(0xffffffffu, w, j);
+        const int own_lane = (NG > 1) ? (ej & 31) : ej;
+#pragma unroll
+        for (int g = 0; g < NG; ++g) {
+          if (lane == own_lane && g == ((NG > 1) ? (ej >> 5) : 0)) {
+            cnt[g] += 1;
+            if (gating == FFM_GATING_SOFTMAX) mass[g] += wj;
+          }
+        }
+      }
+    }
+  }
+
+  // ---- block reduction in fixed warp order ----
+#pragma unroll
+  for (int g = 0; g < NG; ++g) {
+    const int e = g * GW + (NG > 1 ? lane : (lane % GW));
+    const bool holder_lane = (NG > 1) || (lane < GW);
+    if (holder_lane && e < E) {
+      s_mass[warp][e] = mass[g];
+      s_cnt[warp][e] = cnt[g];
+    }
+  }
+  if (lane == 0) s_z[warp] = zsum;
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += ROUTE_THREADS) {
+    float m = 0.0f;
+    int c = 0;
+    for (int w = 0; w < ROUTE_WARPS; ++w) {
+      m += s_mass[w][e];
+      c += s_cnt[w][e];
+    }
+    block_mass[static_cast<long long>(blockIdx.x) * E + e] = m;
+    block_hist[static_cast<long long>(blockIdx.x) * E + e] = c;
+  }
+  if (threadIdx.x == 0) {
+    float z = 0.0f;
+    for (int w = 0; w < ROUTE_WARPS; ++w) z += s_z[w];
+    block_z[blockIdx.x] = z;
+  }
+}
+
+// Histogram of given expert ids with the same block chunking (expert-parallel receive side).
+__global__ void __launch_bounds__(ROUTE_THREADS)
+route_hist_ids(const int32_t* __restrict__ ids, long long T, int E, int slots_per_block,
+               int32_t* __restrict__ block_hist, int32_t* __restrict__ status) {
+  __shared__ int s_cnt[MAX_E];
+  for (int e = threadIdx.x; e < E; e += ROUTE_THREADS) s_cnt[e] = 0;
+  __syncthreads();
+  const long long begin = static_cast<long long>(blockIdx.x) * slots_per_block;
+  long long end = begin + slots_per_block;
+  if (end > T) end = T;
+  for (long long i = begin + threadIdx.x; i < end; i += ROUTE_THREADS) {
+    const int e = ids[i];
+    if (e >= 0 && e < E) {
+      atomicAdd(&s_cnt[e], 1);
+    } else {
+      atomicCAS(status, 0, FFM_STATUS_BAD_INDEX);
+    }
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += ROUTE_THREADS) block_hist[static_cast<long long>(blockIdx.x) * E + e] = s_cnt[e];
+}
+
+// One block. block_off[b][e] = sum_{b' < b} hist[b'][e]; counts; tile_start; stats.
+__global__ void __launch_bounds__(ROUTE_THREADS)
+route_scan(const int32_t* __restrict__ block_hist, const float* __restrict__ block_mass,
+           const float* __restrict__ block_z, int blocks, int E, int32_t* __restrict__ block_off,
+           int32_t* __restrict__ counts, int32_t* __restrict__ tile_start, float* __restrict__ stats) {
+  __shared__ int s_counts[MAX_E];
+  __shared__ float s_mass[MAX_E];
+  for (int e = threadIdx.x; e < E; e += ROUTE_THREADS) {
+    int run = 0;
+    float m = 0.0f;
+    for (int b = 0; b < blocks; ++b) {
+      const long long o = static_cast<long long>(b) * E + e;
+      block_off[o] = run;
+      run += block_hist[o];
+      if (block_mass != nullptr) m += block_mass[o];
+    }
+    s_counts[e] = run;
+    s_mass[e] = m;
+    counts[e] = run;
+    if (stats != nullptr) stats[e] = m;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int tiles = 0;
+    float dot = 0.0f;
+    tile_start[0] = 0;
+    for (int e = 0; e < E; ++e) {
+      tiles += (s_counts[e] + 127) >> 7;
+      tile_start[e + 1] = tiles;
+      dot += static_cast<float>(s_counts[e]) * s_mass[e];
+    }
+    if (stats != nullptr) {
+      float z = 0.0f;
+      if (block_z != nullptr) {
+        for (int b = 0; b < blocks; ++b) z += block_z[b];
+      }
+      stats[E] = z;
+      stats[E + 1] = dot;
+    }
+  }
+}
+
+// Stable rank inside each expert segment. Each warp owns a contiguous run of the block's slots.
+__global__ void __launch_bounds__(ROUTE_THREADS)
+route_rank(const int32_t* __restrict__ ids, long long T, int E, int slots_per_block,
+           const int32_t* __restrict__ block_off, const int32_t* __restrict__ tile_start, long long rows_cap,
+           int32_t* __restrict__ pos, int32_t* __restrict__ src, int32_t* __restrict__ status) {
+  __shared__ int s_run[ROUTE_WARPS][MAX_E];
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long begin = static_cast<long long>(blockIdx.x) * slots_per_block;
+  long long end = begin + slots_per_block;
+  if (end > T) end = T;
+  const long long span = end > begin ? end - begin : 0;
+  const long long per_warp = ((span + ROUTE_WARPS - 1) / ROUTE_WARPS + 31) / 32 * 32;
+  const long long wb = begin + warp * per_warp;
+  long long we = wb + per_warp;
+  if (we > end) we = end;
+
+  for (int e = lane; e < E; e += 32) s_run[warp][e] = 0;
+  __syncwarp();
+  // pass 1: per-warp counts
+  for (long long i = wb + lane; i < we; i += 32) {
+    const int e = ids[i];
+    if (e >= 0 && e < E) atomicAdd(&s_run[warp][e], 1);
+  }
+  __syncthreads();
+  // exclusive scan over warps, per expert, plus the block and segment bases
+  for (int e = threadIdx.x; e < E; e += ROUTE_THREADS) {
+    int run = tile_start[e] * 128 + block_off[static_cast<long long>(blockIdx.x) * E + e];
+    for (int w = 0; w < ROUTE_WARPS; ++w) {
+      const int c = s_run[w][e];
+      s_run[w][e] = run;
+      run += c;
+    }
+  }
+  __syncthreads();
+  // pass 2: walk the run in order, 32 slots at a time
+  for (long long i0 = wb; i0 < we; i0 += 32) {
+    const long long i = i0 + lane;
+    const bool active = i < we;
+    int e = active ? ids[i] : -1;
+    if (active && (e < 0 || e >= E)) {
+      atomicCAS(status, 0, FFM_STATUS_BAD_INDEX);
+      e = -1;
+    }
+    const unsigned same = __match_any_sync(0xffffffffu, e);
+    const int leader = __ffs(same) - 1;
+    const int rank = __popc(same & ((1u << lane) - 1u));
+    int base = 0;
+    if (e >= 0 && lane == leader) {
+      base = s_run[warp][e];
+      s_run[warp][e] = base + __popc(same);
+    }
+    base = __shfl_sync(0xffffffffu, base, leader);
+    __syncwarp();
+    if (e >= 0) {
+      const long long r = static_cast<long long>(base) + rank;
+      if (r < rows_cap) {
+        pos[i] = static_cast<int32_t>(r);
+        src[r] = static_cast<int32_t>(i);
+      } else {
+        atomicCAS(status, 0, FFM_STATUS_BAD_INDEX);
+      }
+    }
+  }
+}
+
+struct RouteWorkspace {
+  int32_t* block_hist;
+  int32_t* block_off;
+  float* block_mass;
+  float* block_z;
+  size_t bytes;
+};
+
+RouteWorkspace carve_workspace(void* base, int blocks, int E) {
+  RouteWorkspace w;
+  size_t off = 0;
+  auto take = [&](size_t n) {
+    size_t o = off;
+    off += (n + 255) / 256 * 256;
+    return o;
+  };
+  const size_t per = static_cast<size_t>(blocks) * E * 4;
+  size_t o_hist = take(per), o_off = take(per), o_mass = take(per), o_z = take(static_cast<size_t>(blocks) * 4);
+  uint8_t* b = static_cast<uint8_t*>(base);
+  w.block_hist = reinterpret_cast<int32_t*>(b + o_hist);
+  w.block_off = reinterpret_cast<int32_t*>(b + o_off);
+  w.block_mass = reinterpret_cast<float*>(b + o_mass);
+  w.block_z = reinterpret_cast<float*>(b + o_z);
+  w.bytes = off;
+  return w;
+}
+
+template <int GW, int NG>
+void launch_route(int blocks, cudaStream_t s, const bf16* hidden, const bf16* gate_w, const float* bias, long long N,
+                  int D, int E, int top_k, int gating, float weight_scale, int tpb, bf16* logits, float* topk_w,
+                  int32_t* topk_idx, float* lse, const RouteWorkspace& w) {
+  route_gate_topk<GW, NG><<<blocks, ROUTE_THREADS, 0, s>>>(hidden, gate_w, bias, N, D, E, top_k, gating, weight_scale,
+                                                           tpb, logits, topk_w, topk_idx, lse, w.block_hist,
+                                                           w.block_mass, w.block_z);
+}
+
+}  // namespace
+
+}  // namespace ffm
+
+using namespace ffm;
+
+extern "C" int64_t ffm_rows_capacity(int64_t T, int E) {
+  if (T < 0 || E < 1) return 0;
+  return ((T + 127LL * E) / 128) * 128;
+}
+
+extern "C" size_t ffm_route_workspace_bytes(int64_t N, int E, int top_k) {
+  (void)top_k;
+  if (N < 0 || E < 1) return 0;
+  // The same workspace serves ffm_group_rows over N * top_k slots, whose grid is never larger.
+  RouteGrid g = route_grid(N > 0 ? N : 1);
+  RouteGrid g2 = route_grid(N > 0 ? N * (top_k > 0 ? top_k : 1) : 1);
+  int blocks = g.blocks > g2.blocks ? g.blocks : g2.blocks;
+  return carve_workspace(nullptr, blocks, E).bytes;
+}
+
+extern "C" int ffm_route_forward(const void* hidden, const void* gate_w, const float* expert_bias, int64_t N, int D,
+                                 int E, int top_k, int gating, float weight_scale, void* logits, float* topk_w,
+                                 int32_t* topk_idx, float* lse, int32_t* counts, int32_t* tile_start, int32_t* pos,
+                                 int32_t* src, int64_t rows_cap, float* stats, void* workspace,
+                                 size_t workspace_bytes, int32_t* status, ffm_stream_t stream) {
+  if (!hidden || !gate_w || !topk_w || !topk_idx || !lse || !counts || !tile_start || !pos || !src || !stats ||
+      !workspace || !status)
+    return FFM_ERR_BAD_ARG;
+  if (N < 0 || D <= 0 || E < 1 || top_k < 1) return FFM_ERR_BAD_ARG;
+  if (gating != FFM_GATING_SOFTMAX && gating != FFM_GATING_SIGMOID) return FFM_ERR_BAD_ARG;
+  if (D % 8 != 0 || E > MAX_E || top_k > E || top_k > 32) return FFM_ERR_UNSUPPORTED;
+  if (rows_cap < ffm_rows_capacity(N * top_k, E)) return FFM_ERR_BAD_ARG;
+  if (workspace_bytes < ffm_route_workspace_bytes(N, E, top_k)) return FFM_ERR_WORKSPACE;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (cudaMemsetAsync(src, 0xFF, static_cast<size_t>(rows_cap) * 4, s) != cudaSuccess) return FFM_ERR_LAUNCH;
+  const RouteGrid g = route_grid(N > 0 ? N : 1);
+  RouteWorkspace w = carve_workspace(workspace, g.blocks, E);
+  const bf16* h = static_cast<const bf16*>(hidden);
+  const bf16* gw = static_cast<const bf16*>(gate_w);
+  bf16* lg = static_cast<bf16*>(logits);
+#define FFM_ROUTE_CASE(GW, NG)                                                                                 \
+  launch_route<GW, NG>(g.blocks, s, h, gw, expert_bias, N, D, E, top_k, gating, weight_scale, g.tokens_per_block, \
+                       lg, topk_w, topk_idx, lse, w)
+  if (E <= 8) {
+    FFM_ROUTE_CASE(8, 1);
+  } else if (E <= 16) {
+    FFM_ROUTE_CASE(16, 1);
+  } else if (E <= 32) {
+    FFM_ROUTE_CASE(32, 1);
+  } else if (E <= 64) {
+    FFM_ROUTE_CASE(32, 2);
+  } else if (E <= 128) {
+    FFM_ROUTE_CASE(32, 4);
+  } else {
+    FFM_ROUTE_CASE(32, 8);
+  }
+#undef FFM_ROUTE_CASE
+  route_scan<<<1, ROUTE_THREADS, 0, s>>>(w.block_hist, w.block_mass, w.block_z, g.blocks, E, w.block_off, counts,
+                                         tile_start, stats);
+  route_rank<<<g.blocks, ROUTE_THREADS, 0, s>>>(topk_idx, N * top_k, E, g.tokens_per_block * top_k, w.block_off,
+                                                tile_start, rows_cap, pos, src, status);
+  return cudaGetLastError() == cudaSuccess ? FFM_OK : FFM_ERR_LAUNCH;
+}
+
+extern "C" int ffm_group_rows(const int32_t* expert_ids, int64_t T, int E, int32_t* counts, int32_t* tile_start,
+                              int32_t* pos, int32_t* src, int64_t rows_cap, void* workspace, size_t workspace_bytes,
+                              int32_t* status, ffm_stream_t stream) {
+  if (!expert_ids || !counts || !tile_start || !pos || !src || !workspace || !status) return FFM_ERR_BAD_ARG;
+  if (T < 0 || E < 1) return FFM_ERR_BAD_ARG;
+  if (E > MAX_E) return FFM_ERR_UNSUPPORTED;
+  if (rows_cap < ffm_rows_capacity(T, E)) return FFM_ERR_BAD_ARG;
+  const RouteGrid g = route_grid(T > 0 ? T : 1);
+  if (workspace_bytes < carve_workspace(nullptr, g.blocks, E).bytes) return FFM_ERR_WORKSPACE;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (cudaMemsetAsync(src, 0xFF, static_cast<size_t>(rows_cap) * 4, s) != cudaSuccess) return FFM_ERR_LAUNCH;
+  RouteWorkspace w = carve_workspace(workspace, g.blocks, E);
+  route_hist_ids<<<g.blocks, ROUTE_THREADS, 0, s>>>(expert_ids, T, E, g.tokens_per_block, w.block_hist, status);
+  route_scan<<<1, ROUTE_THREADS, 0, s>>>(w.block_hist, nullptr, nullptr, g.blocks, E, w.block_off, counts, tile_start,
+                                         nullptr);
+  route_rank<<<g.blocks, ROUTE_THREADS, 0, s>>>(expert_ids, T, E, g.tokens_per_block, w.block_off, tile_start,
+                                                rows_cap, pos, src, status);
+  return cudaGetLastError() == cudaSuccess ? FFM_OK : FFM_ERR_LAUNCH;
+}

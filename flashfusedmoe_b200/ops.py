@@ -1,0 +1,242 @@
+"""Tensor-level wrappers around the libffmoe C ABI.
+
+Each function takes CUDA bf16/int32/float32 tensors, allocates outputs through torch's caching allocator
+and enqueues the kernels on the current CUDA stream. Nothing here computes on the host; without a GPU
+or without the built library every call raises.
+"""
+
+from dataclasses import dataclass
+
+import torch
+
+from . import _lib
+
+_status = {}
+_workspaces = {}
+
+
+def _ptr(t):
+    return 0 if t is None else t.data_ptr()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _req(t, dtype, name):
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor: flashfusedmoe_b200 has no CPU path")
+    if t.dtype != dtype:
+        raise TypeError(f"{name} must be {dtype}, got {t.dtype}")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+    return t
+
+
+def status_tensor(device):
+    """Per-device int32 status word written by kernels whose bounded waits ran out."""
+    key = torch.device(device).index
+    if key is None:
+        key = torch.cuda.current_device()
+    if key not in _status:
+        _status[key] = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", key))
+    return _status[key]
+
+
+def check_status(device=None):
+    """Synchronise and raise if any kernel reported a device-side failure since the last check."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    st = status_tensor(dev)
+    code = int(st.item())
+    if code != 0:
+        st.zero_()
+        raise RuntimeError(f"libffmoe device status {code}: {_lib.error_string(code)}")
+
+
+def rows_capacity(T, E):
+    return int(_lib.load().ffm_rows_capacity(int(T), int(E)))
+
+
+def _workspace(device, nbytes, tag):
+    """Grow-only scratch buffer per (device, tag); reused across calls on the same stream order."""
+    key = (torch.device(device).index, tag)
+    buf = _workspaces.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
+        _workspaces[key] = buf
+    return buf
+
+
+@dataclass
+class Routing:
+    """Everything the routing kernels produce for one call (see include/ffmoe.h for the layout)."""
+    topk_w: torch.Tensor      # [N, k] f32
+    topk_idx: torch.Tensor    # [N, k] int32
+    logits: torch.Tensor      # [N, E] bf16
+    lse: torch.Tensor         # [N] f32
+    counts: torch.Tensor      # [E] int32
+    tile_start: torch.Tensor  # [E + 1] int32
+    pos: torch.Tensor         # [N * k] int32
+    src: torch.Tensor         # [rows_cap] int32
+    stats: torch.Tensor       # [E + 2] f32
+    rows_cap: int
+    top_k: int
+    num_experts: int
+
+
+def route_forward(hidden, gate_w, top_k, gating="softmax", expert_bias=None, weight_scale=1.0):
+    lib = _lib.load()
+    _req(hidden, torch.bfloat16, "hidden")
+    _req(gate_w, torch.bfloat16, "gate_w")
+    N, D = hidden.shape
+    E = gate_w.shape[0]
+    dev = hidden.device
+    T = N * top_k
+    rows_cap = rows_capacity(T, E)
+    if expert_bias is not None:
+        expert_bias = _req(expert_bias.to(torch.float32).contiguous(), torch.float32, "expert_bias")
+    r = Routing(
+        topk_w=torch.empty(N, top_k, dtype=torch.float32, device=dev),
+        topk_idx=torch.empty(N, top_k, dtype=torch.int32, device=dev),
+        logits=torch.empty(N, E, dtype=torch.bfloat16, device=dev),
+        lse=torch.empty(N, dtype=torch.float32, device=dev),
+        counts=torch.empty(E, dtype=torch.int32, device=dev),
+        tile_start=torch.empty(E + 1, dtype=torch.int32, device=dev),
+        pos=torch.empty(T, dtype=torch.int32, device=dev),
+        src=torch.empty(max(rows_cap, 1), dtype=torch.int32, device=dev),
+        stats=torch.empty(E + 2, dtype=torch.float32, device=dev),
+        rows_cap=rows_cap, top_k=top_k, num_experts=E)
+    ws_bytes = int(lib.ffm_route_workspace_bytes(N, E, top_k))
+    ws = _workspace(dev, ws_bytes, "route")
+    rc = lib.ffm_route_forward(_ptr(hidden), _ptr(gate_w), _ptr(expert_bias), N, D, E, top_k,
+                               _lib.GATING[gating], float(weight_scale), _ptr(r.logits), _ptr(r.topk_w),
+                               _ptr(r.topk_idx), _ptr(r.lse), _ptr(r.counts), _ptr(r.tile_start), _ptr(r.pos),
+                               _ptr(r.src), rows_cap, _ptr(r.stats), _ptr(ws), ws.numel(),
+                               _ptr(status_tensor(dev)), _stream())
+    _lib.check(rc, "ffm_route_forward")
+    return r
+
+
+def group_rows(expert_ids, num_experts):
+    """Grouped-row map for rows already tagged with an expert id (int32 [T])."""
+    lib = _lib.load()
+    _req(expert_ids, torch.int32, "expert_ids")
+    T = expert_ids.numel()
+    dev = expert_ids.device
+    rows_cap = rows_capacity(T, num_experts)
+    counts = torch.empty(num_experts, dtype=torch.int32, device=dev)
+    tile_start = torch.empty(num_experts + 1, dtype=torch.int32, device=dev)
+    pos = torch.empty(max(T, 1), dtype=torch.int32, device=dev)
+    src = torch.empty(max(rows_cap, 1), dtype=torch.int32, device=dev)
+    ws_bytes = int(lib.ffm_route_workspace_bytes(max(T, 1), num_experts, 1))
+    ws = _workspace(dev, ws_bytes, "group")
+    rc = lib.ffm_group_rows(_ptr(expert_ids), T, num_experts, _ptr(counts), _ptr(tile_start), _ptr(pos), _ptr(src),
+                            rows_cap, _ptr(ws), ws.numel(), _ptr(status_tensor(dev)), _stream())
+    _lib.check(rc, "ffm_group_rows")
+    return counts, tile_start, pos[:T], src, rows_cap
+
+
+def permute_rows(x, src, rows_cap, top_k):
+    lib = _lib.load()
+    _req(x, torch.bfloat16, "x")
+    _req(src, torch.int32, "src")
+    D = x.shape[1]
+    out = torch.empty(rows_cap, D, dtype=torch.bfloat16, device=x.device)
+    _lib.check(lib.ffm_permute_rows(_ptr(x), _ptr(src), rows_cap, top_k, D, _ptr(out), _stream()),
+               "ffm_permute_rows")
+    return out
+
+
+def grouped_gemm_glu(A, w_gate, w_up, group_rows_, groups, tile_start, K, H, activation, want_preact=True):
+    """act = glu(A Wg^T, A Wu^T). w_gate / w_up are tensors whose data pointers address the first gate / up row."""
+    lib = _lib.load()
+    _req(A, torch.bfloat16, "A")
+    rows = A.shape[0]
+    act = torch.empty(rows, H, dtype=torch.bfloat16, device=A.device)
+    pre = torch.empty(rows, 2 * H, dtype=torch.bfloat16, device=A.device) if want_preact else None
+    rc = lib.ffm_grouped_gemm_glu(_ptr(A), _ptr(w_gate), _ptr(w_up), group_rows_, groups, _ptr(tile_start), rows, K,
+                                  H, _lib.ACTIVATION[activation], _ptr(act), _ptr(pre),
+                                  _ptr(status_tensor(A.device)), _stream())
+    _lib.check(rc, "ffm_grouped_gemm_glu")
+    return act, pre
+
+
+def grouped_gemm(A, B, b_major, groups, tile_start, K, n_out, scale=1.0):
+    lib = _lib.load()
+    _req(A, torch.bfloat16, "A")
+    _req(B, torch.bfloat16, "B")
+    rows = A.shape[0]
+    out = torch.empty(rows, n_out, dtype=torch.bfloat16, device=A.device)
+    rc = lib.ffm_grouped_gemm(_ptr(A), _ptr(B), b_major, groups, _ptr(tile_start), rows, K, n_out, float(scale),
+                              _ptr(out), _ptr(status_tensor(A.device)), _stream())
+    _lib.check(rc, "ffm_grouped_gemm")
+    return out
+
+
+def grouped_gemm_wgrad(A, B, groups, tile_start, scale=1.0):
+    """dW[e] = scale * A[rows of e]^T B[rows of e]; A [rows_cap, M], B [rows_cap, N] -> [groups, M, N]."""
+    lib = _lib.load()
+    _req(A, torch.bfloat16, "A")
+    _req(B, torch.bfloat16, "B")
+    rows_cap, M = A.shape
+    n_out = B.shape[1]
+    out = torch.empty(groups, M, n_out, dtype=torch.bfloat16, device=A.device)
+    rc = lib.ffm_grouped_gemm_wgrad(_ptr(A), _ptr(B), groups, _ptr(tile_start), rows_cap, M, n_out, float(scale),
+                                    _ptr(out), _ptr(status_tensor(A.device)), _stream())
+    _lib.check(rc, "ffm_grouped_gemm_wgrad")
+    return out
+
+
+def combine_forward(Y, pos, w, N, top_k, addend=None):
+    lib = _lib.load()
+    _req(Y, torch.bfloat16, "Y")
+    _req(pos, torch.int32, "pos")
+    D = Y.shape[1]
+    out = torch.empty(N, D, dtype=torch.bfloat16, device=Y.device)
+    rc = lib.ffm_combine_forward(_ptr(Y), _ptr(pos), _ptr(w), _ptr(addend), N, top_k, D, _ptr(out), _stream())
+    _lib.check(rc, "ffm_combine_forward")
+    return out
+
+
+def combine_backward(go, Y, w, src, rows_cap, top_k, want_gw=True):
+    lib = _lib.load()
+    _req(go, torch.bfloat16, "go")
+    D = go.shape[1]
+    gYw = torch.empty(rows_cap, D, dtype=torch.bfloat16, device=go.device)
+    gw = torch.zeros(go.shape[0] * top_k, dtype=torch.float32, device=go.device) if want_gw else None
+    rc = lib.ffm_combine_backward(_ptr(go), _ptr(Y if want_gw else None), _ptr(w), _ptr(src), rows_cap, top_k, D,
+                                  _ptr(gYw), _ptr(gw), _stream())
+    _lib.check(rc, "ffm_combine_backward")
+    return gYw, gw
+
+
+def glu_backward(dAct, preact, tile_start, groups, activation):
+    lib = _lib.load()
+    _req(dAct, torch.bfloat16, "dAct")
+    _req(preact, torch.bfloat16, "preact")
+    rows, H = dAct.shape
+    gU = torch.empty(rows, 2 * H, dtype=torch.bfloat16, device=dAct.device)
+    rc = lib.ffm_glu_backward(_ptr(dAct), _ptr(preact), _ptr(tile_start), groups, rows, H,
+                              _lib.ACTIVATION[activation], _ptr(gU), _stream())
+    _lib.check(rc, "ffm_glu_backward")
+    return gU
+
+
+def route_backward(gw, routing, gaux, gz, hidden, gate_w, gating, dH=None):
+    """Returns (dH, dGate). If dH is given the routing term is added to it in place."""
+    lib = _lib.load()
+    N, D = hidden.shape
+    E = gate_w.shape[0]
+    dev = hidden.device
+    accumulate = dH is not None
+    if dH is None:
+        dH = torch.empty(N, D, dtype=torch.bfloat16, device=dev)
+    dGate = torch.empty(E, D, dtype=torch.bfloat16, device=dev)
+    ws_bytes = int(lib.ffm_route_backward_workspace_bytes(N, D, E))
+    ws = _workspace(dev, ws_bytes, "route_bwd")
+    rc = lib.ffm_route_backward(_ptr(gw), _ptr(routing.topk_w), _ptr(routing.topk_idx), _ptr(routing.logits),
+                                _ptr(routing.lse), _ptr(gaux), float(gz), _ptr(hidden), _ptr(gate_w), N, D, E,
+                                routing.top_k, _lib.GATING[gating], 1 if accumulate else 0, _ptr(dH), _ptr(dGate),
+                                _ptr(ws), ws.numel(), _stream())
+    _lib.check(rc, "ffm_route_backward")
+    return dH, dGate

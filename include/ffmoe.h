@@ -1,0 +1,191 @@
+/*
+ * libffmoe — C ABI of the sm_100a fused Mixture-of-Experts layer.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream; none of them allocates,
+ * synchronises or throws. They enqueue work on `stream` and return FFM_OK or a negative FFM_ERR_* code
+ * (argument validation and launch errors). Failures that can only be seen on the device (a bounded wait
+ * that ran out) are written to the caller's `status` word, which must be zero-initialised device memory;
+ * the first failure wins and later kernels keep running on whatever data is there.
+ *
+ * The reference project (FlashFusedMoE, Python + Triton + torch.bmm) has no C boundary of its own; each
+ * declaration below cites the reference Python/Triton routine whose work it takes over.
+ *
+ * Data layout shared by all entry points
+ * --------------------------------------
+ *   N tokens, D model width, H = ffn_dim / 2, E experts (E_local with expert parallelism), k = top_k,
+ *   T = N * k routed rows. All activations and weights are bf16, row-major, contiguous.
+ *   "Grouped rows": routed rows sorted by expert, stable in (token, slot) order, each expert's segment
+ *   starting on a multiple of 128 rows (the MMA tile height). Rows between the end of an expert's tokens
+ *   and the next multiple of 128 are zero. Buffers hold ffm_rows_capacity(T, E) rows.
+ *     tile_start[E + 1]  int32  cumulative count of 128-row tiles per expert (tile_start[E] = tiles in use)
+ *     pos[T]             int32  grouped row of flat slot i = n * k + j          (reference: expand_to_batch)
+ *     src[rows_cap]      int32  flat slot held by a grouped row, -1 for padding (reference: sorted_order)
+ */
+#ifndef FFMOE_H_
+#define FFMOE_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FFM_VERSION 100
+
+/* Return codes */
+#define FFM_OK 0
+#define FFM_ERR_BAD_ARG (-1)      /* null pointer, negative size, unknown enum */
+#define FFM_ERR_UNSUPPORTED (-2)  /* shape outside what the kernels handle (see each function) */
+#define FFM_ERR_LAUNCH (-3)       /* cudaGetLastError() after a launch, or a driver call failed */
+#define FFM_ERR_WORKSPACE (-4)    /* workspace too small */
+#define FFM_ERR_NO_DRIVER (-5)    /* cuTensorMapEncodeTiled could not be resolved */
+
+/* Device-side status codes written into *status (0 = fine) */
+#define FFM_STATUS_WAIT_PRODUCER 101 /* TMA producer gave up waiting for a free stage */
+#define FFM_STATUS_WAIT_MMA 102      /* MMA issuer gave up waiting for operands or a free accumulator */
+#define FFM_STATUS_WAIT_EPILOGUE 103 /* epilogue gave up waiting for an accumulator */
+#define FFM_STATUS_BAD_INDEX 104     /* an expert index or row position was out of range */
+
+/* Gating */
+#define FFM_GATING_SOFTMAX 0
+#define FFM_GATING_SIGMOID 1
+
+/* GLU activations (gate = first H rows of w_up, up = last H rows) */
+#define FFM_ACT_SWIGLU 0
+#define FFM_ACT_GEGLU_TANH 1
+#define FFM_ACT_RELU2 2
+#define FFM_ACT_GEGLU_ERF 3
+
+/* Operand majorness for ffm_grouped_gemm */
+#define FFM_B_KMAJOR 0  /* B stored [groups * n, k]: out = A * B^T   (forward projections) */
+#define FFM_B_NMAJOR 1  /* B stored [groups * k, n]: out = A * B     (input-gradient GEMMs) */
+
+typedef void* ffm_stream_t; /* cudaStream_t */
+
+int ffm_version(void);
+const char* ffm_error_string(int code);
+
+/* Rows a grouped buffer must hold for T routed rows over E experts: 128 * floor((T + 127 E) / 128). */
+int64_t ffm_rows_capacity(int64_t T, int E);
+
+/* Set the cycle budget of every bounded device-side wait (default 2e9, about one second). Returns the old value. */
+long long ffm_set_wait_cycles(long long cycles);
+
+/* -------------------------------------------------------------------------------------------------
+ * Routing forward: gate GEMM + scoring + top-k + renormalisation + loss statistics + grouped-row map.
+ * Replaces fused_moe.py:327-348 (gate matmul, _apply_routing, argsort/bincount/cumsum),
+ * kernels/fused_topk.py:31-136 (iterative-argmax top-k, lowest index wins ties, descending order) and the
+ * loss block fused_moe.py:1160-1194.
+ *
+ * Logits are accumulated in fp32, rounded to bf16 and re-widened before selection, as the reference's
+ * bf16 GEMM output is. Selection uses logit (+ expert_bias) for softmax gating and sigmoid(logit)
+ * (+ expert_bias) for sigmoid gating; weights always come from the unbiased values and are multiplied by
+ * weight_scale (scoring_factor / top_k, or 1).
+ *
+ *   hidden [N, D] bf16, gate_w [E, D] bf16, expert_bias [E] f32 or NULL
+ *   logits [N, E] bf16 out (may be NULL), topk_w [N, k] f32 out, topk_idx [N, k] int32 out, lse [N] f32 out
+ *   counts [E] int32 out, tile_start [E + 1] int32 out, pos [T] int32 out, src [rows_cap] int32 out
+ *   stats [E + 2] f32 out: stats[e] = sum of routing probability mass of expert e (softmax: selected
+ *     weights; sigmoid: all scores), stats[E] = sum_n lse[n]^2, stats[E + 1] = sum_e counts[e] * stats[e]
+ *   workspace: ffm_route_workspace_bytes(N, E, k) bytes
+ * Limits: D % 8 == 0, 1 <= k <= min(E, 32), E <= 256.
+ * ------------------------------------------------------------------------------------------------- */
+size_t ffm_route_workspace_bytes(int64_t N, int E, int top_k);
+int ffm_route_forward(const void* hidden, const void* gate_w, const float* expert_bias, int64_t N, int D, int E,
+                      int top_k, int gating, float weight_scale, void* logits, float* topk_w, int32_t* topk_idx,
+                      float* lse, int32_t* counts, int32_t* tile_start, int32_t* pos, int32_t* src,
+                      int64_t rows_cap, float* stats, void* workspace, size_t workspace_bytes, int32_t* status,
+                      ffm_stream_t stream);
+
+/* Grouped-row map from given expert ids (no gate GEMM): used on the receiving side of expert parallelism,
+ * where rows arrive already tagged with a local expert id. Replaces fused_moe.py:704-707.
+ *   expert_ids [T] int32 in; outputs as in ffm_route_forward. */
+int ffm_group_rows(const int32_t* expert_ids, int64_t T, int E, int32_t* counts, int32_t* tile_start, int32_t* pos,
+                   int32_t* src, int64_t rows_cap, void* workspace, size_t workspace_bytes, int32_t* status,
+                   ffm_stream_t stream);
+
+/* -------------------------------------------------------------------------------------------------
+ * Permute: grouped[r, :] = x[src[r] / k, :] for src[r] >= 0, zero otherwise.
+ * Replaces fused_routing_scatter (kernels/moe_ops.py:53-149) without the padded [E, max_tokens, D] buffer.
+ * Limits: D % 8 == 0.
+ * ------------------------------------------------------------------------------------------------- */
+int ffm_permute_rows(const void* x, const int32_t* src, int64_t rows_cap, int top_k, int D, void* grouped,
+                     ffm_stream_t stream);
+
+/* -------------------------------------------------------------------------------------------------
+ * Grouped GEMMs on tcgen05 / TMEM tiles fed by TMA (128 x 256 x 64 tiles, fp32 accumulation).
+ * tile_start == NULL selects the dense case: one group, `rows` rows of A (any value, masked at the edge).
+ *
+ * ffm_grouped_gemm_glu:  act[r, :] = glu(A[r, :] * Wg[e]^T, A[r, :] * Wu[e]^T), optional preact[r, 0:2H].
+ *   Replaces torch.bmm up-projection + activation_forward (fused_moe.py:435-438,
+ *   kernels/activations.py:28-74). Gate and up pre-activations are rounded to bf16 before the activation,
+ *   as the reference's bf16 bmm output is. w_gate / w_up are [groups * group_rows, K] row-major with the
+ *   group's gate rows starting at row e * group_rows of w_gate and its up rows at e * group_rows of w_up;
+ *   for stacked expert weights pass w_gate = w_up_tensor, w_up = w_up_tensor + H * K, group_rows = 2H.
+ *   Limits: K % 64 == 0, H % 32 == 0.
+ *
+ * ffm_grouped_gemm: out[r, 0:Nout] = scale * A[r, :] * op(B[e]).
+ *   Replaces the down-projection bmm (fused_moe.py:441) and the input-gradient bmms (:547, :553).
+ *   Limits: K % 64 == 0, Nout % 32 == 0 (b_major = FFM_B_NMAJOR also needs Nout % 64 == 0).
+ *
+ * ffm_grouped_gemm_wgrad: dW[e][m, n] = scale * sum over the rows r of expert e of A[r, m] * B[r, n].
+ *   Replaces the weight-gradient bmms (fused_moe.py:564-565, :961-966). A is [rows_cap, M], B is
+ *   [rows_cap, Nout], dW is [groups, M, Nout]. Padding rows must be finite in A and zero in A or B.
+ *   Limits: M % 64 == 0, Nout % 64 == 0.
+ * ------------------------------------------------------------------------------------------------- */
+int ffm_grouped_gemm_glu(const void* A, const void* w_gate, const void* w_up, int64_t group_rows, int groups,
+                         const int32_t* tile_start, int64_t rows, int K, int H, int activation, void* act,
+                         void* preact, int32_t* status, ffm_stream_t stream);
+int ffm_grouped_gemm(const void* A, const void* B, int b_major, int groups, const int32_t* tile_start,
+                     int64_t rows, int K, int Nout, float scale, void* out, int32_t* status, ffm_stream_t stream);
+int ffm_grouped_gemm_wgrad(const void* A, const void* B, int groups, const int32_t* tile_start, int64_t rows_cap,
+                           int M, int Nout, float scale, void* dW, int32_t* status, ffm_stream_t stream);
+
+/* -------------------------------------------------------------------------------------------------
+ * Combine forward: out[n, :] = sum_j w[n, j] * Y[pos[n k + j], :] (+ addend[n, :]), fp32 accumulation.
+ * w (f32) is rounded to bf16 before the multiply, as the reference does (fused_moe.py:412); w == NULL
+ * means 1. Replaces fused_gather_reduce (kernels/moe_ops.py:166-241). Limits: D % 8 == 0, k <= 32.
+ * ------------------------------------------------------------------------------------------------- */
+int ffm_combine_forward(const void* Y, const int32_t* pos, const float* w, const void* addend, int64_t N,
+                        int top_k, int D, void* out, ffm_stream_t stream);
+
+/* -------------------------------------------------------------------------------------------------
+ * Combine backward, one pass over the grouped rows:
+ *   gw[i]     = <Y[r, :], go[n, :]>         (f32; routing-weight gradient, fused_moe.py:527-535)
+ *   gYw[r, :] = go[n, :] * bf16(w[i])       (fused_weighted_scatter, kernels/moe_ops.py:258-332)
+ * with i = src[r], n = i / k; padding rows of gYw are written as zero. Y may be NULL (gw not produced).
+ * ------------------------------------------------------------------------------------------------- */
+int ffm_combine_backward(const void* go, const void* Y, const float* w, const int32_t* src, int64_t rows_cap,
+                         int top_k, int D, void* gYw, float* gw, ffm_stream_t stream);
+
+/* -------------------------------------------------------------------------------------------------
+ * GLU backward: gU[r, 0:H] = d gate, gU[r, H:2H] = d up from dAct[r, 0:H] and preact[r, 0:2H].
+ * Replaces activation_backward (kernels/activations.py:78-231). tile_start/groups bound the rows in use
+ * (NULL: all `rows`). Limits: H % 8 == 0.
+ * ------------------------------------------------------------------------------------------------- */
+int ffm_glu_backward(const void* dAct, const void* preact, const int32_t* tile_start, int groups, int64_t rows,
+                     int H, int activation, void* gU, ffm_stream_t stream);
+
+/* -------------------------------------------------------------------------------------------------
+ * Routing backward (fused_moe.py:573-591, :915-932) plus the analytic gradients of the two losses.
+ *   gl[n, :]  = bf16( scatter(softmax/sigmoid Jacobian applied to gw + aux term)
+ *                     + gz * 2 lse[n] / N * softmax(logits[n, :])                 (z-loss, fused_moe.py:1193)
+ *                     + sigmoid gating only: gaux_e * s (1 - s) / N )              (aux loss, :1186-1189)
+ *   dH[n, :] += gl[n, :] * gate_w           (accumulate = 0 overwrites)
+ *   dGate     = gl^T * hidden
+ * gaux [E] f32 or NULL: d loss / d P_e (softmax gating: added to gw of every slot routed to e).
+ * gz: d loss / d (sum_n lse^2 / N), i.e. z_loss_coeff * upstream gradient; 0 disables the term.
+ * workspace: ffm_route_backward_workspace_bytes(N, D, E).
+ * ------------------------------------------------------------------------------------------------- */
+size_t ffm_route_backward_workspace_bytes(int64_t N, int D, int E);
+int ffm_route_backward(const float* gw, const float* topk_w, const int32_t* topk_idx, const void* logits,
+                       const float* lse, const float* gaux, float gz, const void* hidden, const void* gate_w,
+                       int64_t N, int D, int E, int top_k, int gating, int accumulate, void* dH, void* dGate,
+                       void* workspace, size_t workspace_bytes, ffm_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* FFMOE_H_ */
