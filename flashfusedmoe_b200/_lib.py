@@ -47,7 +47,7 @@ SIGNATURES = {
                                      c_void_p, c_void_p]),
     "ffm_glu_backward": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_void_p, c_void_p]),
     "ffm_route_backward_workspace_bytes": (c_size_t, [c_int64, c_int, c_int]),
-    "ffm_route_backward": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p,
+    "ffm_route_backward": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                    c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
                                    c_void_p, c_size_t, c_void_p]),
 }

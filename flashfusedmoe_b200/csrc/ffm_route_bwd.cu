@@ -23,13 +23,14 @@ __device__ __forceinline__ int round_up8(int x) { return (x + 7) & ~7; }
 __global__ void __launch_bounds__(RB_THREADS)
 route_bwd_token(const float* __restrict__ gw, const float* __restrict__ topk_w, const int32_t* __restrict__ topk_idx,
                 const bf16* __restrict__ logits, const float* __restrict__ lse, const float* __restrict__ gaux,
-                float gz, const bf16* __restrict__ gate_w, long long N, int D, int E, int top_k, int gating,
+                const float* __restrict__ gz_ptr, const bf16* __restrict__ gate_w, long long N, int D, int E, int top_k, int gating,
                 int accumulate, bf16* __restrict__ gl_out, bf16* __restrict__ dH) {
   const int lane = threadIdx.x & 31;
   const int chunks = D >> 3;
   const int groups = (E + 31) >> 5;
   const int ldg_ = round_up8(E);
   const float inv_n = 1.0f / static_cast<float>(N);
+  const float gz = (gz_ptr != nullptr) ? __ldg(gz_ptr) : 0.0f;
 
   for (long long n = static_cast<long long>(blockIdx.x) * RB_WARPS + (threadIdx.x >> 5); n < N;
        n += static_cast<long long>(gridDim.x) * RB_WARPS) {
@@ -235,15 +236,15 @@ extern "C" size_t ffm_route_backward_workspace_bytes(int64_t N, int D, int E) {
 }
 
 extern "C" int ffm_route_backward(const float* gw, const float* topk_w, const int32_t* topk_idx, const void* logits,
-                                  const float* lse, const float* gaux, float gz, const void* hidden,
+                                  const float* lse, const float* gaux, const float* gz, const void* hidden,
                                   const void* gate_w, int64_t N, int D, int E, int top_k, int gating, int accumulate,
                                   void* dH, void* dGate, void* workspace, size_t workspace_bytes,
                                   ffm_stream_t stream) {
   if (!gw || !topk_w || !topk_idx || !hidden || !gate_w || !dH || !dGate || !workspace) return FFM_ERR_BAD_ARG;
   if (N < 0 || D <= 0 || E < 1 || top_k < 1) return FFM_ERR_BAD_ARG;
   if (gating != FFM_GATING_SOFTMAX && gating != FFM_GATING_SIGMOID) return FFM_ERR_BAD_ARG;
-  const bool need_logits = gating == FFM_GATING_SIGMOID || gz != 0.0f;
-  if (need_logits && (!logits || (gz != 0.0f && !lse))) return FFM_ERR_BAD_ARG;
+  const bool need_logits = gating == FFM_GATING_SIGMOID || gz != nullptr;
+  if (need_logits && (!logits || (gz != nullptr && !lse))) return FFM_ERR_BAD_ARG;
   if (D % 8 != 0 || E > MAX_E || top_k > 32 || top_k > E) return FFM_ERR_UNSUPPORTED;
   if (workspace_bytes < ffm_route_backward_workspace_bytes(N, D, E)) return FFM_ERR_WORKSPACE;
   cudaStream_t s = static_cast<cudaStream_t>(stream);

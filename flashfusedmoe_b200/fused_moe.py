@@ -1,0 +1,611 @@
+"""Functional API of the fused MoE layer: gate -> top-k route -> GLU experts -> weighted combine.
+
+Same call signature, return value and error behaviour as the reference's
+`flashfusemoe.fused_moe` (src/flashfusemoe/fused_moe.py:1073-1246); every tensor operation runs in the
+sm_100a kernels of libffmoe through `flashfusedmoe_b200.ops`. There is no CPU path and no other backend.
+
+Semantics kept from the reference's CUDA path, with the places where this implementation chooses differently:
+  * compute dtype is the autocast dtype if autocast is on, else the input dtype (fused_moe.py:93-97); only
+    bfloat16 is implemented, anything else raises;
+  * routing indices follow the Triton kernel's rule (lowest index wins ties) on bf16-rounded logits;
+  * `aux_loss` and `z_loss` are returned as differentiable tensors whose gradients are folded analytically
+    into the routing backward. On the reference's CUDA fast path the softmax-gating aux loss carries no
+    gradient (fused_topk.py:161-162); `set_aux_loss_grad("reference_cuda")` reproduces that;
+  * there is no padded [E, max_tokens, D] buffer, so no token is ever dropped by overflow.
+    `max_tokens_per_expert` is only consulted when `allow_dropped_tokens=False` and the caller gave a value:
+    the same RuntimeError("MoE routing overflow ...") is raised if an expert received more rows;
+  * expert parallelism (ep_group / set_ep_group) keeps the reference's backward contract: `grad_hidden` holds
+    the routing and shared-expert terms only and expert weight gradients are scaled by 1 / ep_size
+    (fused_moe.py:956-966, :1001-1005).
+"""
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from . import _lib, ops
+from .expert_parallel import all_to_all_rows, exchange_counts, local_ids_from_counts
+
+_WEIGHT_EPS = 1e-6
+
+# Process-wide expert-parallel state (reference: fused_moe.py:67-69). One EP group per process.
+_EP_GROUP = None
+_EP_ACTIVE = False
+_EP_BACKEND = "nccl"
+
+# "analytic": aux loss back-propagates into the gate; "reference_cuda": constant for softmax gating.
+_AUX_LOSS_GRAD = "analytic"
+
+_side_streams = {}
+_dense_tile_start = {}
+
+
+def set_aux_loss_grad(mode):
+    """Choose how the load-balance loss back-propagates: "analytic" (default) or "reference_cuda"."""
+    global _AUX_LOSS_GRAD
+    if mode not in ("analytic", "reference_cuda"):
+        raise ValueError(f"unknown aux loss gradient mode: {mode}")
+    _AUX_LOSS_GRAD = mode
+
+
+def _get_side_stream(name, priority=0):
+    idx = torch.cuda.current_device()
+    key = (idx, name)
+    if key not in _side_streams:
+        _side_streams[key] = torch.cuda.Stream(device=idx, priority=priority)
+    return _side_streams[key]
+
+
+def _get_compute_dtype(fallback_dtype):
+    if torch.is_autocast_enabled("cuda"):
+        return torch.get_autocast_dtype("cuda")
+    return fallback_dtype
+
+
+def _estimate_max_tokens(N, top_k, E):
+    """The reference's static per-expert buffer bound (fused_moe.py:100-113): twice the balanced share,
+    or every routed row when there are at most 4 rows per expert. Kept for callers that size buffers with it;
+    the kernels here do not need it."""
+    balanced = -(-N * top_k // E)
+    bound = balanced + max(balanced, top_k)
+    if N * top_k <= 4 * E:
+        bound = N * top_k
+    return bound
+
+
+def _validate_inputs(hidden_states, gate_weight, w_up, w_down, top_k, activation, gating, ep_group=None):
+    assert hidden_states.dim() == 2, f"hidden_states must be 2D [N, D], got {hidden_states.shape}"
+    N, D = hidden_states.shape
+    E = gate_weight.shape[0]
+    E_w = w_up.shape[0]
+    ffn_dim = w_up.shape[1]
+    assert gate_weight.shape == (E, D), f"gate_weight must be [{E}, {D}], got {gate_weight.shape}"
+    assert w_up.shape == (E_w, ffn_dim, D), f"w_up must be [{E_w}, {ffn_dim}, {D}], got {w_up.shape}"
+    assert w_down.shape == (E_w, D, ffn_dim // 2), \
+        f"w_down must be [{E_w}, {D}, {ffn_dim // 2}], got {w_down.shape}"
+    if ep_group is not None:
+        ep_size = torch.distributed.get_world_size(ep_group)
+        assert E % ep_size == 0, f"n_experts ({E}) must be divisible by ep_size ({ep_size})"
+        assert E_w == E // ep_size, f"With EP, w_up must have E/ep_size={E // ep_size} experts, got {E_w}"
+    else:
+        assert E_w == E, f"w_up must have {E} experts, got {E_w}"
+    assert ffn_dim % 2 == 0, f"ffn_dim must be even, got {ffn_dim}"
+    assert 1 <= top_k <= E, f"top_k must be in [1, {E}], got {top_k}"
+    dev = hidden_states.device
+    assert all(t.device == dev for t in [gate_weight, w_up, w_down]), "All tensors must be on same device"
+    assert activation in ("swiglu", "geglu", "relu_squared"), f"Unknown activation: {activation}"
+    assert gating in ("softmax", "sigmoid"), f"Unknown gating: {gating}"
+
+
+@dataclass
+class _Cfg:
+    top_k: int
+    activation: str
+    gating: str
+    aux_loss_coeff: float
+    z_loss_coeff: float
+    recompute: bool
+    expert_bias: Optional[torch.Tensor]
+    weight_scale: float
+    aux_grad: str
+    shared_activation: str = "swiglu"
+    ep_group: object = None
+    ep_full_input_grad: bool = False
+
+
+def _to(t, dtype):
+    t = t if t.dtype == dtype else t.to(dtype)
+    return t if t.is_contiguous() else t.contiguous()
+
+
+def _dense_ts(rows, device):
+    """tile_start for a single dense group of `rows` rows (cached per size; a tiny host-to-device copy)."""
+    key = (torch.device(device).index, int(rows))
+    t = _dense_tile_start.get(key)
+    if t is None:
+        t = torch.tensor([0, (rows + 127) // 128], dtype=torch.int32, device=device)
+        _dense_tile_start[key] = t
+    return t
+
+
+def _loss_tensors(routing, N, E, cfg):
+    """aux = c E sum_e f_e P_e and z = c_z mean(lse^2) from the routing kernel's statistics (no host sync)."""
+    aux = routing.stats[E + 1] * (cfg.aux_loss_coeff * E / (float(N) * float(N)))
+    z = routing.stats[E] * (cfg.z_loss_coeff / float(N))
+    return aux, z
+
+
+def _loss_grads(routing, N, E, cfg, grad_aux, grad_z):
+    """Device tensors fed to the routing backward: d loss / d P_e and d loss / d mean(lse^2)."""
+    gaux = None
+    if cfg.aux_loss_coeff > 0.0 and grad_aux is not None and (cfg.aux_grad == "analytic" or cfg.gating == "sigmoid"):
+        gaux = routing.counts.to(torch.float32) * (grad_aux.to(torch.float32) * (cfg.aux_loss_coeff * E / float(N)))
+    gz = None
+    if cfg.z_loss_coeff > 0.0 and grad_z is not None:
+        gz = (grad_z.to(torch.float32) * cfg.z_loss_coeff).reshape(1).contiguous()
+    return gaux, gz
+
+
+# ----------------------------------------------------------------------------------------------
+# Dense GLU FFN (shared expert) on the same kernels: one group, stacked [gate; up] weights
+# ----------------------------------------------------------------------------------------------
+
+def _glu_ffn_forward(x, w_gate, w_up, w_down, activation, want_preact):
+    Hs, D = w_gate.shape
+    act, pre = ops.grouped_gemm_glu(x, w_gate, w_up, Hs, 1, None, D, Hs, activation, want_preact=want_preact)
+    y = ops.grouped_gemm(act, w_down, _lib.B_KMAJOR, 1, None, Hs, D)
+    return y, act, pre
+
+
+def _glu_ffn_backward(go, x, act, pre, w_gate, w_up, w_down, activation):
+    Hs, D = w_gate.shape
+    d_act = ops.grouped_gemm(go, w_down, _lib.B_NMAJOR, 1, None, D, Hs)
+    gU = ops.glu_backward(d_act, pre, None, 1, activation)
+    w_cat = torch.cat([w_gate, w_up], dim=0)
+    dx = ops.grouped_gemm(gU, w_cat, _lib.B_NMAJOR, 1, None, 2 * Hs, D)
+    ts = _dense_ts(x.shape[0], x.device)
+    d_wcat = ops.grouped_gemm_wgrad(gU, x, 1, ts)[0]
+    d_wdown = ops.grouped_gemm_wgrad(go, act, 1, ts)[0]
+    return dx, d_wcat[:Hs], d_wcat[Hs:], d_wdown
+
+
+class _GLUFFNFunction(torch.autograd.Function):
+    """y = act(x Wg^T) * (x Wu^T) Wd^T for the non-EP shared expert (reference: nn.py:22-44)."""
+
+    @staticmethod
+    def forward(ctx, x, w_gate, w_up, w_down, activation, dtype):
+        xs = _to(x, dtype)
+        wg, wu, wd = _to(w_gate, dtype), _to(w_up, dtype), _to(w_down, dtype)
+        y, act, pre = _glu_ffn_forward(xs, wg, wu, wd, activation, want_preact=True)
+        ctx.save_for_backward(xs, act, pre, wg, wu, wd)
+        ctx.activation = activation
+        ctx.in_dtypes = (x.dtype, w_gate.dtype, w_up.dtype, w_down.dtype)
+        return y
+
+    @staticmethod
+    def backward(ctx, go):
+        xs, act, pre, wg, wu, wd = ctx.saved_tensors
+        go = _to(go, xs.dtype)
+        dx, dwg, dwu, dwd = _glu_ffn_backward(go, xs, act, pre, wg, wu, wd, ctx.activation)
+        dt = ctx.in_dtypes
+        return dx.to(dt[0]), dwg.to(dt[1]), dwu.to(dt[2]), dwd.to(dt[3]), None, None
+
+
+def glu_ffn(x, w_gate, w_up, w_down, activation="swiglu"):
+    """Dense GLU feed-forward on the library's GEMM kernels. x [N, D] -> [N, D]."""
+    dtype = _require_bf16(_get_compute_dtype(x.dtype))
+    return _GLUFFNFunction.apply(x, w_gate, w_up, w_down, activation, dtype)
+
+
+def _require_bf16(dtype):
+    if dtype != torch.bfloat16:
+        raise NotImplementedError(
+            f"flashfusedmoe_b200 computes in bfloat16 on sm_100a; got compute dtype {dtype}. Pass bf16 tensors "
+            "or run under torch.autocast('cuda', dtype=torch.bfloat16).")
+    return dtype
+
+
+# ----------------------------------------------------------------------------------------------
+# Single-GPU layer
+# ----------------------------------------------------------------------------------------------
+
+class _FusedMoEFunction(torch.autograd.Function):
+    """Routed experts on one GPU. Outputs: (out [N, D], aux_loss, z_loss, tokens_per_expert)."""
+
+    @staticmethod
+    def forward(ctx, hidden_states, gate_weight, w_up, w_down, addend, cfg, dtype):
+        N, D = hidden_states.shape
+        E = gate_weight.shape[0]
+        H = w_up.shape[1] // 2
+        k = cfg.top_k
+        h = _to(hidden_states, dtype)
+        g = _to(gate_weight, dtype)
+        wu = _to(w_up, dtype)
+        wd = _to(w_down, dtype)
+        add = None if addend is None else _to(addend, dtype)
+
+        routing = ops.route_forward(h, g, k, cfg.gating, cfg.expert_bias, cfg.weight_scale)
+        Xg = ops.permute_rows(h, routing.src, routing.rows_cap, k)
+        need_grad = any(ctx.needs_input_grad[:5])
+        keep = need_grad and not cfg.recompute
+        act, pre = ops.grouped_gemm_glu(Xg, wu, wu.view(-1, D)[H:], 2 * H, E, routing.tile_start, D, H,
+                                        cfg.activation, want_preact=keep)
+        Y = ops.grouped_gemm(act, wd, _lib.B_KMAJOR, E, routing.tile_start, H, D)
+        out = ops.combine_forward(Y, routing.pos, routing.topk_w, N, k, addend=add)
+        aux, z = _loss_tensors(routing, N, E, cfg)
+
+        ctx.set_materialize_grads(False)
+        ctx.cfg = cfg
+        ctx.shape = (N, D, E, H)
+        ctx.rows_cap = routing.rows_cap
+        ctx.in_dtypes = (hidden_states.dtype, gate_weight.dtype, w_up.dtype, w_down.dtype,
+                         None if addend is None else addend.dtype)
+        saved = [h, g, wu, wd, routing.topk_w, routing.topk_idx, routing.logits, routing.lse, routing.counts,
+                 routing.tile_start, routing.pos, routing.src, Xg]
+        if keep:
+            saved += [pre, act, Y]
+        ctx.kept = keep
+        ctx.save_for_backward(*saved)
+        counts = routing.counts
+        ctx.mark_non_differentiable(counts)
+        return out, aux, z, counts
+
+    @staticmethod
+    def backward(ctx, grad_out, grad_aux, grad_z, _grad_counts):
+        cfg = ctx.cfg
+        N, D, E, H = ctx.shape
+        k = cfg.top_k
+        saved = ctx.saved_tensors
+        (h, g, wu, wd, topk_w, topk_idx, logits, lse, counts, tile_start, pos, src, Xg) = saved[:13]
+        if ctx.kept:
+            pre, act, Y = saved[13:16]
+        else:
+            # recompute the three large tensors with the same kernels: bit-identical to the forward pass
+            act, pre = ops.grouped_gemm_glu(Xg, wu, wu.view(-1, D)[H:], 2 * H, E, tile_start, D, H, cfg.activation,
+                                            want_preact=True)
+            Y = ops.grouped_gemm(act, wd, _lib.B_KMAJOR, E, tile_start, H, D)
+        routing = ops.Routing(topk_w, topk_idx, logits, lse, counts, tile_start, pos, src, None, ctx.rows_cap, k, E)
+        if grad_out is None:
+            grad_out = torch.zeros(N, D, dtype=h.dtype, device=h.device)
+        go = _to(grad_out, h.dtype)  # also densifies expanded (stride-0) gradients
+
+        gYw, gw = ops.combine_backward(go, Y, topk_w, src, ctx.rows_cap, k)
+        d_act = ops.grouped_gemm(gYw, wd, _lib.B_NMAJOR, E, tile_start, D, H)
+        gU = ops.glu_backward(d_act, pre, tile_start, E, cfg.activation)
+        dXg = ops.grouped_gemm(gU, wu, _lib.B_NMAJOR, E, tile_start, 2 * H, D)
+        dH = ops.combine_forward(dXg, pos, None, N, k)
+        d_wd = ops.grouped_gemm_wgrad(gYw, act, E, tile_start)
+        d_wu = ops.grouped_gemm_wgrad(gU, Xg, E, tile_start)
+        gaux, gz = _loss_grads(routing, N, E, cfg, grad_aux, grad_z)
+        dH, d_gate = ops.route_backward(gw, routing, gaux, gz, h, g, cfg.gating, dH=dH)
+
+        dt = ctx.in_dtypes
+        d_add = None
+        if dt[4] is not None and ctx.needs_input_grad[4]:
+            d_add = go.to(dt[4])
+        return (dH.to(dt[0]), d_gate.to(dt[1]), d_wu.to(dt[2]), d_wd.to(dt[3]), d_add, None, None)
+
+
+# ----------------------------------------------------------------------------------------------
+# Expert-parallel layer
+# ----------------------------------------------------------------------------------------------
+
+def _compact_send_map(routing, T):
+    """Send-buffer position of every flat slot: the grouped order with the 128-row padding squeezed out.
+    Rows are expert-major, hence destination-rank-major (each rank owns a contiguous block of experts)."""
+    counts = routing.counts.to(torch.int64)
+    starts = torch.cumsum(counts, 0) - counts
+    pad = routing.tile_start[:-1].to(torch.int64) * 128 - starts
+    cpos = (routing.pos.to(torch.int64) - pad[routing.topk_idx.reshape(-1).to(torch.int64)])
+    src_c = torch.empty(T, dtype=torch.int32, device=cpos.device)
+    src_c[cpos] = torch.arange(T, dtype=torch.int32, device=cpos.device)
+    return cpos.to(torch.int32), src_c
+
+
+class _FusedMoEEPFunction(torch.autograd.Function):
+    """Expert-parallel layer: route -> all-to-all dispatch -> local grouped GEMMs -> all-to-all combine.
+
+    Mirrors reference _FusedMoEEPAutograd (fused_moe.py:598-1022): shared expert on a high-priority side
+    stream, optional latent projection around both exchanges, backward with one exchange of the weighted
+    output gradient, no expert input gradient unless cfg.ep_full_input_grad.
+    """
+
+    @staticmethod
+    def forward(ctx, hidden_states, gate_weight, w_up, w_down, sw_gate, sw_up, sw_down, lw_down, lw_up, cfg, dtype):
+        group = cfg.ep_group
+        ep = torch.distributed.get_world_size(group)
+        N, D = hidden_states.shape
+        El = w_up.shape[0]
+        E = ep * El
+        H = w_up.shape[1] // 2
+        k = cfg.top_k
+        T = N * k
+        has_shared = sw_gate is not None
+        has_latent = lw_down is not None
+        h = _to(hidden_states, dtype)
+        g = _to(gate_weight, dtype)
+        wu = _to(w_up, dtype)
+        wd = _to(w_down, dtype)
+        need_grad = any(ctx.needs_input_grad[:9])
+
+        routing = ops.route_forward(h, g, k, cfg.gating, cfg.expert_bias, cfg.weight_scale)
+
+        # shared expert on a side stream: queued before the host waits for the split sizes
+        shared = None
+        if has_shared:
+            swg, swu, swd = _to(sw_gate, dtype), _to(sw_up, dtype), _to(sw_down, dtype)
+            side = _get_side_stream("shared", priority=-1)
+            ready = torch.cuda.Event()
+            ready.record()
+            with torch.cuda.stream(side):
+                side.wait_event(ready)
+                s_out, s_act, s_pre = _glu_ffn_forward(h, swg, swu, swd, cfg.shared_activation, want_preact=need_grad)
+            shared_done = torch.cuda.Event()
+            shared_done.record(side)
+            shared = (s_out, s_act, s_pre, swg, swu, swd)
+
+        if has_latent:
+            lwd, lwu = _to(lw_down, dtype), _to(lw_up, dtype)
+            L = lwd.shape[0]
+            disp = ops.grouped_gemm(h, lwd, _lib.B_KMAJOR, 1, None, D, L)   # [N, L]
+        else:
+            disp = h
+
+        recv_counts, send_splits, recv_splits = exchange_counts(routing.counts, ep, group)
+        M = sum(recv_splits)
+        cpos, src_c = _compact_send_map(routing, T)
+        send = ops.permute_rows(disp, src_c, T, k)
+        recv = all_to_all_rows(send, recv_splits, send_splits, group)        # [M, W]
+
+        if M > 0:
+            local_ids = local_ids_from_counts(recv_counts, M).to(torch.int32)
+            _, ts_l, pos_l, src_l, rows_l = ops.group_rows(local_ids, El)
+        else:
+            ts_l = pos_l = src_l = None
+            rows_l = 0
+        recv_lat = None
+        if has_latent:
+            recv_lat = recv
+            recv = ops.grouped_gemm(recv, lwu, _lib.B_KMAJOR, 1, None, L, D) if M > 0 else recv.new_empty(0, D)
+        if M > 0:
+            Xg = ops.permute_rows(recv, src_l, rows_l, 1)
+            act, pre = ops.grouped_gemm_glu(Xg, wu, wu.view(-1, D)[H:], 2 * H, El, ts_l, D, H, cfg.activation,
+                                            want_preact=need_grad)
+            Y = ops.grouped_gemm(act, wd, _lib.B_KMAJOR, El, ts_l, H, D)
+            local_out = ops.combine_forward(Y, pos_l, None, M, 1)            # back to arrival order [M, D]
+        else:
+            Xg = act = pre = None
+            local_out = h.new_empty(0, D)
+        local_out_D = local_out
+        if has_latent and M > 0:
+            local_out = ops.grouped_gemm(local_out, lwd, _lib.B_KMAJOR, 1, None, D, L)
+        elif has_latent:
+            local_out = h.new_empty(0, L)
+        returned = all_to_all_rows(local_out, send_splits, recv_splits, group)  # [T, W], send order
+        returned_lat = None
+        if has_latent:
+            returned_lat = returned
+            returned = ops.grouped_gemm(returned, lwu, _lib.B_KMAJOR, 1, None, L, D)
+        if has_shared:
+            torch.cuda.current_stream().wait_event(shared_done)
+        out = ops.combine_forward(returned, cpos, routing.topk_w, N, k, addend=shared[0] if has_shared else None)
+        aux, z = _loss_tensors(routing, N, E, cfg)
+
+        ctx.set_materialize_grads(False)
+        ctx.cfg = cfg
+        ctx.dims = (N, D, E, El, H, k, M, ep, rows_l)
+        ctx.flags = (has_shared, has_latent)
+        ctx.splits = (send_splits, recv_splits)
+        ctx.in_dtypes = tuple(None if t is None else t.dtype for t in
+                              (hidden_states, gate_weight, w_up, w_down, sw_gate, sw_up, sw_down, lw_down, lw_up))
+        ctx.routing_meta = (routing.rows_cap,)
+        tensors = dict(h=h, g=g, wu=wu, wd=wd, topk_w=routing.topk_w, topk_idx=routing.topk_idx,
+                       logits=routing.logits, lse=routing.lse, counts=routing.counts, src_c=src_c,
+                       returned=returned, ts_l=ts_l, src_l=src_l, pos_l=pos_l, Xg=Xg, act=act, pre=pre)
+        if has_shared:
+            tensors.update(s_act=shared[1], s_pre=shared[2], swg=shared[3], swu=shared[4], swd=shared[5])
+        if has_latent:
+            tensors.update(lwd=lwd, lwu=lwu, recv_lat=recv_lat, returned_lat=returned_lat, local_out_D=local_out_D)
+        ctx.names = [n for n, t in tensors.items() if t is not None]
+        ctx.save_for_backward(*[tensors[n] for n in ctx.names])
+        counts = routing.counts
+        ctx.mark_non_differentiable(counts)
+        return out, aux, z, counts
+
+    @staticmethod
+    def backward(ctx, grad_out, grad_aux, grad_z, _grad_counts):
+        cfg = ctx.cfg
+        group = cfg.ep_group
+        N, D, E, El, H, k, M, ep, rows_l = ctx.dims
+        has_shared, has_latent = ctx.flags
+        send_splits, recv_splits = ctx.splits
+        t = dict(zip(ctx.names, ctx.saved_tensors))
+        h, g, wu, wd = t["h"], t["g"], t["wu"], t["wd"]
+        T = N * k
+        if grad_out is None:
+            grad_out = torch.zeros(N, D, dtype=h.dtype, device=h.device)
+        go = _to(grad_out, h.dtype)
+        inv_ep = 1.0 / ep
+
+        # shared expert backward on the side stream
+        if has_shared:
+            side = _get_side_stream("shared", priority=-1)
+            ready = torch.cuda.Event()
+            ready.record()
+            with torch.cuda.stream(side):
+                side.wait_event(ready)
+                s_dx, s_dwg, s_dwu, s_dwd = _glu_ffn_backward(go, h, t["s_act"], t["s_pre"], t["swg"], t["swu"],
+                                                              t["swd"], cfg.shared_activation)
+            shared_done = torch.cuda.Event()
+            shared_done.record(side)
+
+        # routing-weight gradient and weighted output gradient, in send order (fused_moe.py:882-898)
+        gYw, gw = ops.combine_backward(go, t["returned"], t["topk_w"], t["src_c"], T, k)
+        if has_latent:
+            L = t["lwd"].shape[0]
+            send = ops.grouped_gemm(gYw, t["lwu"], _lib.B_NMAJOR, 1, None, D, L)
+        else:
+            send = gYw
+
+        # exchange on a side stream, routing backward meanwhile on the main stream (:901-932)
+        a2a = _get_side_stream("a2a")
+        ready2 = torch.cuda.Event()
+        ready2.record()
+        with torch.cuda.stream(a2a):
+            a2a.wait_event(ready2)
+            recv_grad = all_to_all_rows(send, recv_splits, send_splits, group)
+        a2a_done = torch.cuda.Event()
+        a2a_done.record(a2a)
+        send.record_stream(a2a)
+
+        routing = ops.Routing(t["topk_w"], t["topk_idx"], t["logits"], t["lse"], t["counts"], None, None, None, None,
+                              ctx.routing_meta[0], k, E)
+        gaux, gz = _loss_grads(routing, N, E, cfg, grad_aux, grad_z)
+        dH, d_gate = ops.route_backward(gw, routing, gaux, gz, h, g, cfg.gating, dH=None)
+
+        torch.cuda.current_stream().wait_event(a2a_done)
+        recv_grad.record_stream(torch.cuda.current_stream())
+        d_lwd = d_lwu = None
+        if has_latent:
+            recv_grad_lat = recv_grad
+            recv_grad = (ops.grouped_gemm(recv_grad_lat, t["lwu"], _lib.B_KMAJOR, 1, None, L, D)
+                         if M > 0 else recv_grad.new_empty(0, D))
+        if M > 0:
+            gYg = ops.permute_rows(recv_grad, t["src_l"], rows_l, 1)
+            d_act = ops.grouped_gemm(gYg, wd, _lib.B_NMAJOR, El, t["ts_l"], D, H)
+            gU = ops.glu_backward(d_act, t["pre"], t["ts_l"], El, cfg.activation)
+            d_wd = ops.grouped_gemm_wgrad(gYg, t["act"], El, t["ts_l"], scale=inv_ep)
+            d_wu = ops.grouped_gemm_wgrad(gU, t["Xg"], El, t["ts_l"], scale=inv_ep)
+        else:
+            d_wd = torch.zeros_like(wd)
+            d_wu = torch.zeros_like(wu)
+        if has_latent:
+            # fused_moe.py:989-999: both un-projection sites feed proj_up, the combine projection feeds proj_down
+            d_lwu = ops.grouped_gemm_wgrad(gYw, t["returned_lat"], 1, _dense_ts(T, h.device), scale=inv_ep)[0]
+            if M > 0:
+                ts_m = _dense_ts(M, h.device)
+                d_lwu = d_lwu + ops.grouped_gemm_wgrad(recv_grad, t["recv_lat"], 1, ts_m, scale=inv_ep)[0]
+                d_lwd = ops.grouped_gemm_wgrad(recv_grad_lat, t["local_out_D"], 1, ts_m, scale=inv_ep)[0]
+            else:
+                d_lwd = torch.zeros_like(t["lwd"])
+
+        s_grads = (None, None, None)
+        if has_shared:
+            torch.cuda.current_stream().wait_event(shared_done)
+            dH = dH + s_dx
+            s_grads = (s_dwg, s_dwu, s_dwd)
+        dt = ctx.in_dtypes
+
+        def cast(x, i):
+            return None if x is None or dt[i] is None else x.to(dt[i])
+
+        return (cast(dH, 0), cast(d_gate, 1), cast(d_wu, 2), cast(d_wd, 3), cast(s_grads[0], 4), cast(s_grads[1], 5),
+                cast(s_grads[2], 6), cast(d_lwd, 7), cast(d_lwu, 8), None, None)
+
+
+# ----------------------------------------------------------------------------------------------
+# Public API
+# ----------------------------------------------------------------------------------------------
+
+@torch.compiler.disable
+def set_ep_group(group, backend="nccl"):
+    """Store the expert-parallel process group for later fused_moe() calls (reference: fused_moe.py:1026-1040)."""
+    global _EP_GROUP, _EP_ACTIVE, _EP_BACKEND
+    if group is not None and backend != "nccl":
+        raise ValueError(f"ep backend {backend!r} is not available; use 'nccl'")
+    _EP_GROUP = group
+    _EP_ACTIVE = group is not None
+    _EP_BACKEND = backend if group is not None else "nccl"
+
+
+def _metrics(losses, counts, N, top_k, capacity_factor, E):
+    tpe = counts.to(torch.float32)
+    losses["tokens_per_expert"] = counts.to(torch.int32)
+    losses["max_expert_load"] = tpe.max().int()
+    losses["min_expert_load"] = tpe.min().int()
+    losses["expert_load_imbalance"] = tpe.max() / (tpe.mean() + _WEIGHT_EPS)
+
+
+@torch.compiler.disable
+def fused_moe(
+    hidden_states,            # [N, D]
+    gate_weight,              # [E, D]
+    w_up,                     # [E, ffn_dim, D]  (gate rows, then up rows)
+    w_down,                   # [E, D, ffn_dim // 2]
+    top_k=2,
+    activation="swiglu",
+    gating="softmax",
+    capacity_factor=None,
+    aux_loss_coeff=0.0,
+    z_loss_coeff=0.0,
+    recompute_activations=False,
+    ep_group=None,
+    max_tokens_per_expert=None,
+    allow_dropped_tokens=False,
+    return_metrics=False,
+    shared_expert_weights=None,
+    latent_weights=None,
+    n_group=None,
+    topk_group=None,
+    scoring_factor=None,
+    pre_softmax=False,
+    input_jitter=0.0,
+    expert_bias=None,
+    _addend=None,
+):
+    """Fused MoE forward; returns (output [N, D], losses dict). Arguments as in the reference
+    (fused_moe.py:1073-1138). `_addend` is a private hook used by MoELayer to fold the shared expert's output
+    into the combine kernel."""
+    group = ep_group if ep_group is not None else (_EP_GROUP if _EP_ACTIVE else None)
+    if not _EP_ACTIVE:
+        _validate_inputs(hidden_states, gate_weight, w_up, w_down, top_k, activation, gating, ep_group=ep_group)
+    else:
+        assert hidden_states.dim() == 2, f"hidden_states must be 2D [N, D], got {hidden_states.shape}"
+        assert w_up.shape[0] < gate_weight.shape[0] or torch.distributed.get_world_size(group) == 1, \
+            f"EP mode: w_up should have E_local < E experts, got {w_up.shape[0]} >= {gate_weight.shape[0]}"
+        assert 1 <= top_k <= gate_weight.shape[0], f"top_k must be in [1, {gate_weight.shape[0]}], got {top_k}"
+        assert activation in ("swiglu", "geglu", "relu_squared"), f"Unknown activation: {activation}"
+        assert gating in ("softmax", "sigmoid"), f"Unknown gating: {gating}"
+    if capacity_factor is not None:
+        raise NotImplementedError("capacity_factor (token dropping) is not implemented in flashfusedmoe_b200 yet")
+    if n_group is not None or topk_group is not None or pre_softmax:
+        raise NotImplementedError("group-limited and pre-softmax routing are not implemented in flashfusedmoe_b200 yet")
+    if input_jitter and input_jitter > 0.0:
+        raise NotImplementedError("input_jitter is not implemented in flashfusedmoe_b200 yet")
+    if not hidden_states.is_cuda:
+        raise RuntimeError("flashfusedmoe_b200 runs on CUDA (sm_100a) tensors only; there is no CPU path")
+
+    N, D = hidden_states.shape
+    E = gate_weight.shape[0]
+    dtype = _require_bf16(_get_compute_dtype(hidden_states.dtype))
+    cfg = _Cfg(top_k=top_k, activation=activation, gating=gating, aux_loss_coeff=float(aux_loss_coeff),
+               z_loss_coeff=float(z_loss_coeff), recompute=bool(recompute_activations), expert_bias=expert_bias,
+               weight_scale=1.0 if scoring_factor is None else float(scoring_factor) / top_k,
+               aux_grad=_AUX_LOSS_GRAD, ep_group=group)
+
+    if group is not None:
+        sw = shared_expert_weights if shared_expert_weights is not None else (None, None, None)
+        lw = latent_weights if latent_weights is not None else (None, None)
+        out, aux, z, counts = _FusedMoEEPFunction.apply(hidden_states, gate_weight, w_up, w_down, sw[0], sw[1],
+                                                        sw[2], lw[0], lw[1], cfg, dtype)
+    else:
+        out, aux, z, counts = _FusedMoEFunction.apply(hidden_states, gate_weight, w_up, w_down, _addend, cfg, dtype)
+        if max_tokens_per_expert is not None and not allow_dropped_tokens:
+            actual_max = int(counts.max().item())
+            if actual_max > max_tokens_per_expert:
+                raise RuntimeError(
+                    f"MoE routing overflow: expert received {actual_max} tokens but buffer "
+                    f"is {max_tokens_per_expert}. {actual_max - max_tokens_per_expert} tokens exceed the bound "
+                    f"given by max_tokens_per_expert. Fix options:\n"
+                    f"  1. Set max_tokens_per_expert={actual_max} (or higher) via calibration\n"
+                    f"  2. Set allow_dropped_tokens=True to suppress this error")
+
+    losses = {}
+    if aux_loss_coeff > 0.0:
+        losses["aux_loss"] = aux
+    if z_loss_coeff > 0.0:
+        losses["z_loss"] = z
+    if return_metrics:
+        _metrics(losses, counts, N, top_k, capacity_factor, E)
+    return out, losses

@@ -223,7 +223,8 @@ def glu_backward(dAct, preact, tile_start, groups, activation):
 
 
 def route_backward(gw, routing, gaux, gz, hidden, gate_w, gating, dH=None):
-    """Returns (dH, dGate). If dH is given the routing term is added to it in place."""
+    """Returns (dH, dGate). If dH is given the routing term is added to it in place.
+    gaux: f32 [E] device tensor or None; gz: f32 device scalar tensor or None."""
     lib = _lib.load()
     N, D = hidden.shape
     E = gate_w.shape[0]
@@ -235,7 +236,7 @@ def route_backward(gw, routing, gaux, gz, hidden, gate_w, gating, dH=None):
     ws_bytes = int(lib.ffm_route_backward_workspace_bytes(N, D, E))
     ws = _workspace(dev, ws_bytes, "route_bwd")
     rc = lib.ffm_route_backward(_ptr(gw), _ptr(routing.topk_w), _ptr(routing.topk_idx), _ptr(routing.logits),
-                                _ptr(routing.lse), _ptr(gaux), float(gz), _ptr(hidden), _ptr(gate_w), N, D, E,
+                                _ptr(routing.lse), _ptr(gaux), _ptr(gz), _ptr(hidden), _ptr(gate_w), N, D, E,
                                 routing.top_k, _lib.GATING[gating], 1 if accumulate else 0, _ptr(dH), _ptr(dGate),
                                 _ptr(ws), ws.numel(), _stream())
     _lib.check(rc, "ffm_route_backward")

@@ -175,12 +175,13 @@ int ffm_glu_backward(const void* dAct, const void* preact, const int32_t* tile_s
  *   dH[n, :] += gl[n, :] * gate_w           (accumulate = 0 overwrites)
  *   dGate     = gl^T * hidden
  * gaux [E] f32 or NULL: d loss / d P_e (softmax gating: added to gw of every slot routed to e).
- * gz: d loss / d (sum_n lse^2 / N), i.e. z_loss_coeff * upstream gradient; 0 disables the term.
+ * gz: device pointer to one f32 = d loss / d (sum_n lse^2 / N), i.e. z_loss_coeff * upstream gradient;
+ *     NULL (or a stored 0) disables the term. A device scalar keeps the backward pass free of host syncs.
  * workspace: ffm_route_backward_workspace_bytes(N, D, E).
  * ------------------------------------------------------------------------------------------------- */
 size_t ffm_route_backward_workspace_bytes(int64_t N, int D, int E);
 int ffm_route_backward(const float* gw, const float* topk_w, const int32_t* topk_idx, const void* logits,
-                       const float* lse, const float* gaux, float gz, const void* hidden, const void* gate_w,
+                       const float* lse, const float* gaux, const float* gz, const void* hidden, const void* gate_w,
                        int64_t N, int D, int E, int top_k, int gating, int accumulate, void* dH, void* dGate,
                        void* workspace, size_t workspace_bytes, ffm_stream_t stream);
 

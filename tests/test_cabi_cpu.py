@@ -1,0 +1,66 @@
+"""CPU: libffmoe.so loads, exports every symbol include/ffmoe.h declares, and its host-only entry points
+answer without a GPU. No compute kernel is launched here."""
+
+import ctypes
+import os
+import re
+
+import pytest
+
+from flashfusedmoe_b200 import _lib
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "ffmoe.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(ffm_[a-z_0-9]+)\s*\(", text)))
+
+
+def test_library_is_built():
+    assert os.path.exists(_lib.LIB_PATH), "run `python -m flashfusedmoe_b200.build` first"
+
+
+def test_every_declared_symbol_is_exported_and_bound():
+    lib = ctypes.CDLL(_lib.LIB_PATH)
+    names = declared_symbols()
+    assert len(names) >= 16
+    for name in names:
+        assert hasattr(lib, name), f"{name} declared in ffmoe.h but not exported"
+        assert name in _lib.SIGNATURES, f"{name} has no ctypes prototype in _lib.SIGNATURES"
+    assert sorted(_lib.SIGNATURES) == names
+
+
+def test_host_only_entry_points():
+    lib = _lib.load()
+    assert lib.ffm_version() == 100
+    assert _lib.error_string(0) == "ok"
+    assert "workspace" in _lib.error_string(-4)
+    assert "epilogue" in _lib.error_string(103)
+    # rows capacity: 128 * floor((T + 127 E) / 128)
+    assert lib.ffm_rows_capacity(32768, 8) == 128 * ((32768 + 127 * 8) // 128)
+    assert lib.ffm_rows_capacity(0, 4) == 128 * ((127 * 4) // 128)
+    assert lib.ffm_route_workspace_bytes(16384, 8, 2) > 0
+    assert lib.ffm_route_backward_workspace_bytes(16384, 1024, 8) > 16384 * 8 * 2
+    old = lib.ffm_set_wait_cycles(12345)
+    assert lib.ffm_set_wait_cycles(old) == 12345
+
+
+def test_argument_validation_without_gpu():
+    lib = _lib.load()
+    # null pointers are rejected before any CUDA call
+    assert lib.ffm_permute_rows(0, 0, 128, 1, 64, 0, 0) == -1
+    assert lib.ffm_grouped_gemm(0, 0, 0, 1, 0, 128, 64, 64, 1.0, 0, 0, 0) == -1
+    assert lib.ffm_combine_forward(0, 0, 0, 0, 4, 2, 64, 0, 0) == -1
+
+
+def test_product_path_has_no_cpu_fallback():
+    import torch
+    from flashfusedmoe_b200 import fused_moe
+    h = torch.randn(4, 64).bfloat16()
+    g = torch.randn(4, 64).bfloat16()
+    wu = torch.randn(4, 128, 64).bfloat16()
+    wd = torch.randn(4, 64, 64).bfloat16()
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        fused_moe(h, g, wu, wd, top_k=2)

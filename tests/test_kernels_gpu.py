@@ -307,7 +307,8 @@ def test_route_backward(N, D, E, k, gating):
     gaux = torch.randn(E, device=DEV)
     gz = 0.37
     dH0 = torch.randn(N, D, device=DEV).bfloat16()
-    dH, dGate = ops.route_backward(gw.view(-1), r, gaux, gz, hidden, gate, gating, dH=dH0.clone())
+    dH, dGate = ops.route_backward(gw.view(-1), r, gaux, torch.tensor(gz, device=DEV), hidden, gate, gating,
+                                   dH=dH0.clone())
     # torch restatement from the kernel's own logits / indices
     lg = r.logits.float().requires_grad_()
     idx = r.topk_idx.long()
