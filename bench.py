@@ -1,0 +1,322 @@
+"""Benchmark of the fused MoE layer: tokens/s of forward + backward on synthetic data.
+
+    python bench.py --gpus N --steps K --warmup W            (N > 1: launched with torch.distributed.run)
+    python bench.py --impl reference ...                      the reference algorithm on the host CPU cores
+
+Workload at N = 1: BASELINE configs[1] — MoELayer(d_model 1024, ffn_dim 4096, 8 experts, top-2, swiglu, one shared
+expert), x [8, 2048, 1024] bf16, seed 1, all weights N(0, 0.02). At N > 1 the same layer with its experts sharded
+over the N ranks (expert parallelism) and 16,384 tokens per rank (weak scaling).
+
+One step = forward, loss = <out, grad_out>, backward to every parameter and to the input.
+Prints ONE JSON line on rank 0 (see the keys below).
+"""
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+METRIC = "moe_layer_tokens_per_s_fwd_bwd"
+UNIT = "tokens/s"
+CFG = dict(d_model=1024, ffn_dim=4096, num_experts=8, top_k=2, shared_ffn_dim=4096, batch=8, seq=2048, seed=1)
+SMI_QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+
+def algorithmic_flops(tokens, ep):
+    """FLOPs of one step per GPU, unpadded (T = tokens * k routed rows)."""
+    D, H, k, E = CFG["d_model"], CFG["ffn_dim"] // 2, CFG["top_k"], CFG["num_experts"]
+    Hs = CFG["shared_ffn_dim"] // 2
+    T = tokens * k
+    routed_fwd = 6.0 * T * D * H
+    routed_bwd = 12.0 * T * D * H if ep == 1 else 8.0 * T * D * H  # EP backward has no expert input gradient
+    shared = 18.0 * tokens * D * Hs
+    return dict(gemm=routed_fwd + routed_bwd + shared, gate=6.0 * tokens * D * E)
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return dict(tflops=p["bf16_tflops_sustained"], tflops_burst=p["bf16_tflops"], hbm_gbs=p["hbm_gbs"],
+                    source="measured")
+    return dict(tflops=1400.0, tflops_burst=1590.0, hbm_gbs=6650.0, source="fallback")
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples every 200 ms while the timed region runs."""
+
+    def __init__(self, gpu_index):
+        self.proc = None
+        self.gpu_index = gpu_index
+        self.path = f"/tmp/ffm_bench_clocks_{os.getpid()}.csv"
+
+    def start(self):
+        try:
+            self.out = open(self.path, "w")
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={SMI_QUERY}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.gpu_index)], stdout=self.out,
+                                         stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.out.close()
+        sm, smax, reasons = [], [], set()
+        for line in open(self.path):
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                smax.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        try:
+            os.remove(self.path)
+        except OSError:
+            pass
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def build_layer(device, ep_group):
+    import flashfusedmoe_b200 as ffm
+    torch.manual_seed(CFG["seed"])
+    layer = ffm.MoELayer(CFG["d_model"], CFG["ffn_dim"], CFG["num_experts"], CFG["top_k"], num_shared_experts=1,
+                         shared_ffn_dim=CFG["shared_ffn_dim"])
+    with torch.no_grad():
+        for p in layer.parameters():
+            p.normal_(0.0, 0.02)   # same generator order on every rank: weights are replicated before sharding
+    layer = layer.to(device).bfloat16()
+    if ep_group is not None:
+        layer.shard_experts(ep_group)
+    return layer
+
+
+def make_step(layer, x, go):
+    def step():
+        for p in layer.parameters():
+            p.grad = None
+        x.grad = None
+        out, _ = layer(x)
+        out.backward(go)
+    return step
+
+
+def oracle_sample_tokens_per_s(sample_tokens, threads, repeats=1):
+    """The oracle's forward + backward (the reference algorithm restated on CPU, fp32 accumulation, bf16 rounding
+    points) on a token sub-sample of the same workload; returns (tokens/s, seconds per pass)."""
+    from oracle import moe_oracle as orc
+    torch.set_num_threads(threads)
+    torch.manual_seed(CFG["seed"])
+    D, F, E, k = CFG["d_model"], CFG["ffn_dim"], CFG["num_experts"], CFG["top_k"]
+    Hs = CFG["shared_ffn_dim"] // 2
+    g = (torch.randn(E, D) * 0.02).bfloat16()
+    wu = (torch.randn(E, F, D) * 0.02).bfloat16()
+    wd = (torch.randn(E, D, F // 2) * 0.02).bfloat16()
+    sg, su = (torch.randn(Hs, D) * 0.02).bfloat16(), (torch.randn(Hs, D) * 0.02).bfloat16()
+    sd = (torch.randn(D, Hs) * 0.02).bfloat16()
+    h = torch.randn(sample_tokens, D).bfloat16()
+    go = torch.randn(sample_tokens, D).bfloat16()
+    best = None
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        fw = orc.fused_moe_forward(h, g, wu, wd, k, "swiglu", "softmax", dtype=torch.bfloat16)
+        orc.fused_moe_backward(fw, go)
+        # shared expert forward + backward (same GLU FFN arithmetic, one group)
+        pre = torch.cat([orc.mm(h, sg.T, torch.bfloat16), orc.mm(h, su.T, torch.bfloat16)], -1)
+        act = orc.glu_forward(pre, "swiglu", torch.bfloat16)
+        orc.mm(act, sd.T, torch.bfloat16)
+        d_act = orc.mm(go, sd, torch.bfloat16)
+        gU = orc.glu_backward(d_act, pre, "swiglu", torch.bfloat16)
+        orc.mm(gU, torch.cat([sg, su], 0), torch.bfloat16)
+        orc.mm(gU.T, h, torch.bfloat16)
+        orc.mm(go.T, act, torch.bfloat16)
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    return sample_tokens / best, best
+
+
+def run_reference_arm(args, rank):
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    sample = 2048
+    # warm-up passes and timed steps, each step one bounded sample of the workload
+    for _ in range(max(args.warmup, 1)):
+        oracle_sample_tokens_per_s(256, threads)
+    vals = [oracle_sample_tokens_per_s(sample, threads)[0] for _ in range(args.steps)]
+    v = statistics.median(vals)
+    line = {"impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": 1e3 * sample / v, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "BASELINE configs[1]: MoELayer d_model=1024 ffn_dim=4096 E=8 top_k=2 swiglu + 1 shared expert, "
+                                   "fwd+bwd; reference algorithm on host CPU cores"},
+            "cpu_baseline": {"value": v, "unit": UNIT, "cores": threads, "kind": "port",
+                             "sample": f"{sample} of 16384 tokens per step, same layer shape; the Python/Triton reference "
+                                       "cannot travel to the GPU box, its CPU restatement (oracle/) is timed"},
+            "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference_arm(args, rank)
+        return
+
+    import torch.distributed as dist
+    from flashfusedmoe_b200 import ops
+
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    group = None
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=device)
+        group = dist.group.WORLD
+    W = max(args.warmup, 3)
+    K = args.steps
+
+    layer = build_layer(device, group)
+    tokens = CFG["batch"] * CFG["seq"]
+    torch.manual_seed(CFG["seed"] + 1000 + rank)  # different tokens on every rank
+    x_host = torch.randn(CFG["batch"], CFG["seq"], CFG["d_model"]).bfloat16().pin_memory()
+    go = torch.randn(CFG["batch"], CFG["seq"], CFG["d_model"], device=device).bfloat16()
+    x = x_host.to(device).requires_grad_()
+    step = make_step(layer, x, go)
+
+    def fence():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    # ---- device-resident timing --------------------------------------------------------------
+    for _ in range(W):
+        step()
+    ops.check_status()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    timer = ops.KernelTimer()
+    fence()
+    if sampler:
+        sampler.start()
+    launches0 = ops.launch_count
+    ops.set_timer(timer)
+    t0 = torch.cuda.Event(enable_timing=True)
+    t1 = torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(K):
+        step()
+    t1.record()
+    fence()
+    ops.set_timer(None)
+    launches = ops.launch_count - launches0
+    ms = t0.elapsed_time(t1)
+    clocks = sampler.stop() if sampler else None
+    ops.check_status()
+
+    # ---- end to end: pinned host input in, loss scalar out, every step ------------------------
+    def e2e_step():
+        for p in layer.parameters():
+            p.grad = None
+        xd = x_host.to(device, non_blocking=True).requires_grad_()
+        out, _ = layer(xd)
+        loss = (out.float() * go.float()).sum()
+        loss.backward()
+        return float(loss.item())
+
+    for _ in range(3):
+        e2e_step()
+    fence()
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(K):
+        e2e_step()
+    e1.record()
+    fence()
+    e2e_ms = e0.elapsed_time(e1)
+
+    t = torch.tensor([ms, e2e_ms], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, e2e_ms = float(t[0]), float(t[1])
+
+    if rank == 0:
+        peaks = measured_peaks()
+        fl = algorithmic_flops(tokens, world)
+        kt = timer.totals_ms()
+        gemm_names = ("gemm_up_glu", "gemm", "gemm_wgrad")
+        gemm_ms = sum(kt[n][1] for n in gemm_names if n in kt)
+        gemm_launches = sum(kt[n][0] for n in gemm_names if n in kt)
+        achieved = fl["gemm"] * K / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else None
+        value = tokens * world * K / (ms * 1e-3)
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "BASELINE configs[1]: MoELayer d_model=1024 ffn_dim=4096 E=8 top_k=2 swiglu + 1 shared "
+                                   "expert (ffn_dim 4096), x [8,2048,1024] bf16 seed 1, weights N(0,0.02), forward+backward",
+                       "tokens_per_gpu": tokens, "expert_parallel": world,
+                       "l2": "no explicit flush: one step streams > 1 GB of activations and weights, 8x the 126 MB L2"},
+            "e2e": {"value": tokens * world * K / (e2e_ms * 1e-3), "unit": UNIT,
+                    "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": 4},
+            "gpu_launches": launches,
+            "clocks": clocks,
+            "roofline": {
+                "bound": "tensor", "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
+                "frac": (achieved / peaks["tflops"]) if achieved else None, "traffic": None,
+                "kernel": "ffm_gemm_kernel (tcgen05 grouped GEMM, all instantiations)",
+                "peak_source": f"{peaks['source']} sustained cuBLAS bf16 (burst {peaks['tflops_burst']})",
+                "frac_of_burst": (achieved / peaks["tflops_burst"]) if achieved else None,
+                "frac_of_nominal_2250": (achieved / 2250.0) if achieved else None,
+                "gemm_launches": gemm_launches, "gemm_ms_per_step": gemm_ms / K,
+                "algorithmic_tflop_per_step": fl["gemm"] / 1e12,
+                "other_kernels_ms_per_step": {n: v[1] / K for n, v in kt.items() if n not in gemm_names},
+            },
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            threads = os.cpu_count() or 1
+            v, secs = oracle_sample_tokens_per_s(2048, threads, repeats=2)
+            line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": threads, "kind": "port",
+                                    "sample": f"2048 of 16384 tokens, same layer shape, oracle fwd+bwd, {secs:.2f} s per pass"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -14,6 +14,50 @@ from . import _lib
 _status = {}
 _workspaces = {}
 
+# Instrumentation used by bench.py: a launch counter (kernels of this library enqueued so far) and an
+# optional per-kernel CUDA-event timer on the launching stream.
+launch_count = 0
+_timer = None
+
+
+class KernelTimer:
+    """Records a CUDA-event pair around selected kernel launches while installed with set_timer()."""
+
+    def __init__(self):
+        self.events = {}
+
+    def totals_ms(self):
+        """name -> (launches, total milliseconds); call after torch.cuda.synchronize()."""
+        return {n: (len(ev), sum(a.elapsed_time(b) for a, b in ev)) for n, ev in self.events.items()}
+
+
+def set_timer(timer):
+    global _timer
+    _timer = timer
+
+
+class _Launch:
+    """Counts `kernels` launches under `name`; with a timer installed also brackets them with events."""
+
+    def __init__(self, name, kernels=1):
+        self.name = name
+        self.kernels = kernels
+
+    def __enter__(self):
+        global launch_count
+        launch_count += self.kernels
+        if _timer is not None:
+            self.start = torch.cuda.Event(enable_timing=True)
+            self.start.record()
+        return self
+
+    def __exit__(self, *exc):
+        if _timer is not None:
+            end = torch.cuda.Event(enable_timing=True)
+            end.record()
+            _timer.events.setdefault(self.name, []).append((self.start, end))
+        return False
+
 
 def _ptr(t):
     return 0 if t is None else t.data_ptr()
@@ -108,11 +152,12 @@ def route_forward(hidden, gate_w, top_k, gating="softmax", expert_bias=None, wei
         rows_cap=rows_cap, top_k=top_k, num_experts=E)
     ws_bytes = int(lib.ffm_route_workspace_bytes(N, E, top_k))
     ws = _workspace(dev, ws_bytes, "route")
-    rc = lib.ffm_route_forward(_ptr(hidden), _ptr(gate_w), _ptr(expert_bias), N, D, E, top_k,
-                               _lib.GATING[gating], float(weight_scale), _ptr(r.logits), _ptr(r.topk_w),
-                               _ptr(r.topk_idx), _ptr(r.lse), _ptr(r.counts), _ptr(r.tile_start), _ptr(r.pos),
-                               _ptr(r.src), rows_cap, _ptr(r.stats), _ptr(ws), ws.numel(),
-                               _ptr(status_tensor(dev)), _stream())
+    with _Launch("route_forward", 3):
+        rc = lib.ffm_route_forward(_ptr(hidden), _ptr(gate_w), _ptr(expert_bias), N, D, E, top_k,
+                                   _lib.GATING[gating], float(weight_scale), _ptr(r.logits), _ptr(r.topk_w),
+                                   _ptr(r.topk_idx), _ptr(r.lse), _ptr(r.counts), _ptr(r.tile_start), _ptr(r.pos),
+                                   _ptr(r.src), rows_cap, _ptr(r.stats), _ptr(ws), ws.numel(),
+                                   _ptr(status_tensor(dev)), _stream())
     _lib.check(rc, "ffm_route_forward")
     return r
 
@@ -130,8 +175,9 @@ def group_rows(expert_ids, num_experts):
     src = torch.empty(max(rows_cap, 1), dtype=torch.int32, device=dev)
     ws_bytes = int(lib.ffm_route_workspace_bytes(max(T, 1), num_experts, 1))
     ws = _workspace(dev, ws_bytes, "group")
-    rc = lib.ffm_group_rows(_ptr(expert_ids), T, num_experts, _ptr(counts), _ptr(tile_start), _ptr(pos), _ptr(src),
-                            rows_cap, _ptr(ws), ws.numel(), _ptr(status_tensor(dev)), _stream())
+    with _Launch("group_rows", 3):
+        rc = lib.ffm_group_rows(_ptr(expert_ids), T, num_experts, _ptr(counts), _ptr(tile_start), _ptr(pos), _ptr(src),
+                                rows_cap, _ptr(ws), ws.numel(), _ptr(status_tensor(dev)), _stream())
     _lib.check(rc, "ffm_group_rows")
     return counts, tile_start, pos[:T], src, rows_cap
 
@@ -142,7 +188,8 @@ def permute_rows(x, src, rows_cap, top_k):
     _req(src, torch.int32, "src")
     D = x.shape[1]
     out = torch.empty(rows_cap, D, dtype=torch.bfloat16, device=x.device)
-    _lib.check(lib.ffm_permute_rows(_ptr(x), _ptr(src), rows_cap, top_k, D, _ptr(out), _stream()),
+    with _Launch("permute_rows", 1):
+        _lib.check(lib.ffm_permute_rows(_ptr(x), _ptr(src), rows_cap, top_k, D, _ptr(out), _stream()),
                "ffm_permute_rows")
     return out
 
@@ -154,9 +201,10 @@ def grouped_gemm_glu(A, w_gate, w_up, group_rows_, groups, tile_start, K, H, act
     rows = A.shape[0]
     act = torch.empty(rows, H, dtype=torch.bfloat16, device=A.device)
     pre = torch.empty(rows, 2 * H, dtype=torch.bfloat16, device=A.device) if want_preact else None
-    rc = lib.ffm_grouped_gemm_glu(_ptr(A), _ptr(w_gate), _ptr(w_up), group_rows_, groups, _ptr(tile_start), rows, K,
-                                  H, _lib.ACTIVATION[activation], _ptr(act), _ptr(pre),
-                                  _ptr(status_tensor(A.device)), _stream())
+    with _Launch("gemm_up_glu", 1):
+        rc = lib.ffm_grouped_gemm_glu(_ptr(A), _ptr(w_gate), _ptr(w_up), group_rows_, groups, _ptr(tile_start), rows, K,
+                                      H, _lib.ACTIVATION[activation], _ptr(act), _ptr(pre),
+                                      _ptr(status_tensor(A.device)), _stream())
     _lib.check(rc, "ffm_grouped_gemm_glu")
     return act, pre
 
@@ -167,8 +215,9 @@ def grouped_gemm(A, B, b_major, groups, tile_start, K, n_out, scale=1.0):
     _req(B, torch.bfloat16, "B")
     rows = A.shape[0]
     out = torch.empty(rows, n_out, dtype=torch.bfloat16, device=A.device)
-    rc = lib.ffm_grouped_gemm(_ptr(A), _ptr(B), b_major, groups, _ptr(tile_start), rows, K, n_out, float(scale),
-                              _ptr(out), _ptr(status_tensor(A.device)), _stream())
+    with _Launch("gemm", 1):
+        rc = lib.ffm_grouped_gemm(_ptr(A), _ptr(B), b_major, groups, _ptr(tile_start), rows, K, n_out, float(scale),
+                                  _ptr(out), _ptr(status_tensor(A.device)), _stream())
     _lib.check(rc, "ffm_grouped_gemm")
     return out
 
@@ -181,8 +230,9 @@ def grouped_gemm_wgrad(A, B, groups, tile_start, scale=1.0):
     rows_cap, M = A.shape
     n_out = B.shape[1]
     out = torch.empty(groups, M, n_out, dtype=torch.bfloat16, device=A.device)
-    rc = lib.ffm_grouped_gemm_wgrad(_ptr(A), _ptr(B), groups, _ptr(tile_start), rows_cap, M, n_out, float(scale),
-                                    _ptr(out), _ptr(status_tensor(A.device)), _stream())
+    with _Launch("gemm_wgrad", 1):
+        rc = lib.ffm_grouped_gemm_wgrad(_ptr(A), _ptr(B), groups, _ptr(tile_start), rows_cap, M, n_out, float(scale),
+                                        _ptr(out), _ptr(status_tensor(A.device)), _stream())
     _lib.check(rc, "ffm_grouped_gemm_wgrad")
     return out
 
@@ -193,7 +243,8 @@ def combine_forward(Y, pos, w, N, top_k, addend=None):
     _req(pos, torch.int32, "pos")
     D = Y.shape[1]
     out = torch.empty(N, D, dtype=torch.bfloat16, device=Y.device)
-    rc = lib.ffm_combine_forward(_ptr(Y), _ptr(pos), _ptr(w), _ptr(addend), N, top_k, D, _ptr(out), _stream())
+    with _Launch("combine_forward", 1):
+        rc = lib.ffm_combine_forward(_ptr(Y), _ptr(pos), _ptr(w), _ptr(addend), N, top_k, D, _ptr(out), _stream())
     _lib.check(rc, "ffm_combine_forward")
     return out
 
@@ -204,8 +255,9 @@ def combine_backward(go, Y, w, src, rows_cap, top_k, want_gw=True):
     D = go.shape[1]
     gYw = torch.empty(rows_cap, D, dtype=torch.bfloat16, device=go.device)
     gw = torch.zeros(go.shape[0] * top_k, dtype=torch.float32, device=go.device) if want_gw else None
-    rc = lib.ffm_combine_backward(_ptr(go), _ptr(Y if want_gw else None), _ptr(w), _ptr(src), rows_cap, top_k, D,
-                                  _ptr(gYw), _ptr(gw), _stream())
+    with _Launch("combine_backward", 1):
+        rc = lib.ffm_combine_backward(_ptr(go), _ptr(Y if want_gw else None), _ptr(w), _ptr(src), rows_cap, top_k, D,
+                                      _ptr(gYw), _ptr(gw), _stream())
     _lib.check(rc, "ffm_combine_backward")
     return gYw, gw
 
@@ -216,8 +268,9 @@ def glu_backward(dAct, preact, tile_start, groups, activation):
     _req(preact, torch.bfloat16, "preact")
     rows, H = dAct.shape
     gU = torch.empty(rows, 2 * H, dtype=torch.bfloat16, device=dAct.device)
-    rc = lib.ffm_glu_backward(_ptr(dAct), _ptr(preact), _ptr(tile_start), groups, rows, H,
-                              _lib.ACTIVATION[activation], _ptr(gU), _stream())
+    with _Launch("glu_backward", 1):
+        rc = lib.ffm_glu_backward(_ptr(dAct), _ptr(preact), _ptr(tile_start), groups, rows, H,
+                                  _lib.ACTIVATION[activation], _ptr(gU), _stream())
     _lib.check(rc, "ffm_glu_backward")
     return gU
 
@@ -235,9 +288,10 @@ def route_backward(gw, routing, gaux, gz, hidden, gate_w, gating, dH=None):
     dGate = torch.empty(E, D, dtype=torch.bfloat16, device=dev)
     ws_bytes = int(lib.ffm_route_backward_workspace_bytes(N, D, E))
     ws = _workspace(dev, ws_bytes, "route_bwd")
-    rc = lib.ffm_route_backward(_ptr(gw), _ptr(routing.topk_w), _ptr(routing.topk_idx), _ptr(routing.logits),
-                                _ptr(routing.lse), _ptr(gaux), _ptr(gz), _ptr(hidden), _ptr(gate_w), N, D, E,
-                                routing.top_k, _lib.GATING[gating], 1 if accumulate else 0, _ptr(dH), _ptr(dGate),
-                                _ptr(ws), ws.numel(), _stream())
+    with _Launch("route_backward", 3):
+        rc = lib.ffm_route_backward(_ptr(gw), _ptr(routing.topk_w), _ptr(routing.topk_idx), _ptr(routing.logits),
+                                    _ptr(routing.lse), _ptr(gaux), _ptr(gz), _ptr(hidden), _ptr(gate_w), N, D, E,
+                                    routing.top_k, _lib.GATING[gating], 1 if accumulate else 0, _ptr(dH), _ptr(dGate),
+                                    _ptr(ws), ws.numel(), _stream())
     _lib.check(rc, "ffm_route_backward")
     return dH, dGate
