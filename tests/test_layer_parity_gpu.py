@@ -92,9 +92,12 @@ def test_routing_bit_exact_vs_oracle_on_identical_logits():
         assert torch.equal(r.topk_idx.cpu().long(), i_o)
         assert torch.allclose(r.topk_w.cpu(), w_o, atol=2e-6, rtol=1e-4)
         ref_lg = orc.gate_logits(h, g, torch.bfloat16)
+        # one bf16 unit in the last place, plus the fp32 accumulation-order error of a D-term dot product
+        # (it dominates for logits that cancel to nearly zero)
         diff = (lg.float() - ref_lg.float()).abs()
         ulp = torch.maximum(lg.float().abs(), ref_lg.float().abs()) * 2.0 ** -7
-        assert (diff <= ulp).all()
+        acc_err = 2e-6 * (h.float().abs() @ g.float().abs().T)
+        assert (diff <= ulp + acc_err).all()
         same_rows = (lg == ref_lg).all(1)
         _, i_ref = orc.route(ref_lg, "softmax", k)
         assert torch.equal(i_o[same_rows], i_ref[same_rows])
