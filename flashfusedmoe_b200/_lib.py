@@ -28,6 +28,7 @@ SIGNATURES = {
     "ffm_error_string": (ctypes.c_char_p, [c_int]),
     "ffm_rows_capacity": (c_int64, [c_int64, c_int]),
     "ffm_set_wait_cycles": (ctypes.c_longlong, [ctypes.c_longlong]),
+    "ffm_set_gemm_cta_pair": (c_int, [c_int]),
     "ffm_route_workspace_bytes": (c_size_t, [c_int64, c_int, c_int]),
     "ffm_route_forward": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_float,
                                   c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,

@@ -1,14 +1,24 @@
 // Grouped GEMM for sm_100a: TMA-fed shared-memory ring, tcgen05.mma with fp32 accumulators in TMEM,
-// persistent CTAs, warp-specialised roles.
+// persistent CTAs, warp-specialised roles, TMA-store epilogue.
 //
-//   warp 0      TMA producer   (one lane issues cp.async.bulk.tensor loads into a 4-stage ring)
-//   warp 1      MMA issuer     (one lane issues tcgen05.mma; owns the TMEM allocation)
-//   warps 2..5  epilogue       (tcgen05.ld of the 128 x 256 fp32 accumulator, math, bf16 stores)
+//   warp 0      TMA producer   (one lane issues cp.async.bulk.tensor loads into the stage ring)
+//   warp 1      MMA issuer     (one lane issues tcgen05.mma; the warp owns the TMEM allocation)
+//   warps 2..5  epilogue       (tcgen05.ld of the fp32 accumulator one chunk ahead, math, bf16 rows staged in
+//                               swizzled shared memory and written out with cp.async.bulk.tensor stores)
 //
-// The accumulator is double-buffered in TMEM (2 x 256 columns), so the epilogue of tile i overlaps the
-// main loop of tile i + 1. Every mbarrier wait is bounded: when a wait runs out the role records a code in
-// the caller's status word, raises a CTA-wide abort flag and all roles fall through to the common exit,
-// where TMEM is released.
+// Two tile shapes from one template:
+//   CTA2 = 0   one CTA per 128 x 256 tile, tcgen05.mma.cta_group::1, 4 stages of (A 16 KiB + B 32 KiB)
+//   CTA2 = 1   a cluster of two CTAs per 256 x 256 tile, tcgen05.mma.cta_group::2 issued by the even CTA.
+//              Each CTA stages its own 128 rows of A and its own 128-column half of B (6 stages of 32 KiB), so
+//              every byte of B is read from shared memory once for 256 rows of output instead of once for 128.
+//              Both CTAs' loads complete on the even CTA's "full" barrier; MMA completion is committed to the
+//              "empty" and "accumulator full" barriers of both CTAs; the odd CTA's epilogue hands its
+//              accumulator back with a remote arrive. No load is broadcast to more than one CTA.
+//
+// The accumulator is double-buffered in TMEM (2 x 256 columns), so the epilogue of tile i overlaps the main
+// loop of tile i + 1. Every mbarrier wait is bounded: when a wait runs out the role records a code in the
+// caller's status word, raises a CTA-wide abort flag and all roles fall through to the common exit, where the
+// cluster (if any) is joined and TMEM is released.
 //
 // Operand tiles in shared memory use the 128-byte swizzle that both TMA and the MMA descriptors understand:
 //   K-major operand  (rows = M or N index, 64 contiguous K elements per row): box {64, 128 rows}
@@ -16,26 +26,41 @@
 //   MN-major operand (rows = K index, 64 contiguous M/N elements per row):    box {64, 64 rows} per 64 columns
 //       descriptor: LBO = 8192 B between 64-column blocks, SBO = 1024 B between 8-row K groups;
 //       K step of 16 rows = +2048 B on the start address
+// Output staging: per epilogue warp three 32-row x 64-byte buffers with the 64-byte swizzle
+// (16-byte chunk index ^= (row >> 1) & 3), stored with box {32 columns, 32 rows, 1}; stores clip at the
+// tensor extents, so ragged row and column edges need no masking.
+#include <stdlib.h>
+
 #include "ffm_common.cuh"
 
 namespace ffm {
 
 namespace {
 
-constexpr int BM = 128;
-constexpr int BN = 256;
+constexpr int BM = 128;  // rows per CTA
+constexpr int BN = 256;  // columns per tile
 constexpr int BK = 64;
 constexpr int UMMA_K = 16;
-constexpr int STAGES = 4;
-constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KiB
-constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KiB
-constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
 constexpr int NUM_ACC = 2;
 constexpr int TMEM_COLS = 512;
 constexpr int GEMM_THREADS = 192;
+constexpr int EPI_WARPS = 4;
 constexpr int MAX_GROUPS = 256;
+constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KiB
+constexpr int STG_ARRAY_BYTES = 32 * 64;    // one staged block: 32 rows x 32 bf16
+constexpr int STG_WARP_BYTES = 3 * STG_ARRAY_BYTES;
+constexpr int STG_BYTES = EPI_WARPS * STG_WARP_BYTES;  // 24 KiB
 constexpr int SMEM_CTRL_BYTES = 2048;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + SMEM_CTRL_BYTES + 1024;  // + slack for 1 KiB alignment
+constexpr int MAX_STAGES = 6;
+
+template <int CTA2>
+struct Shape {
+  static constexpr int STAGES = CTA2 ? 6 : 4;
+  static constexpr int B_STAGE_BYTES = (CTA2 ? 128 : 256) * BK * 2;
+  static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+  static constexpr int RING_BYTES = STAGES * STAGE_BYTES;  // 192 KiB either way
+  static constexpr int SMEM_BYTES = RING_BYTES + STG_BYTES + SMEM_CTRL_BYTES + 1024;  // + 1 KiB alignment slack
+};
 
 enum { EPI_PLAIN = 0, EPI_GLU = 1 };
 
@@ -43,28 +68,23 @@ struct GemmParams {
   const int32_t* tile_start;  // [groups + 1] cumulative 128-row tiles, or null (dense)
   int groups;
   int dense_m_tiles;
-  long long m_rows;        // store bound on output rows (grouped-M / dense)
   int n_cols;              // output columns per group (GLU: H)
   int k_blocks;            // K / 64 (grouped-M / dense)
   long long b_group_rows;  // rows of the B tensor map per group
   int b1_row_offset;       // row offset of the second 128-row half of a K-major B tile
-  bf16* C;
-  long long ldc;
-  long long c_group_stride;  // grouped-K: elements between consecutive groups of C
-  bf16* C2;                  // GLU: pre-activations [rows, 2H] or null
-  long long ldc2;
+  int has_c2;              // GLU: also store the pre-activations
   int glu_h;
   float scale;
   int act;
-  int m_tiles_per_group;  // grouped-K
+  int m_tiles_per_group;  // grouped-K: 128-row tiles of M per group
   int n_tiles;            // number of BN (GLU: 128-column) blocks over n_cols
   int32_t* status;
   long long wait_cycles;
 };
 
 struct Ctrl {
-  unsigned long long full_bar[STAGES];
-  unsigned long long empty_bar[STAGES];
+  unsigned long long full_bar[MAX_STAGES];
+  unsigned long long empty_bar[MAX_STAGES];
   unsigned long long acc_full_bar[NUM_ACC];
   unsigned long long acc_empty_bar[NUM_ACC];
   uint32_t tmem_base;
@@ -75,75 +95,170 @@ static_assert(sizeof(Ctrl) <= SMEM_CTRL_BYTES, "control block too large");
 
 struct TileCoord {
   int group;
-  int m_tile;    // grouped-M: global 128-row tile; grouped-K: 128-row tile of M within the group
+  int m_tile;    // 128-row tile of this CTA: global (grouped-M / dense) or inside the group's M (grouped-K)
   int n_block;   // BN-column block (GLU: 128-column block of H)
   int k_row0;    // grouped-K: first K row; else 0
   int k_blocks;  // 64-deep K blocks to accumulate
 };
 
-// Walks this CTA's tiles in launch order. Grouped-M order is expert-major, then N block, then M tile
-// (M fastest), so CTAs running side by side share one weight tile through L2.
-template <int GROUPK>
+// Walks the tiles of this CTA (or CTA pair) in launch order. The unit is one MMA tile: 128 rows, or with CTA2
+// a pair of consecutive 128-row tiles (segments are aligned to 256 rows, so a pair never straddles experts).
+// Grouped-M order is expert-major, then N block, then M (M fastest), so CTAs running side by side share one
+// weight tile through L2.
+template <int GROUPK, int CTA2>
 struct TileWalker {
   const int* ts;
-  int groups, n_tiles, m_tiles_per_group, k_blocks;
-  long long total;
-  long long cur;
-  int g;  // cursor for grouped-M
+  int groups, n_tiles, m_units_per_group, k_blocks, rank;
+  long long total, cur, step;
+  int g;
 
-  __device__ TileWalker(const GemmParams& p, const int* ts_smem) {
+  __device__ static int units(int tiles) { return CTA2 ? (tiles + 1) / 2 : tiles; }
+
+  __device__ TileWalker(const GemmParams& p, const int* ts_smem, int cta_rank) {
     ts = ts_smem;
     groups = p.groups;
     n_tiles = p.n_tiles;
-    m_tiles_per_group = p.m_tiles_per_group;
     k_blocks = p.k_blocks;
+    rank = cta_rank;
+    m_units_per_group = units(p.m_tiles_per_group);
     if (GROUPK) {
-      total = static_cast<long long>(groups) * m_tiles_per_group * n_tiles;
+      total = static_cast<long long>(groups) * m_units_per_group * n_tiles;
     } else {
-      total = static_cast<long long>(ts[groups]) * n_tiles;
+      total = static_cast<long long>(units(ts[groups])) * n_tiles;
     }
-    cur = blockIdx.x;
+    cur = CTA2 ? (blockIdx.x >> 1) : blockIdx.x;
+    step = CTA2 ? (gridDim.x >> 1) : gridDim.x;
     g = 0;
   }
 
   __device__ bool next(TileCoord& t) {
     if (cur >= total) return false;
+    int unit;
     if (GROUPK) {
-      const int per_group = m_tiles_per_group * n_tiles;
+      const int per_group = m_units_per_group * n_tiles;
       t.group = static_cast<int>(cur / per_group);
       const int r = static_cast<int>(cur % per_group);
-      t.m_tile = r % m_tiles_per_group;
-      t.n_block = r / m_tiles_per_group;
+      unit = r % m_units_per_group;
+      t.n_block = r / m_units_per_group;
       t.k_row0 = ts[t.group] * BM;
       t.k_blocks = (ts[t.group + 1] - ts[t.group]) * (BM / BK);
     } else {
-      while (g < groups - 1 && cur >= static_cast<long long>(ts[g + 1]) * n_tiles) ++g;
-      const int cnt = ts[g + 1] - ts[g];
-      const int r = static_cast<int>(cur - static_cast<long long>(ts[g]) * n_tiles);
+      while (g < groups - 1 && cur >= static_cast<long long>(units(ts[g + 1])) * n_tiles) ++g;
+      const int u0 = units(ts[g]);
+      const int cnt = units(ts[g + 1]) - u0;
+      const int r = static_cast<int>(cur - static_cast<long long>(u0) * n_tiles);
       t.group = g;
       t.n_block = r / cnt;
-      t.m_tile = ts[g] + r % cnt;
+      unit = u0 + r % cnt;
       t.k_row0 = 0;
       t.k_blocks = k_blocks;
     }
-    cur += gridDim.x;
+    t.m_tile = CTA2 ? (unit * 2 + rank) : unit;
+    cur += step;
     return true;
   }
 };
 
-template <int A_MN, int B_MN, int EPI, int GROUPK>
+// ---- PTX used only by this kernel --------------------------------------------------------------
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+
+// shared::cluster address of the same shared-memory offset in CTA `rank` of this cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+
+// 2-D TMA load issued by either CTA of a pair into its own shared memory; the byte count completes on the
+// mbarrier at `bar`, a shared::cluster address that may belong to the other CTA of the pair.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const void* map, uint32_t bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], "
+      "[%2];" ::"r"(dst),
+      "l"(map), "r"(bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+
+__device__ __forceinline__ void tma_store_3d(const void* map, uint32_t src, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(map), "r"(src),
+               "r"(c0), "r"(c1), "r"(c2)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_alloc2(uint32_t slot_smem_addr, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_smem_addr), "r"(cols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish2() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc2(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                               uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// Arrive (once the pair's MMAs issued so far have completed) on one mbarrier given by shared::cluster address.
+__device__ __forceinline__ void umma_commit_pair(uint32_t cluster_bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar)
+               : "memory");
+}
+
+// 16-byte chunk q of row r inside a 32-row x 64-byte block with the 64-byte TMA swizzle
+__device__ __forceinline__ uint32_t stg_offset(int r, int q) { return r * 64 + ((q ^ ((r >> 1) & 3)) << 4); }
+
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
+template <int A_MN, int B_MN, int EPI, int GROUPK, int CTA2>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 ffm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB0,
-                const __grid_constant__ CUtensorMap tmB1, const GemmParams p) {
+                const __grid_constant__ CUtensorMap tmB1, const __grid_constant__ CUtensorMap tmC,
+                const __grid_constant__ CUtensorMap tmC2, const GemmParams p) {
+  using S = Shape<CTA2>;
+  constexpr int STAGES = S::STAGES;
+  constexpr int STAGE_BYTES = S::STAGE_BYTES;
+
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
   uint8_t* smem = smem_raw + pad;
   const uint32_t smem_base = raw_addr + pad;
-  Ctrl* ctrl = reinterpret_cast<Ctrl*>(smem + STAGES * STAGE_BYTES);
+  const uint32_t stg_base = smem_base + S::RING_BYTES;
+  Ctrl* ctrl = reinterpret_cast<Ctrl*>(smem + S::RING_BYTES + STG_BYTES);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  const uint32_t rank = CTA2 ? cluster_ctarank() : 0u;
+  const bool leader = rank == 0;
 
   // ---- set-up ------------------------------------------------------------------------------
   if (threadIdx.x == 0) {
@@ -153,13 +268,15 @@ ffm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     }
     for (int a = 0; a < NUM_ACC; ++a) {
       mbar_init(smem_u32(&ctrl->acc_full_bar[a]), 1);
-      mbar_init(smem_u32(&ctrl->acc_empty_bar[a]), 4);  // one arrival per epilogue warp
+      mbar_init(smem_u32(&ctrl->acc_empty_bar[a]), EPI_WARPS * (CTA2 ? 2 : 1));  // one arrival per epilogue warp
     }
     ctrl->abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB0);
     tma_prefetch_desc(&tmB1);
+    tma_prefetch_desc(&tmC);
+    tma_prefetch_desc(&tmC2);
   }
   if (p.tile_start != nullptr) {
     for (int i = threadIdx.x; i <= p.groups; i += GEMM_THREADS) ctrl->tile_start[i] = p.tile_start[i];
@@ -168,11 +285,17 @@ ffm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     ctrl->tile_start[1] = p.dense_m_tiles;
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(&ctrl->tmem_base), TMEM_COLS);
-    tmem_relinquish();
+    if (CTA2) {
+      tmem_alloc2(smem_u32(&ctrl->tmem_base), TMEM_COLS);
+      tmem_relinquish2();
+    } else {
+      tmem_alloc(smem_u32(&ctrl->tmem_base), TMEM_COLS);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if (CTA2) cluster_sync_all();  // the peer's barriers exist before anything arrives on them
   tc_fence_after();
 
   const uint32_t tmem_base = ctrl->tmem_base;
@@ -182,7 +305,7 @@ ffm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   if (warp == 0) {
     // ================= TMA producer =================
     if (lane == 0) {
-      TileWalker<GROUPK> walker(p, ctrl->tile_start);
+      TileWalker<GROUPK, CTA2> walker(p, ctrl->tile_start, rank);
       TileCoord t;
       int stage = 0;
       uint32_t phase = 0;
@@ -193,29 +316,52 @@ ffm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           ok = mbar_wait_bounded(smem_u32(&ctrl->empty_bar[stage]), phase ^ 1u, abort_flag, p.status,
                                  FFM_STATUS_WAIT_PRODUCER, p.wait_cycles);
           if (!ok) break;
-          const uint32_t full = smem_u32(&ctrl->full_bar[stage]);
+          const uint32_t full_local = smem_u32(&ctrl->full_bar[stage]);
+          const uint32_t full = CTA2 ? map_to_cta(full_local, 0) : full_local;  // the even CTA's barrier
           const uint32_t a_dst = smem_base + stage * STAGE_BYTES;
           const uint32_t b_dst = a_dst + A_STAGE_BYTES;
-          mbar_expect_tx(full, STAGE_BYTES);
+          if (leader) mbar_expect_tx(full_local, STAGE_BYTES * (CTA2 ? 2 : 1));
           const int k0 = kb * BK;
-          // A tile
+          // A tile: this CTA's 128 rows
           if (A_MN) {
             const int krow = t.k_row0 + k0;
-            tma_load_2d(a_dst, &tmA, full, m0, krow);
-            tma_load_2d(a_dst + 8192, &tmA, full, m0 + 64, krow);
+            if (CTA2) {
+              tma_load_2d_pair(a_dst, &tmA, full, m0, krow);
+              tma_load_2d_pair(a_dst + 8192, &tmA, full, m0 + 64, krow);
+            } else {
+              tma_load_2d(a_dst, &tmA, full, m0, krow);
+              tma_load_2d(a_dst + 8192, &tmA, full, m0 + 64, krow);
+            }
           } else {
-            tma_load_2d(a_dst, &tmA, full, k0, m0);
+            if (CTA2) {
+              tma_load_2d_pair(a_dst, &tmA, full, k0, m0);
+            } else {
+              tma_load_2d(a_dst, &tmA, full, k0, m0);
+            }
           }
-          // B tile
+          // B tile: all 256 columns, or with CTA2 this CTA's 128-column half
           if (B_MN) {
             const int krow = GROUPK ? (t.k_row0 + k0) : static_cast<int>(t.group * p.b_group_rows + k0);
-            const int n0 = t.n_block * BN;
+            const int n0 = t.n_block * BN + (CTA2 ? static_cast<int>(rank) * 128 : 0);
+            if (CTA2) {
+              tma_load_2d_pair(b_dst, &tmB0, full, n0, krow);
+              tma_load_2d_pair(b_dst + 8192, &tmB0, full, n0 + 64, krow);
+            } else {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) tma_load_2d(b_dst + j * 8192, &tmB0, full, n0 + 64 * j, krow);
+              for (int j = 0; j < 4; ++j) tma_load_2d(b_dst + j * 8192, &tmB0, full, n0 + 64 * j, krow);
+            }
           } else {
             const int nrow = static_cast<int>(t.group * p.b_group_rows) + t.n_block * (EPI == EPI_GLU ? 128 : BN);
-            tma_load_2d(b_dst, &tmB0, full, k0, nrow);
-            tma_load_2d(b_dst + 16384, &tmB1, full, k0, nrow + p.b1_row_offset);
+            if (CTA2) {
+              if (rank == 0) {
+                tma_load_2d_pair(b_dst, &tmB0, full, k0, nrow);
+              } else {
+                tma_load_2d_pair(b_dst, &tmB1, full, k0, nrow + p.b1_row_offset);
+              }
+            } else {
+              tma_load_2d(b_dst, &tmB0, full, k0, nrow);
+              tma_load_2d(b_dst + 16384, &tmB1, full, k0, nrow + p.b1_row_offset);
+            }
           }
           if (++stage == STAGES) {
             stage = 0;
@@ -225,10 +371,10 @@ ffm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       }
     }
   } else if (warp == 1) {
-    // ================= MMA issuer =================
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN, B_MN);
-      TileWalker<GROUPK> walker(p, ctrl->tile_start);
+    // ================= MMA issuer (with CTA2: only in the even CTA of the pair) =================
+    if (lane == 0 && leader) {
+      constexpr uint32_t idesc = make_idesc_bf16(CTA2 ? 256 : 128, BN, A_MN, B_MN);
+      TileWalker<GROUPK, CTA2> walker(p, ctrl->tile_start, rank);
       TileCoord t;
       int stage = 0;
       uint32_t phase = 0;
@@ -236,15 +382,15 @@ ffm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       uint32_t acc_phase = 0;
       bool ok = true;
       while (ok && walker.next(t)) {
-        if (t.k_blocks == 0) continue;  // empty group: the epilogue writes zeros without an accumulator
+        if (t.k_blocks == 0) continue;  // empty group: the epilogue stores zeros without an accumulator
         ok = mbar_wait_bounded(smem_u32(&ctrl->acc_empty_bar[acc]), acc_phase ^ 1u, abort_flag, p.status,
                                FFM_STATUS_WAIT_MMA, p.wait_cycles);
         if (!ok) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < t.k_blocks; ++kb) {
-          ok = mbar_wait_bounded(smem_u32(&ctrl->full_bar[stage]), phase, abort_flag, p.status,
-                                 FFM_STATUS_WAIT_MMA, p.wait_cycles);
+          ok = mbar_wait_bounded(smem_u32(&ctrl->full_bar[stage]), phase, abort_flag, p.status, FFM_STATUS_WAIT_MMA,
+                                 p.wait_cycles);
           if (!ok) break;
           tc_fence_after();
           const uint32_t a_src = smem_base + stage * STAGE_BYTES;
@@ -255,16 +401,33 @@ ffm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                                         : make_smem_desc_sw128(a_src + kk * 32, 16, 1024);
             const uint64_t bdesc = B_MN ? make_smem_desc_sw128(b_src + kk * 2048, 8192, 1024)
                                         : make_smem_desc_sw128(b_src + kk * 32, 16, 1024);
-            umma_bf16(d_tmem, adesc, bdesc, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+            if (CTA2) {
+              umma_bf16_pair(d_tmem, adesc, bdesc, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+            } else {
+              umma_bf16(d_tmem, adesc, bdesc, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+            }
           }
-          umma_commit(smem_u32(&ctrl->empty_bar[stage]));  // frees the stage once these MMAs retire
+          // free the stage (in both CTAs) once these MMAs retire
+          const uint32_t empty_local = smem_u32(&ctrl->empty_bar[stage]);
+          if (CTA2) {
+            umma_commit_pair(empty_local);
+            umma_commit_pair(map_to_cta(empty_local, 1));
+          } else {
+            umma_commit(empty_local);
+          }
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
           }
         }
         if (!ok) break;
-        umma_commit(smem_u32(&ctrl->acc_full_bar[acc]));
+        const uint32_t accf_local = smem_u32(&ctrl->acc_full_bar[acc]);
+        if (CTA2) {
+          umma_commit_pair(accf_local);
+          umma_commit_pair(map_to_cta(accf_local, 1));
+        } else {
+          umma_commit(accf_local);
+        }
         if (++acc == NUM_ACC) {
           acc = 0;
           acc_phase ^= 1u;
@@ -274,112 +437,142 @@ ffm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   } else {
     // ================= epilogue (warps 2..5) =================
     const int quarter = warp & 3;  // TMEM lanes [32 * quarter, 32 * quarter + 32) belong to this warp
-    const int row_in_tile = quarter * 32 + lane;
-    TileWalker<GROUPK> walker(p, ctrl->tile_start);
+    const uint32_t stg = stg_base + (warp - 2) * STG_WARP_BYTES;
+    TileWalker<GROUPK, CTA2> walker(p, ctrl->tile_start, rank);
     TileCoord t;
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
     while (ok && walker.next(t)) {
-      const long long row = static_cast<long long>(t.m_tile) * BM + row_in_tile;
-      if (t.k_blocks == 0) {
-        // grouped-K with an empty group: the gradient tile is zero
-        if (GROUPK && row < p.m_rows) {
-          bf16* crow = p.C + t.group * p.c_group_stride + row * p.ldc;
-          const int n0 = t.n_block * BN;
-          for (int c = 0; c < BN / 8; ++c) {
-            const int col = n0 + c * 8;
-            if (col < p.n_cols) *reinterpret_cast<uint4*>(crow + col) = make_uint4(0, 0, 0, 0);
-          }
-        }
-        continue;
+      const int row0 = t.m_tile * BM + quarter * 32;  // first row of this warp's 32-row slab
+      const int zdim = GROUPK ? t.group : 0;
+      const bool have_acc = t.k_blocks > 0;
+      if (have_acc) {
+        ok = mbar_wait_bounded(smem_u32(&ctrl->acc_full_bar[acc]), acc_phase, abort_flag, p.status,
+                               FFM_STATUS_WAIT_EPILOGUE, p.wait_cycles);
+        ok = __all_sync(0xffffffffu, ok ? 1 : 0) != 0;
+        if (!ok) break;
+        tc_fence_after();
       }
-      ok = mbar_wait_bounded(smem_u32(&ctrl->acc_full_bar[acc]), acc_phase, abort_flag, p.status,
-                             FFM_STATUS_WAIT_EPILOGUE, p.wait_cycles);
-      ok = __all_sync(0xffffffffu, ok ? 1 : 0) != 0;
-      if (!ok) break;
-      tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
 
       if (EPI == EPI_GLU) {
+        // four 32-column chunks of gate and up; the TMEM loads of chunk c + 1 fly while chunk c is processed
         const int h0 = t.n_block * 128;
-        const bool row_ok = row < p.m_rows;
-        bf16* act_row = p.C + row * p.ldc + h0;
-        bf16* pre_row = p.C2 ? (p.C2 + row * p.ldc2 + h0) : nullptr;
-#pragma unroll 1
+        uint32_t g[2][32], u[2][32];
+        tmem_ld_32x32(taddr, g[0]);
+        tmem_ld_32x32(taddr + 128, u[0]);
+#pragma unroll
         for (int c = 0; c < 4; ++c) {
-          if (h0 + c * 32 >= p.n_cols) break;
-          uint32_t g[32], u[32];
-          tmem_ld_32x32(taddr + c * 32, g);
-          tmem_ld_32x32(taddr + 128 + c * 32, u);
           tmem_ld_wait();
-          uint32_t pg[16], pu[16], pa[16];
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            pg[i] = pack_bf16x2(__uint_as_float(g[2 * i]), __uint_as_float(g[2 * i + 1]));
-            pu[i] = pack_bf16x2(__uint_as_float(u[2 * i]), __uint_as_float(u[2 * i + 1]));
-            const float2 gf = unpack_bf16x2(pg[i]);
-            const float2 uf = unpack_bf16x2(pu[i]);
-            pa[i] = pack_bf16x2(glu_fwd(p.act, gf.x, uf.x), glu_fwd(p.act, gf.y, uf.y));
+          if (c + 1 < 4) {
+            tmem_ld_32x32(taddr + (c + 1) * 32, g[(c + 1) & 1]);
+            tmem_ld_32x32(taddr + 128 + (c + 1) * 32, u[(c + 1) & 1]);
           }
-          if (row_ok) {
+          if (h0 + c * 32 < p.n_cols) {
+            uint32_t pg[16], pu[16], pa[16];
 #pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              *reinterpret_cast<uint4*>(act_row + c * 32 + v * 8) =
-                  make_uint4(pa[4 * v], pa[4 * v + 1], pa[4 * v + 2], pa[4 * v + 3]);
+            for (int i = 0; i < 16; ++i) {
+              pg[i] = pack_bf16x2(__uint_as_float(g[c & 1][2 * i]), __uint_as_float(g[c & 1][2 * i + 1]));
+              pu[i] = pack_bf16x2(__uint_as_float(u[c & 1][2 * i]), __uint_as_float(u[c & 1][2 * i + 1]));
+              const float2 gf = unpack_bf16x2(pg[i]);
+              const float2 uf = unpack_bf16x2(pu[i]);
+              pa[i] = pack_bf16x2(glu_fwd(p.act, gf.x, uf.x), glu_fwd(p.act, gf.y, uf.y));
             }
-            if (pre_row != nullptr) {
+            // the staging buffers are free once the previous chunk's bulk stores have read them
+            if (lane == 0) bulk_wait_read0();
+            __syncwarp();
 #pragma unroll
-              for (int v = 0; v < 4; ++v) {
-                *reinterpret_cast<uint4*>(pre_row + c * 32 + v * 8) =
-                    make_uint4(pg[4 * v], pg[4 * v + 1], pg[4 * v + 2], pg[4 * v + 3]);
-                *reinterpret_cast<uint4*>(pre_row + p.glu_h + c * 32 + v * 8) =
-                    make_uint4(pu[4 * v], pu[4 * v + 1], pu[4 * v + 2], pu[4 * v + 3]);
+            for (int q = 0; q < 4; ++q) {
+              const uint32_t o = stg_offset(lane, q);
+              st_shared_v4(stg + o, pa[4 * q], pa[4 * q + 1], pa[4 * q + 2], pa[4 * q + 3]);
+              if (p.has_c2) {
+                st_shared_v4(stg + STG_ARRAY_BYTES + o, pg[4 * q], pg[4 * q + 1], pg[4 * q + 2], pg[4 * q + 3]);
+                st_shared_v4(stg + 2 * STG_ARRAY_BYTES + o, pu[4 * q], pu[4 * q + 1], pu[4 * q + 2], pu[4 * q + 3]);
               }
+            }
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_3d(&tmC, stg, h0 + c * 32, row0, 0);
+              if (p.has_c2) {
+                tma_store_3d(&tmC2, stg + STG_ARRAY_BYTES, h0 + c * 32, row0, 0);
+                tma_store_3d(&tmC2, stg + 2 * STG_ARRAY_BYTES, p.glu_h + h0 + c * 32, row0, 0);
+              }
+              bulk_commit();
             }
           }
         }
       } else {
+        // eight 32-column chunks, TMEM loads one chunk ahead, two staging buffers in rotation
         const int n0 = t.n_block * BN;
-        bf16* crow = p.C + (GROUPK ? t.group * p.c_group_stride : 0LL) + row * p.ldc + n0;
-        const bool row_ok = row < p.m_rows;
         const float scale = p.scale;
-#pragma unroll 1
+        uint32_t v[2][32];
+        int slot = 0;  // staging buffer of the next store; toggles per store actually issued
+        if (have_acc) tmem_ld_32x32(taddr, v[0]);
+#pragma unroll
         for (int c = 0; c < BN / 32; ++c) {
-          if (n0 + c * 32 >= p.n_cols) break;
-          uint32_t v[32];
-          tmem_ld_32x32(taddr + c * 32, v);
-          tmem_ld_wait();
-          if (row_ok) {
+          if (have_acc) {
+            tmem_ld_wait();
+            if (c + 1 < BN / 32) tmem_ld_32x32(taddr + (c + 1) * 32, v[(c + 1) & 1]);
+          }
+          if (n0 + c * 32 < p.n_cols) {
             uint32_t o[16];
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
-              o[i] = pack_bf16x2(__uint_as_float(v[2 * i]) * scale, __uint_as_float(v[2 * i + 1]) * scale);
+              o[i] = have_acc ? pack_bf16x2(__uint_as_float(v[c & 1][2 * i]) * scale,
+                                            __uint_as_float(v[c & 1][2 * i + 1]) * scale)
+                              : 0u;
             }
+            const uint32_t buf = stg + slot * STG_ARRAY_BYTES;
+            slot ^= 1;
+            if (lane == 0) bulk_wait_read1();  // the store issued two stores ago has read this buffer
+            __syncwarp();
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
-              *reinterpret_cast<uint4*>(crow + c * 32 + q * 8) = make_uint4(o[4 * q], o[4 * q + 1], o[4 * q + 2], o[4 * q + 3]);
+              st_shared_v4(buf + stg_offset(lane, q), o[4 * q], o[4 * q + 1], o[4 * q + 2], o[4 * q + 3]);
+            }
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_3d(&tmC, buf, n0 + c * 32, row0, zdim);
+              bulk_commit();
             }
           }
         }
       }
-      // hand the accumulator back to the MMA issuer
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&ctrl->acc_empty_bar[acc]));
-      if (++acc == NUM_ACC) {
-        acc = 0;
-        acc_phase ^= 1u;
+      if (have_acc) {
+        // hand the accumulator back to the MMA issuer (from the odd CTA of a pair: a remote arrive)
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          const uint32_t bar = smem_u32(&ctrl->acc_empty_bar[acc]);
+          if (CTA2) {
+            mbar_arrive_cluster(map_to_cta(bar, 0));
+          } else {
+            mbar_arrive(bar);
+          }
+        }
+        if (++acc == NUM_ACC) {
+          acc = 0;
+          acc_phase ^= 1u;
+        }
       }
     }
+    if (lane == 0) bulk_wait0();  // this lane's bulk stores have landed before the CTA's shared memory goes away
   }
 
   // ---- common exit: every role reaches this point, also after an abort ----------------------
   tc_fence_before();
   __syncthreads();
+  if (CTA2) cluster_sync_all();  // neither CTA leaves while its peer may still touch its barriers or operands
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, TMEM_COLS);
+    if (CTA2) {
+      tmem_dealloc2(tmem_base, TMEM_COLS);
+    } else {
+      tmem_dealloc(tmem_base, TMEM_COLS);
+    }
   }
 }
 
@@ -422,6 +615,22 @@ int make_map_2d(CUtensorMap* map, const void* base, long long rows, long long co
   return r == CUDA_SUCCESS ? FFM_OK : FFM_ERR_LAUNCH;
 }
 
+// 3-D bf16 output map over [groups, rows, cols] (row-major, contiguous), 64-byte swizzle, box {32, 32, 1}.
+int make_out_map(CUtensorMap* map, void* base, long long groups, long long rows, long long cols) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return FFM_ERR_NO_DRIVER;
+  if (groups <= 0 || rows <= 0 || cols <= 0) return FFM_ERR_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0 || (cols * 2) % 16 != 0) return FFM_ERR_UNSUPPORTED;
+  cuuint64_t dims[3] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(groups)};
+  cuuint64_t strides[2] = {static_cast<cuuint64_t>(cols) * 2, static_cast<cuuint64_t>(cols) * rows * 2};
+  cuuint32_t box[3] = {32, 32, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, base, dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? FFM_OK : FFM_ERR_LAUNCH;
+}
+
 int num_sms() {
   static int sms = 0;
   if (sms == 0) {
@@ -434,23 +643,82 @@ int num_sms() {
 }
 
 long long g_wait_cycles = 2000000000LL;
+int g_cta_pair = -1;  // -1: read FFM_GEMM_CTA_PAIR from the environment on first use (default on)
 
-template <int A_MN, int B_MN, int EPI, int GROUPK>
-int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB0, const CUtensorMap& tmB1, const GemmParams& p,
-                long long max_tiles, cudaStream_t stream) {
-  static bool configured = false;
-  auto kernel = ffm_gemm_kernel<A_MN, B_MN, EPI, GROUPK>;
-  if (!configured) {
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess) {
+bool use_cta_pair() {
+  if (g_cta_pair < 0) {
+    const char* e = getenv("FFM_GEMM_CTA_PAIR");
+    g_cta_pair = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return g_cta_pair != 0;
+}
+
+template <int A_MN, int B_MN, int EPI, int GROUPK, int CTA2>
+int launch_gemm_shape(const CUtensorMap& tmA, const CUtensorMap& tmB0, const CUtensorMap& tmB1, const CUtensorMap& tmC,
+                      const CUtensorMap& tmC2, const GemmParams& p, long long max_units, cudaStream_t stream) {
+  static int max_ctas = 0;  // persistent grid size, found once per instantiation
+  auto kernel = ffm_gemm_kernel<A_MN, B_MN, EPI, GROUPK, CTA2>;
+  constexpr int smem_bytes = Shape<CTA2>::SMEM_BYTES;
+  if (max_ctas == 0) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess) {
       cudaGetLastError();
       return FFM_ERR_LAUNCH;
     }
-    configured = true;
+    max_ctas = num_sms();
+    if (CTA2) {
+      // co-resident CTA pairs: a GPC with an odd number of usable SMs leaves one SM without a partner
+      cudaLaunchConfig_t q = {};
+      q.gridDim = dim3(num_sms() & ~1, 1, 1);
+      q.blockDim = dim3(GEMM_THREADS, 1, 1);
+      q.dynamicSmemBytes = smem_bytes;
+      cudaLaunchAttribute qa[1];
+      qa[0].id = cudaLaunchAttributeClusterDimension;
+      qa[0].val.clusterDim.x = 2;
+      qa[0].val.clusterDim.y = 1;
+      qa[0].val.clusterDim.z = 1;
+      q.attrs = qa;
+      q.numAttrs = 1;
+      int clusters = 0;
+      if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &q) != cudaSuccess || clusters <= 0) {
+        cudaGetLastError();
+        clusters = num_sms() / 2 - 4;
+      }
+      max_ctas = 2 * clusters;
+    }
   }
-  if (max_tiles <= 0) return FFM_OK;
-  const int grid = static_cast<int>(max_tiles < num_sms() ? max_tiles : num_sms());
-  kernel<<<grid, GEMM_THREADS, SMEM_BYTES, stream>>>(tmA, tmB0, tmB1, p);
-  return cudaGetLastError() == cudaSuccess ? FFM_OK : FFM_ERR_LAUNCH;
+  if (max_units <= 0) return FFM_OK;
+  long long ctas = CTA2 ? 2 * max_units : max_units;
+  if (ctas > max_ctas) ctas = max_ctas;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(ctas), 1, 1);
+  cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = smem_bytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = CTA2 ? 2 : 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, kernel, tmA, tmB0, tmB1, tmC, tmC2, p) != cudaSuccess) {
+    cudaGetLastError();
+    return FFM_ERR_LAUNCH;
+  }
+  return FFM_OK;
+}
+
+// max_m_tiles: upper bound on the 128-row tiles of M the walker can see (per group for grouped-K);
+// multiplier: tiles per M tile (N blocks, times groups for grouped-K).
+template <int A_MN, int B_MN, int EPI, int GROUPK>
+int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB0, const CUtensorMap& tmB1, const CUtensorMap& tmC,
+                const CUtensorMap& tmC2, const GemmParams& p, long long max_m_tiles, long long multiplier,
+                cudaStream_t stream) {
+  if (use_cta_pair()) {
+    return launch_gemm_shape<A_MN, B_MN, EPI, GROUPK, 1>(tmA, tmB0, tmB1, tmC, tmC2, p,
+                                                         ((max_m_tiles + 1) / 2) * multiplier, stream);
+  }
+  return launch_gemm_shape<A_MN, B_MN, EPI, GROUPK, 0>(tmA, tmB0, tmB1, tmC, tmC2, p, max_m_tiles * multiplier, stream);
 }
 
 }  // namespace
@@ -465,6 +733,12 @@ extern "C" long long ffm_set_wait_cycles(long long cycles) {
   return old;
 }
 
+extern "C" int ffm_set_gemm_cta_pair(int enable) {
+  const int old = use_cta_pair() ? 1 : 0;
+  if (enable == 0 || enable == 1) g_cta_pair = enable;
+  return old;
+}
+
 extern "C" int ffm_grouped_gemm_glu(const void* A, const void* w_gate, const void* w_up, int64_t group_rows,
                                     int groups, const int32_t* tile_start, int64_t rows, int K, int H,
                                     int activation, void* act, void* preact, int32_t* status,
@@ -475,33 +749,35 @@ extern "C" int ffm_grouped_gemm_glu(const void* A, const void* w_gate, const voi
   if (tile_start == nullptr && groups != 1) return FFM_ERR_BAD_ARG;
   if (K % 64 != 0 || H % 32 != 0) return FFM_ERR_UNSUPPORTED;
   if (rows == 0) return FFM_OK;
-  CUtensorMap tmA, tmB0, tmB1;
+  CUtensorMap tmA, tmB0, tmB1, tmC, tmC2;
   int rc;
   if ((rc = make_map_2d(&tmA, A, rows, K, 64, 128)) != FFM_OK) return rc;
   const long long wrows = static_cast<long long>(groups - 1) * group_rows + H;
   if ((rc = make_map_2d(&tmB0, w_gate, wrows, K, 64, 128)) != FFM_OK) return rc;
   if ((rc = make_map_2d(&tmB1, w_up, wrows, K, 64, 128)) != FFM_OK) return rc;
+  if ((rc = make_out_map(&tmC, act, 1, rows, H)) != FFM_OK) return rc;
+  if (preact != nullptr) {
+    if ((rc = make_out_map(&tmC2, preact, 1, rows, 2LL * H)) != FFM_OK) return rc;
+  } else {
+    tmC2 = tmC;
+  }
   GemmParams p = {};
   p.tile_start = tile_start;
   p.groups = groups;
   p.dense_m_tiles = static_cast<int>((rows + BM - 1) / BM);
-  p.m_rows = rows;
   p.n_cols = H;
   p.k_blocks = K / BK;
   p.b_group_rows = group_rows;
   p.b1_row_offset = 0;
-  p.C = static_cast<bf16*>(act);
-  p.ldc = H;
-  p.C2 = static_cast<bf16*>(preact);
-  p.ldc2 = 2LL * H;
+  p.has_c2 = preact != nullptr ? 1 : 0;
   p.glu_h = H;
   p.scale = 1.0f;
   p.act = activation;
   p.n_tiles = (H + 127) / 128;
   p.status = status;
   p.wait_cycles = g_wait_cycles;
-  const long long max_tiles = ((rows + BM - 1) / BM) * p.n_tiles;
-  return launch_gemm<0, 0, EPI_GLU, 0>(tmA, tmB0, tmB1, p, max_tiles, static_cast<cudaStream_t>(stream));
+  return launch_gemm<0, 0, EPI_GLU, 0>(tmA, tmB0, tmB1, tmC, tmC2, p, (rows + BM - 1) / BM, p.n_tiles,
+                                       static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int ffm_grouped_gemm(const void* A, const void* B, int b_major, int groups, const int32_t* tile_start,
@@ -514,33 +790,31 @@ extern "C" int ffm_grouped_gemm(const void* A, const void* B, int b_major, int g
   if (K % 64 != 0 || Nout % 32 != 0) return FFM_ERR_UNSUPPORTED;
   if (b_major == FFM_B_NMAJOR && Nout % 64 != 0) return FFM_ERR_UNSUPPORTED;
   if (rows == 0) return FFM_OK;
-  CUtensorMap tmA, tmB;
+  CUtensorMap tmA, tmB, tmC;
   int rc;
   if ((rc = make_map_2d(&tmA, A, rows, K, 64, 128)) != FFM_OK) return rc;
+  if ((rc = make_out_map(&tmC, out, 1, rows, Nout)) != FFM_OK) return rc;
   GemmParams p = {};
   p.tile_start = tile_start;
   p.groups = groups;
   p.dense_m_tiles = static_cast<int>((rows + BM - 1) / BM);
-  p.m_rows = rows;
   p.n_cols = Nout;
   p.k_blocks = K / BK;
-  p.C = static_cast<bf16*>(out);
-  p.ldc = Nout;
   p.scale = scale;
   p.n_tiles = (Nout + BN - 1) / BN;
   p.status = status;
   p.wait_cycles = g_wait_cycles;
-  const long long max_tiles = ((rows + BM - 1) / BM) * p.n_tiles;
+  const long long m_tiles = (rows + BM - 1) / BM;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (b_major == FFM_B_KMAJOR) {
     if ((rc = make_map_2d(&tmB, B, static_cast<long long>(groups) * Nout, K, 64, 128)) != FFM_OK) return rc;
     p.b_group_rows = Nout;
     p.b1_row_offset = 128;
-    return launch_gemm<0, 0, EPI_PLAIN, 0>(tmA, tmB, tmB, p, max_tiles, s);
+    return launch_gemm<0, 0, EPI_PLAIN, 0>(tmA, tmB, tmB, tmC, tmC, p, m_tiles, p.n_tiles, s);
   }
   if ((rc = make_map_2d(&tmB, B, static_cast<long long>(groups) * K, Nout, 64, 64)) != FFM_OK) return rc;
   p.b_group_rows = K;
-  return launch_gemm<0, 1, EPI_PLAIN, 0>(tmA, tmB, tmB, p, max_tiles, s);
+  return launch_gemm<0, 1, EPI_PLAIN, 0>(tmA, tmB, tmB, tmC, tmC, p, m_tiles, p.n_tiles, s);
 }
 
 extern "C" int ffm_grouped_gemm_wgrad(const void* A, const void* B, int groups, const int32_t* tile_start,
@@ -549,23 +823,21 @@ extern "C" int ffm_grouped_gemm_wgrad(const void* A, const void* B, int groups, 
   if (!A || !B || !dW || !status || !tile_start) return FFM_ERR_BAD_ARG;
   if (groups < 1 || groups > MAX_GROUPS || rows_cap <= 0 || M <= 0 || Nout <= 0) return FFM_ERR_BAD_ARG;
   if (M % 64 != 0 || Nout % 64 != 0) return FFM_ERR_UNSUPPORTED;
-  CUtensorMap tmA, tmB;
+  CUtensorMap tmA, tmB, tmC;
   int rc;
   if ((rc = make_map_2d(&tmA, A, rows_cap, M, 64, 64)) != FFM_OK) return rc;
   if ((rc = make_map_2d(&tmB, B, rows_cap, Nout, 64, 64)) != FFM_OK) return rc;
+  if ((rc = make_out_map(&tmC, dW, groups, M, Nout)) != FFM_OK) return rc;
   GemmParams p = {};
   p.tile_start = tile_start;
   p.groups = groups;
-  p.m_rows = M;
   p.n_cols = Nout;
-  p.C = static_cast<bf16*>(dW);
-  p.ldc = Nout;
-  p.c_group_stride = static_cast<long long>(M) * Nout;
   p.scale = scale;
   p.m_tiles_per_group = (M + BM - 1) / BM;
   p.n_tiles = (Nout + BN - 1) / BN;
   p.status = status;
   p.wait_cycles = g_wait_cycles;
-  const long long max_tiles = static_cast<long long>(groups) * p.m_tiles_per_group * p.n_tiles;
-  return launch_gemm<1, 1, EPI_PLAIN, 1>(tmA, tmB, tmB, p, max_tiles, static_cast<cudaStream_t>(stream));
+  return launch_gemm<1, 1, EPI_PLAIN, 1>(tmA, tmB, tmB, tmC, tmC, p, p.m_tiles_per_group,
+                                         static_cast<long long>(groups) * p.n_tiles,
+                                         static_cast<cudaStream_t>(stream));
 }

@@ -308,25 +308,50 @@ route_hist_ids(const int32_t* __restrict__ ids, long long T, int E, int slots_pe
 }
 
 // One block. block_off[b][e] = sum_{b' < b} hist[b'][e]; counts; tile_start; stats.
+// One warp per expert: the lanes sweep the block histograms 32 at a time (independent loads, a shuffle scan and a
+// carry), so the kernel costs a few dozen dependent steps instead of one per block. All sums keep a fixed order.
 __global__ void __launch_bounds__(ROUTE_THREADS)
 route_scan(const int32_t* __restrict__ block_hist, const float* __restrict__ block_mass,
            const float* __restrict__ block_z, int blocks, int E, int32_t* __restrict__ block_off,
            int32_t* __restrict__ counts, int32_t* __restrict__ tile_start, float* __restrict__ stats) {
   __shared__ int s_counts[MAX_E];
   __shared__ float s_mass[MAX_E];
-  for (int e = threadIdx.x; e < E; e += ROUTE_THREADS) {
-    int run = 0;
+  __shared__ float s_zsum;
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  for (int e = warp; e < E; e += ROUTE_WARPS) {
+    int carry = 0;
     float m = 0.0f;
-    for (int b = 0; b < blocks; ++b) {
+#pragma unroll 4
+    for (int b0 = 0; b0 < blocks; b0 += 32) {
+      const int b = b0 + lane;
       const long long o = static_cast<long long>(b) * E + e;
-      block_off[o] = run;
-      run += block_hist[o];
-      if (block_mass != nullptr) m += block_mass[o];
+      const int v = (b < blocks) ? block_hist[o] : 0;
+      if (block_mass != nullptr && b < blocks) m += block_mass[o];
+      int x = v;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, x, d);
+        if (lane >= d) x += t;
+      }
+      if (b < blocks) block_off[o] = carry + x - v;
+      carry += __shfl_sync(0xffffffffu, x, 31);
     }
-    s_counts[e] = run;
-    s_mass[e] = m;
-    counts[e] = run;
-    if (stats != nullptr) stats[e] = m;
+    m = warp_sum(m);
+    if (lane == 0) {
+      s_counts[e] = carry;
+      s_mass[e] = m;
+      counts[e] = carry;
+      if (stats != nullptr) stats[e] = m;
+    }
+  }
+  if (warp == ROUTE_WARPS - 1) {
+    float z = 0.0f;
+    if (block_z != nullptr) {
+      for (int b = lane; b < blocks; b += 32) z += block_z[b];
+    }
+    z = warp_sum(z);
+    if (lane == 0) s_zsum = z;
   }
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -334,16 +359,12 @@ route_scan(const int32_t* __restrict__ block_hist, const float* __restrict__ blo
     float dot = 0.0f;
     tile_start[0] = 0;
     for (int e = 0; e < E; ++e) {
-      tiles += (s_counts[e] + 127) >> 7;
+      tiles += ((s_counts[e] + 255) >> 8) << 1;  // segments start on multiples of 256 rows
       tile_start[e + 1] = tiles;
       dot += static_cast<float>(s_counts[e]) * s_mass[e];
     }
     if (stats != nullptr) {
-      float z = 0.0f;
-      if (block_z != nullptr) {
-        for (int b = 0; b < blocks; ++b) z += block_z[b];
-      }
-      stats[E] = z;
+      stats[E] = s_zsum;
       stats[E + 1] = dot;
     }
   }
@@ -459,7 +480,7 @@ using namespace ffm;
 
 extern "C" int64_t ffm_rows_capacity(int64_t T, int E) {
   if (T < 0 || E < 1) return 0;
-  return ((T + 127LL * E) / 128) * 128;
+  return ((T + 255LL * E) / 256) * 256;
 }
 
 extern "C" size_t ffm_route_workspace_bytes(int64_t N, int E, int top_k) {

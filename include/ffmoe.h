@@ -15,9 +15,10 @@
  *   N tokens, D model width, H = ffn_dim / 2, E experts (E_local with expert parallelism), k = top_k,
  *   T = N * k routed rows. All activations and weights are bf16, row-major, contiguous.
  *   "Grouped rows": routed rows sorted by expert, stable in (token, slot) order, each expert's segment
- *   starting on a multiple of 128 rows (the MMA tile height). Rows between the end of an expert's tokens
- *   and the next multiple of 128 are zero. Buffers hold ffm_rows_capacity(T, E) rows.
- *     tile_start[E + 1]  int32  cumulative count of 128-row tiles per expert (tile_start[E] = tiles in use)
+ *   starting on a multiple of 256 rows (the height of the two-CTA MMA tile). Rows between the end of an
+ *   expert's tokens and the next multiple of 256 are zero. Buffers hold ffm_rows_capacity(T, E) rows.
+ *     tile_start[E + 1]  int32  cumulative count of 128-row tiles per expert, always even
+ *                               (tile_start[E] = tiles in use)
  *     pos[T]             int32  grouped row of flat slot i = n * k + j          (reference: expand_to_batch)
  *     src[rows_cap]      int32  flat slot held by a grouped row, -1 for padding (reference: sorted_order)
  */
@@ -66,11 +67,16 @@ typedef void* ffm_stream_t; /* cudaStream_t */
 int ffm_version(void);
 const char* ffm_error_string(int code);
 
-/* Rows a grouped buffer must hold for T routed rows over E experts: 128 * floor((T + 127 E) / 128). */
+/* Rows a grouped buffer must hold for T routed rows over E experts: 256 * floor((T + 255 E) / 256). */
 int64_t ffm_rows_capacity(int64_t T, int E);
 
 /* Set the cycle budget of every bounded device-side wait (default 2e9, about one second). Returns the old value. */
 long long ffm_set_wait_cycles(long long cycles);
+
+/* Choose the GEMM tile shape: 1 (default) = 256 x 256 tiles on pairs of CTAs (tcgen05.mma.cta_group::2),
+ * 0 = 128 x 256 tiles on single CTAs. Results are identical; the environment variable FFM_GEMM_CTA_PAIR=0
+ * selects 0 at first use. Any other argument only queries. Returns the previous setting. */
+int ffm_set_gemm_cta_pair(int enable);
 
 /* -------------------------------------------------------------------------------------------------
  * Routing forward: gate GEMM + scoring + top-k + renormalisation + loss statistics + grouped-row map.
@@ -114,7 +120,8 @@ int ffm_permute_rows(const void* x, const int32_t* src, int64_t rows_cap, int to
                      ffm_stream_t stream);
 
 /* -------------------------------------------------------------------------------------------------
- * Grouped GEMMs on tcgen05 / TMEM tiles fed by TMA (128 x 256 x 64 tiles, fp32 accumulation).
+ * Grouped GEMMs on tcgen05 / TMEM tiles fed by TMA (256 x 256 x 64 tiles on CTA pairs, fp32 accumulation,
+ * outputs written with TMA stores).
  * tile_start == NULL selects the dense case: one group, `rows` rows of A (any value, masked at the edge).
  *
  * ffm_grouped_gemm_glu:  act[r, :] = glu(A[r, :] * Wg[e]^T, A[r, :] * Wu[e]^T), optional preact[r, 0:2H].

@@ -89,19 +89,20 @@ def sort_metadata(topk_idx, E):
     return order, counts, starts
 
 
-def grouped_layout(topk_idx, E, tile=128):
+def grouped_layout(topk_idx, E, tile=128, align=256):
     """The product's grouped-row layout: the stable order above with every expert segment starting on a
-    multiple of `tile` rows. Returns (tile_start[E+1], pos[T], src[rows_cap])."""
+    multiple of `align` rows; tile_start counts `tile`-row tiles. Returns (tile_start[E+1], pos[T],
+    src[rows_cap])."""
     flat = topk_idx.reshape(-1)
     T = flat.numel()
     order, counts, starts = sort_metadata(topk_idx, E)
-    tiles = (counts + tile - 1) // tile
+    tiles = ((counts + align - 1) // align) * (align // tile)
     tile_start = torch.zeros(E + 1, dtype=torch.long)
     tile_start[1:] = torch.cumsum(tiles, 0)
     rank = torch.arange(T) - starts[flat[order]]
     pos = torch.empty(T, dtype=torch.long)
     pos[order] = tile_start[flat[order]] * tile + rank
-    rows_cap = ((T + (tile - 1) * E) // tile) * tile
+    rows_cap = ((T + (align - 1) * E) // align) * align
     src = torch.full((rows_cap,), -1, dtype=torch.long)
     src[pos] = torch.arange(T)
     return tile_start, pos, src

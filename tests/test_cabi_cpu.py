@@ -38,9 +38,10 @@ def test_host_only_entry_points():
     assert _lib.error_string(0) == "ok"
     assert "workspace" in _lib.error_string(-4)
     assert "epilogue" in _lib.error_string(103)
-    # rows capacity: 128 * floor((T + 127 E) / 128)
-    assert lib.ffm_rows_capacity(32768, 8) == 128 * ((32768 + 127 * 8) // 128)
-    assert lib.ffm_rows_capacity(0, 4) == 128 * ((127 * 4) // 128)
+    # rows capacity: 256 * floor((T + 255 E) / 256)
+    assert lib.ffm_rows_capacity(32768, 8) == 256 * ((32768 + 255 * 8) // 256)
+    assert lib.ffm_rows_capacity(0, 4) == 256 * ((255 * 4) // 256)
+    assert lib.ffm_set_gemm_cta_pair(-1) in (0, 1)
     assert lib.ffm_route_workspace_bytes(16384, 8, 2) > 0
     assert lib.ffm_route_backward_workspace_bytes(16384, 1024, 8) > 16384 * 8 * 2
     old = lib.ffm_set_wait_cycles(12345)

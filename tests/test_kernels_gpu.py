@@ -77,7 +77,7 @@ def test_route_forward(N, D, E, k, gating):
     flat = r.topk_idx.long().view(-1)
     counts = torch.bincount(flat, minlength=E)
     assert torch.equal(r.counts.long(), counts)
-    tiles = (counts + 127) // 128
+    tiles = 2 * ((counts + 255) // 256)
     ts = torch.zeros(E + 1, dtype=torch.long, device=DEV)
     ts[1:] = torch.cumsum(tiles, 0)
     assert torch.equal(r.tile_start.long(), ts)
@@ -124,7 +124,7 @@ def test_group_rows_and_permute():
     c, ts, pos, src, rows_cap = ops.group_rows(ids, E)
     ops.check_status()
     assert c.tolist() == counts
-    assert ts.tolist() == [0] + torch.cumsum((torch.tensor(counts) + 127) // 128, 0).tolist()
+    assert ts.tolist() == [0] + torch.cumsum(2 * ((torch.tensor(counts) + 255) // 256), 0).tolist()
     order = torch.argsort(ids.long(), stable=True)
     starts = torch.zeros(E + 1, dtype=torch.long, device=DEV)
     starts[1:] = torch.cumsum(torch.tensor(counts, device=DEV), 0)
