@@ -35,6 +35,8 @@ SIGNATURES = {
                                   c_int64, c_void_p, c_void_p, c_size_t, c_void_p, c_void_p]),
     "ffm_group_rows": (c_int, [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
                                c_void_p, c_size_t, c_void_p, c_void_p]),
+    "ffm_group_rows_static": (c_int, [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
+                                      c_void_p, c_void_p]),
     "ffm_permute_rows": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p]),
     "ffm_grouped_gemm_glu": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p, c_int64, c_int, c_int,
                                      c_int, c_void_p, c_void_p, c_void_p, c_void_p]),

@@ -11,6 +11,8 @@ extern "C" const char* ffm_error_string(int code) {
     case FFM_ERR_LAUNCH: return "CUDA launch or driver call failed";
     case FFM_ERR_WORKSPACE: return "workspace too small";
     case FFM_ERR_NO_DRIVER: return "cuTensorMapEncodeTiled not available from the CUDA driver";
+    case FFM_ERR_STATIC_LIMIT:
+      return "problem exceeds the built-in scratch of ffm_group_rows_static (E <= 256 experts, T <= 1048576 rows)";
     case FFM_STATUS_WAIT_PRODUCER: return "device: TMA producer wait ran out";
     case FFM_STATUS_WAIT_MMA: return "device: MMA issuer wait ran out";
     case FFM_STATUS_WAIT_EPILOGUE: return "device: epilogue wait ran out";

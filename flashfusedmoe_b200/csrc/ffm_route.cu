@@ -472,6 +472,33 @@ void launch_route(int blocks, cudaStream_t s, const bf16* hidden, const bf16* ga
                                                            w.block_mass, w.block_z);
 }
 
+// ---- scratch for the allocation-free entry point ---------------------------------------------
+// Lives in the library image: every GPU that loads libffmoe holds these bytes until the process exits.
+// Sized for the stated maximum of ffm_group_rows_static: 592 blocks x 256 experts x 4 bytes, twice.
+static __device__ __align__(256) unsigned char g_static_scratch[FFM_STATIC_SCRATCH_BYTES];
+
+// Device address of g_static_scratch on the current device. In host code the array's name is only a
+// stand-in for the symbol, not a pointer a kernel could use, so the address is asked for once per device
+// (with that device current) and remembered.
+int static_scratch_address(void** out) {
+  static void* cached[64] = {};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    cudaGetLastError();
+    return FFM_ERR_LAUNCH;
+  }
+  if (cached[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || p == nullptr) {
+      cudaGetLastError();
+      return FFM_ERR_LAUNCH;
+    }
+    cached[dev] = p;
+  }
+  *out = cached[dev];
+  return FFM_OK;
+}
+
 }  // namespace
 
 }  // namespace ffm
@@ -554,5 +581,32 @@ extern "C" int ffm_group_rows(const int32_t* expert_ids, int64_t T, int E, int32
                                          nullptr);
   route_rank<<<g.blocks, ROUTE_THREADS, 0, s>>>(expert_ids, T, E, g.tokens_per_block, w.block_off, tile_start,
                                                 rows_cap, pos, src, status);
+  return cudaGetLastError() == cudaSuccess ? FFM_OK : FFM_ERR_LAUNCH;
+}
+
+extern "C" int ffm_group_rows_static(const int32_t* expert_ids, int64_t T, int E, int32_t* counts,
+                                     int32_t* tile_start, int32_t* pos, int32_t* src, int64_t rows_cap,
+                                     int32_t* status, ffm_stream_t stream) {
+  if (!expert_ids || !counts || !tile_start || !pos || !src || !status) return FFM_ERR_BAD_ARG;
+  if (T < 0 || E < 1) return FFM_ERR_BAD_ARG;
+  if (E > FFM_STATIC_MAX_EXPERTS || T > FFM_STATIC_MAX_ROWS) return FFM_ERR_STATIC_LIMIT;
+  if (rows_cap < ffm_rows_capacity(T, E)) return FFM_ERR_BAD_ARG;
+  const RouteGrid g = route_grid(T > 0 ? T : 1);
+  const size_t per = (static_cast<size_t>(g.blocks) * E * 4 + 255) / 256 * 256;
+  if (2 * per > FFM_STATIC_SCRATCH_BYTES) return FFM_ERR_STATIC_LIMIT;
+  void* base = nullptr;
+  const int rc = static_scratch_address(&base);
+  if (rc != FFM_OK) return rc;
+  // Every word of the scratch that the scan and rank kernels read is written by the histogram kernel of
+  // this same call, so nothing left over from an earlier call is ever consumed and no clearing is needed.
+  int32_t* block_hist = reinterpret_cast<int32_t*>(base);
+  int32_t* block_off = reinterpret_cast<int32_t*>(static_cast<unsigned char*>(base) + per);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (cudaMemsetAsync(src, 0xFF, static_cast<size_t>(rows_cap) * 4, s) != cudaSuccess) return FFM_ERR_LAUNCH;
+  route_hist_ids<<<g.blocks, ROUTE_THREADS, 0, s>>>(expert_ids, T, E, g.tokens_per_block, block_hist, status);
+  route_scan<<<1, ROUTE_THREADS, 0, s>>>(block_hist, nullptr, nullptr, g.blocks, E, block_off, counts, tile_start,
+                                         nullptr);
+  route_rank<<<g.blocks, ROUTE_THREADS, 0, s>>>(expert_ids, T, E, g.tokens_per_block, block_off, tile_start, rows_cap,
+                                                pos, src, status);
   return cudaGetLastError() == cudaSuccess ? FFM_OK : FFM_ERR_LAUNCH;
 }

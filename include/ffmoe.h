@@ -41,6 +41,7 @@ extern "C" {
 #define FFM_ERR_LAUNCH (-3)       /* cudaGetLastError() after a launch, or a driver call failed */
 #define FFM_ERR_WORKSPACE (-4)    /* workspace too small */
 #define FFM_ERR_NO_DRIVER (-5)    /* cuTensorMapEncodeTiled could not be resolved */
+#define FFM_ERR_STATIC_LIMIT (-6) /* problem larger than the built-in scratch of ffm_group_rows_static */
 
 /* Device-side status codes written into *status (0 = fine) */
 #define FFM_STATUS_WAIT_PRODUCER 101 /* TMA producer gave up waiting for a free stage */
@@ -110,6 +111,28 @@ int ffm_route_forward(const void* hidden, const void* gate_w, const float* exper
 int ffm_group_rows(const int32_t* expert_ids, int64_t T, int E, int32_t* counts, int32_t* tile_start, int32_t* pos,
                    int32_t* src, int64_t rows_cap, void* workspace, size_t workspace_bytes, int32_t* status,
                    ffm_stream_t stream);
+
+/* Allocation-free variant of ffm_group_rows. It has no counterpart in the reference; it exists for callers
+ * that cannot hand over a workspace because they are not allowed to allocate device memory at the point of the
+ * call: code running inside a memory-pool-managed region that forbids cudaMalloc (for example a serving loop
+ * whose allocator is frozen after start-up), or a host language binding that owns no device allocator at all
+ * and only passes through pointers it was given. The histogram / offset scratch that ffm_group_rows takes
+ * from the caller lives here in a fixed array inside the library image (FFM_STATIC_SCRATCH_BYTES per GPU,
+ * held from library load until process exit). Inputs and outputs are still the caller's buffers.
+ *
+ * Limits: E <= FFM_STATIC_MAX_EXPERTS and T <= FFM_STATIC_MAX_ROWS, otherwise FFM_ERR_STATIC_LIMIT is
+ * returned and nothing is launched. The call performs no cudaMalloc / cudaFree and calls no allocating
+ * library routine. The first call on each device looks up the device address of the built-in array (a
+ * one-time, per-device query made with that device current); make that first call outside any CUDA stream
+ * capture. All calls on a device share the one array: two calls whose kernels can overlap on the GPU (different
+ * streams without an ordering between them, or different host threads) race on it and corrupt each other's
+ * result; calls ordered on one stream are safe. The array keeps whatever the last call left in it; each
+ * call overwrites every word it later reads, so stale contents never leak into a result. */
+#define FFM_STATIC_SCRATCH_BYTES 1310720 /* 1.25 MiB */
+#define FFM_STATIC_MAX_EXPERTS 256
+#define FFM_STATIC_MAX_ROWS 1048576
+int ffm_group_rows_static(const int32_t* expert_ids, int64_t T, int E, int32_t* counts, int32_t* tile_start,
+                          int32_t* pos, int32_t* src, int64_t rows_cap, int32_t* status, ffm_stream_t stream);
 
 /* -------------------------------------------------------------------------------------------------
  * Permute: grouped[r, :] = x[src[r] / k, :] for src[r] >= 0, zero otherwise.
