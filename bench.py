@@ -249,25 +249,58 @@ def main():
     ops.check_status()
 
     # ---- end to end: pinned host input in, loss scalar out, every step ------------------------
-    def e2e_step():
-        for p in layer.parameters():
-            p.grad = None
-        xd = x_host.to(device, non_blocking=True).requires_grad_()
-        out, _ = layer(xd)
-        loss = (out.float() * go.float()).sum()
-        loss.backward()
-        return float(loss.item())
+    # The loop a training script would run around the public API: the next step's input is uploaded on a copy
+    # stream while the current step computes (two device buffers), and each step's loss is copied to pinned
+    # host memory and read one step later, so neither transfer stalls the compute stream. Every step still
+    # moves its own input host -> device and its own loss device -> host inside the timed region.
+    copy_stream = torch.cuda.Stream(device=device)
+    x_bufs = [torch.empty_like(x_host, device=device) for _ in range(2)]
+    loss_host = torch.zeros(2, dtype=torch.float32).pin_memory()
+    uploaded = [torch.cuda.Event(), torch.cuda.Event()]
+    consumed = [torch.cuda.Event(), torch.cuda.Event()]
+    loss_ready = [torch.cuda.Event(), torch.cuda.Event()]
 
-    for _ in range(3):
-        e2e_step()
+    def upload(i):
+        with torch.cuda.stream(copy_stream):
+            copy_stream.wait_event(consumed[i % 2])
+            x_bufs[i % 2].copy_(x_host, non_blocking=True)
+            uploaded[i % 2].record(copy_stream)
+
+    def e2e_run(steps):
+        losses_read = []
+        main = torch.cuda.current_stream()
+        for ev in consumed:
+            ev.record(main)
+        upload(0)
+        for i in range(steps):
+            if i + 1 < steps:
+                upload(i + 1)
+            main.wait_event(uploaded[i % 2])
+            for p in layer.parameters():
+                p.grad = None
+            xd = x_bufs[i % 2].detach().requires_grad_()
+            out, _ = layer(xd)
+            loss = (out * go).sum(dtype=torch.float32)
+            loss.backward()
+            consumed[i % 2].record(main)
+            loss_host[i % 2:i % 2 + 1].copy_(loss.detach().reshape(1), non_blocking=True)
+            loss_ready[i % 2].record(main)
+            if i >= 1:
+                loss_ready[(i - 1) % 2].synchronize()
+                losses_read.append(float(loss_host[(i - 1) % 2]))
+        loss_ready[(steps - 1) % 2].synchronize()
+        losses_read.append(float(loss_host[(steps - 1) % 2]))
+        return losses_read
+
+    e2e_run(3)
     fence()
     e0 = torch.cuda.Event(enable_timing=True)
     e1 = torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(K):
-        e2e_step()
+    read = e2e_run(K)
     e1.record()
     fence()
+    assert len(read) == K and all(v == v for v in read)
     e2e_ms = e0.elapsed_time(e1)
 
     t = torch.tensor([ms, e2e_ms], device=device, dtype=torch.float64)

@@ -116,6 +116,8 @@ route_gate_topk(const bf16* __restrict__ hidden, const bf16* __restrict__ gate_w
         acc0[e] = 0.0f;
         acc1[e] = 0.0f;
       }
+      // unrolled so that the loads of several chunks are in flight together (the kernel is latency-bound)
+#pragma unroll(GW <= 16 ? 4 : 1)
       for (int c = lane; c < chunks; c += 32) {
         const uint4 a0 = __ldg(h0p + c);
         const uint4 a1 = __ldg(h1p + c);

@@ -159,18 +159,36 @@ route_bwd_dgate(const bf16* __restrict__ gl, const bf16* __restrict__ hidden, lo
     for (int i = 0; i < 8; ++i) acc[e][i] = 0.0f;
 
   if (col_ok) {
-    for (long long n = n_begin; n < n_end; ++n) {
-      const uint4 gv = __ldg(reinterpret_cast<const uint4*>(gl + n * ldg_ + e0));
-      if ((gv.x | gv.y | gv.z | gv.w) == 0u) continue;  // all eight gradients are +0
-      const uint4 hv = __ldg(reinterpret_cast<const uint4*>(hidden + n * D + col0));
-      const float2 h0 = unpack_bf16x2(hv.x), h1 = unpack_bf16x2(hv.y), h2 = unpack_bf16x2(hv.z), h3 = unpack_bf16x2(hv.w);
-      const float h[8] = {h0.x, h0.y, h1.x, h1.y, h2.x, h2.y, h3.x, h3.y};
-      const float2 g0 = unpack_bf16x2(gv.x), g1 = unpack_bf16x2(gv.y), g2 = unpack_bf16x2(gv.z), g3 = unpack_bf16x2(gv.w);
-      const float g[8] = {g0.x, g0.y, g1.x, g1.y, g2.x, g2.y, g3.x, g3.y};
+    // four tokens per trip: all gradient rows first, then the hidden rows that are needed, then the FMAs
+    for (long long n0 = n_begin; n0 < n_end; n0 += 4) {
+      uint4 gv[4], hv[4];
+      bool need[4];
 #pragma unroll
-      for (int e = 0; e < DG_EXPERTS; ++e)
+      for (int j = 0; j < 4; ++j) {
+        const long long n = n0 + j;
+        gv[j] = make_uint4(0, 0, 0, 0);
+        if (n < n_end) gv[j] = __ldg(reinterpret_cast<const uint4*>(gl + n * ldg_ + e0));
+      }
 #pragma unroll
-        for (int i = 0; i < 8; ++i) acc[e][i] = fmaf(g[e], h[i], acc[e][i]);
+      for (int j = 0; j < 4; ++j) {
+        need[j] = (gv[j].x | gv[j].y | gv[j].z | gv[j].w) != 0u;  // skip rows whose eight gradients are +0
+        hv[j] = make_uint4(0, 0, 0, 0);
+        if (need[j]) hv[j] = __ldg(reinterpret_cast<const uint4*>(hidden + (n0 + j) * D + col0));
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (!need[j]) continue;
+        const float2 h0 = unpack_bf16x2(hv[j].x), h1 = unpack_bf16x2(hv[j].y), h2 = unpack_bf16x2(hv[j].z),
+                     h3 = unpack_bf16x2(hv[j].w);
+        const float h[8] = {h0.x, h0.y, h1.x, h1.y, h2.x, h2.y, h3.x, h3.y};
+        const float2 g0 = unpack_bf16x2(gv[j].x), g1 = unpack_bf16x2(gv[j].y), g2 = unpack_bf16x2(gv[j].z),
+                     g3 = unpack_bf16x2(gv[j].w);
+        const float g[8] = {g0.x, g0.y, g1.x, g1.y, g2.x, g2.y, g3.x, g3.y};
+#pragma unroll
+        for (int e = 0; e < DG_EXPERTS; ++e)
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[e][i] = fmaf(g[e], h[i], acc[e][i]);
+      }
     }
     float* out = partial + (static_cast<long long>(blockIdx.x) * ldg_ + e0) * D + col0;
 #pragma unroll
