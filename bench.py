@@ -331,7 +331,11 @@ def main():
             "clocks": clocks,
             "roofline": {
                 "bound": "tensor", "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
-                "frac": (achieved / peaks["tflops"]) if achieved else None, "traffic": None,
+                "frac": (achieved / peaks["tflops"]) if achieved else None,
+                # dram__bytes_read.sum + dram__bytes_write.sum of the largest grouped-GEMM launch of a step
+                # (up-projection + GLU of the routed experts: 134.4 MB + 350.4 MB against 536 MB algorithmic),
+                # from the ncu capture summarised in profiles/gemm_up_glu_pair_config2_ncu_full.md
+                "traffic": 484.8e6 if world == 1 else None,
                 "kernel": "ffm_gemm_kernel (tcgen05 grouped GEMM, all instantiations)",
                 "peak_source": f"{peaks['source']} sustained cuBLAS bf16 (burst {peaks['tflops_burst']})",
                 "frac_of_burst": (achieved / peaks["tflops_burst"]) if achieved else None,

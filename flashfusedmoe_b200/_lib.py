@@ -31,8 +31,10 @@ SIGNATURES = {
     "ffm_set_gemm_cta_pair": (c_int, [c_int]),
     "ffm_route_workspace_bytes": (c_size_t, [c_int64, c_int, c_int]),
     "ffm_route_forward": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_float,
-                                  c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                  c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                   c_int64, c_void_p, c_void_p, c_size_t, c_void_p, c_void_p]),
+    "ffm_route_apply_capacity": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int,
+                                         c_int, c_void_p, c_void_p]),
     "ffm_group_rows": (c_int, [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
                                c_void_p, c_size_t, c_void_p, c_void_p]),
     "ffm_group_rows_static": (c_int, [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,

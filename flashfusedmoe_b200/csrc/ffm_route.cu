@@ -73,11 +73,207 @@ __device__ __forceinline__ float dot8(const uint4& h, const uint4& w, float acc)
   return acc;
 }
 
+struct RouteOpts {
+  int gating;
+  float weight_scale;
+  int pre_softmax;  // softmax gating: probabilities over all experts before selection (DeepSeek-V3 style)
+  int n_group;      // > 0: group-limited selection over n_group contiguous expert groups
+  int topk_group;   // groups kept per token
+};
+
+// Warp arg-max of (value, expert) pairs: greater value wins, equal values go to the lower expert index.
+__device__ __forceinline__ void warp_argmax(float& best, int& best_e) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+    if (ov > best || (ov == best && oe < best_e)) {
+      best = ov;
+      best_e = oe;
+    }
+  }
+}
+
+// Scoring, selection, weights and statistics of one token whose bf16-rounded logits are spread over the warp:
+// lane holds expert g * 32 + lane for NG > 1 (GW == 32), expert lane % GW for NG == 1 (lanes >= GW replicate).
+template <int GW, int NG>
+__device__ __forceinline__ void route_token(const float (&logit)[NG], long long n, int lane, int E, int top_k,
+                                            const RouteOpts& o, const float* __restrict__ bias,
+                                            bf16* __restrict__ logits_out, float* __restrict__ topk_w,
+                                            int32_t* __restrict__ topk_idx, float* __restrict__ lse_out,
+                                            float (&mass)[NG], int (&cnt)[NG], float& zsum) {
+  const bool holder_lane = (NG > 1) || (lane < GW);
+  const int lane_e = (NG > 1) ? lane : (lane % GW);
+
+  // logsumexp over all experts (z-loss, and the normaliser of pre-softmax scoring)
+  float lmax = -INFINITY;
+#pragma unroll
+  for (int g = 0; g < NG; ++g) {
+    const int e = g * GW + lane_e;
+    if (holder_lane && e < E) {
+      lmax = fmaxf(lmax, logit[g]);
+      if (logits_out != nullptr) logits_out[n * E + e] = __float2bfloat16_rn(logit[g]);
+    }
+  }
+#pragma unroll
+  for (int s = 16; s > 0; s >>= 1) lmax = fmaxf(lmax, __shfl_xor_sync(0xffffffffu, lmax, s));
+  float esum = 0.0f;
+#pragma unroll
+  for (int g = 0; g < NG; ++g) {
+    const int e = g * GW + lane_e;
+    if (holder_lane && e < E) esum += __expf(logit[g] - lmax);
+  }
+  esum = warp_sum(esum);
+  const float lse = lmax + __logf(esum);
+  if (lane == 0) {
+    lse_out[n] = lse;
+    zsum += lse * lse;
+  }
+
+  float sel[NG];  // value used for selection
+  float val[NG];  // unbiased value that becomes the weight (logit, probability or sigmoid score)
+#pragma unroll
+  for (int g = 0; g < NG; ++g) {
+    const int e = g * GW + lane_e;
+    const bool valid = holder_lane && e < E;
+    const float lg = logit[g];
+    float v;
+    if (o.gating == FFM_GATING_SIGMOID) {
+      v = sigmoidf_(lg);
+    } else if (o.pre_softmax) {
+      v = __expf(lg - lse);
+    } else {
+      v = lg;
+    }
+    float sv = v;
+    if (bias != nullptr && valid) sv = v + bias[e];
+    val[g] = valid ? v : 0.0f;
+    sel[g] = valid ? sv : -INFINITY;
+  }
+  if (o.gating == FFM_GATING_SIGMOID) {
+#pragma unroll
+    for (int g = 0; g < NG; ++g) mass[g] += val[g];
+  }
+
+  // ---- group-limited selection: keep the topk_group groups with the best sum of their top scores ----
+  if (o.n_group > 0) {
+    const int epg = E / o.n_group;
+    const int per_group = top_k / o.topk_group;
+    const bool use_sum = per_group > 1 && per_group <= epg;
+    const int rounds = use_sum ? per_group : 1;
+    float my_gscore = -INFINITY;  // lane gi holds the score of group gi
+    for (int gi = 0; gi < o.n_group; ++gi) {
+      float tmp[NG];
+#pragma unroll
+      for (int g = 0; g < NG; ++g) {
+        const int e = g * GW + lane_e;
+        tmp[g] = (e / epg == gi) ? sel[g] : -INFINITY;
+      }
+      float score = 0.0f;
+      for (int r = 0; r < rounds; ++r) {
+        float best = -INFINITY;
+        int best_e = 0x7fffffff;
+#pragma unroll
+        for (int g = 0; g < NG; ++g) {
+          if (tmp[g] > best) {
+            best = tmp[g];
+            best_e = g * GW + lane_e;
+          }
+        }
+        warp_argmax(best, best_e);
+        score = (r == 0) ? best : score + best;
+#pragma unroll
+        for (int g = 0; g < NG; ++g) {
+          if (holder_lane && g * GW + lane_e == best_e) tmp[g] = -INFINITY;
+        }
+      }
+      if (lane == gi) my_gscore = score;
+    }
+    unsigned keep = 0u;
+    float gs = (lane < o.n_group) ? my_gscore : -INFINITY;
+    for (int r = 0; r < o.topk_group; ++r) {
+      float best = gs;
+      int best_l = (gs == -INFINITY) ? 0x7fffffff : lane;
+      warp_argmax(best, best_l);
+      if (best_l < 32) keep |= 1u << best_l;
+      if (lane == best_l) gs = -INFINITY;
+    }
+#pragma unroll
+    for (int g = 0; g < NG; ++g) {
+      const int e = g * GW + lane_e;
+      if (!((keep >> ((e / epg) & 31)) & 1u)) sel[g] = -INFINITY;
+    }
+  }
+
+  // ---- top-k by iterative argmax, lowest index wins ties ----
+  float my_val = 0.0f;
+  int my_idx = 0;
+  for (int j = 0; j < top_k; ++j) {
+    float best = -INFINITY;
+    int best_e = 0x7fffffff;
+#pragma unroll
+    for (int g = 0; g < NG; ++g) {
+      if (sel[g] > best) {
+        best = sel[g];
+        best_e = g * GW + lane_e;
+      }
+    }
+    warp_argmax(best, best_e);
+    // the holder of best_e publishes the unbiased value and retires the expert
+    float v_pub = 0.0f;
+#pragma unroll
+    for (int g = 0; g < NG; ++g) {
+      if (holder_lane && g * GW + lane_e == best_e) {
+        v_pub = val[g];
+        sel[g] = -INFINITY;
+      }
+    }
+    v_pub = __shfl_sync(0xffffffffu, v_pub, best_e & 31);
+    if (lane == j) {
+      my_val = v_pub;
+      my_idx = best_e;
+    }
+  }
+
+  // ---- weights over the k selected values (lanes 0..k-1) ----
+  float w;
+  if (o.gating == FFM_GATING_SOFTMAX && !o.pre_softmax) {
+    float m = (lane < top_k) ? my_val : -INFINITY;
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, s));
+    const float ex = (lane < top_k) ? __expf(my_val - m) : 0.0f;
+    const float den = warp_sum(ex);
+    w = ex / den;
+  } else {
+    const float sc = (lane < top_k) ? my_val : 0.0f;
+    const float den = warp_sum(sc) + 1e-6f;
+    w = sc / den;
+  }
+  w *= o.weight_scale;
+  if (lane < top_k) {
+    topk_w[n * top_k + lane] = w;
+    topk_idx[n * top_k + lane] = my_idx;
+  }
+  // ---- per-warp statistics: lane (e % 32) owns expert e ----
+  for (int j = 0; j < top_k; ++j) {
+    const int ej = __shfl_sync(0xffffffffu, my_idx, j);
+    const float wj = __shfl_sync(0xffffffffu, w, j);
+    const int own_lane = (NG > 1) ? (ej & 31) : ej;
+#pragma unroll
+    for (int g = 0; g < NG; ++g) {
+      if (lane == own_lane && g == ((NG > 1) ? (ej >> 5) : 0)) {
+        cnt[g] += 1;
+        if (o.gating == FFM_GATING_SOFTMAX) mass[g] += wj;
+      }
+    }
+  }
+}
+
 // Expert e = g * 32 + lane for NG > 1 (GW == 32); e = lane % GW for NG == 1.
 template <int GW, int NG>
 __global__ void __launch_bounds__(ROUTE_THREADS)
 route_gate_topk(const bf16* __restrict__ hidden, const bf16* __restrict__ gate_w, const float* __restrict__ bias,
-                long long N, int D, int E, int top_k, int gating, float weight_scale, int tokens_per_block,
+                long long N, int D, int E, int top_k, RouteOpts opts, int tokens_per_block,
                 bf16* __restrict__ logits_out, float* __restrict__ topk_w, int32_t* __restrict__ topk_idx,
                 float* __restrict__ lse_out, int32_t* __restrict__ block_hist, float* __restrict__ block_mass,
                 float* __restrict__ block_z) {
@@ -107,7 +303,7 @@ route_gate_topk(const bf16* __restrict__ hidden, const bf16* __restrict__ gate_w
     const uint4* h1p = reinterpret_cast<const uint4*>(hidden + (has1 ? t0 + 1 : t0) * D);
 
     // ---- gate GEMM: logit[tk][g] for expert g * 32 + lane (or lane % GW) ----
-    float logit[TPW][NG];
+    float logit0[NG], logit1[NG];
 #pragma unroll
     for (int g = 0; g < NG; ++g) {
       float acc0[GW], acc1[GW];
@@ -133,128 +329,14 @@ route_gate_topk(const bf16* __restrict__ hidden, const bf16* __restrict__ gate_w
       }
       transpose_reduce<GW>(acc0, lane);
       transpose_reduce<GW>(acc1, lane);
-      logit[0][g] = bf16_round(acc0[0]);
-      logit[1][g] = bf16_round(acc1[0]);
+      logit0[g] = bf16_round(acc0[0]);
+      logit1[g] = bf16_round(acc1[0]);
     }
 
-#pragma unroll
-    for (int tk = 0; tk < TPW; ++tk) {
-      if (tk == 1 && !has1) break;
-      const long long n = t0 + tk;
-      // expert owned by this lane in group g, and whether this lane is the canonical holder
-      // (for GW < 32 the logits are replicated 32 / GW times; only lanes < GW act as holders)
-      const bool holder_lane = (NG > 1) || (lane < GW);
-
-      float sel[NG];   // value used for selection
-      float val[NG];   // unbiased value that becomes the weight (logit or sigmoid score)
-      float lmax = -INFINITY;
-#pragma unroll
-      for (int g = 0; g < NG; ++g) {
-        const int e = g * GW + (NG > 1 ? lane : (lane % GW));
-        const bool valid = holder_lane && e < E;
-        const float lg = logit[tk][g];
-        if (valid && logits_out != nullptr) logits_out[n * E + e] = __float2bfloat16_rn(lg);
-        float v = (gating == FFM_GATING_SIGMOID) ? sigmoidf_(lg) : lg;
-        float s = v;
-        if (bias != nullptr && valid) s = v + bias[e];
-        val[g] = valid ? v : 0.0f;
-        sel[g] = valid ? s : -INFINITY;
-        if (valid) lmax = fmaxf(lmax, lg);
-      }
-      // logsumexp over all experts (z-loss)
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) lmax = fmaxf(lmax, __shfl_xor_sync(0xffffffffu, lmax, o));
-      float esum = 0.0f;
-#pragma unroll
-      for (int g = 0; g < NG; ++g) {
-        const int e = g * GW + (NG > 1 ? lane : (lane % GW));
-        if (holder_lane && e < E) esum += __expf(logit[tk][g] - lmax);
-      }
-      esum = warp_sum(esum);
-      const float lse = lmax + __logf(esum);
-      if (lane == 0) {
-        lse_out[n] = lse;
-        zsum += lse * lse;
-      }
-      if (gating == FFM_GATING_SIGMOID) {
-#pragma unroll
-        for (int g = 0; g < NG; ++g) mass[g] += val[g];
-      }
-
-      // ---- top-k by iterative argmax, lowest index wins ties ----
-      float my_val = 0.0f;
-      int my_idx = 0;
-      for (int j = 0; j < top_k; ++j) {
-        float best = -INFINITY;
-        int best_e = 0x7fffffff;
-#pragma unroll
-        for (int g = 0; g < NG; ++g) {
-          const int e = g * GW + (NG > 1 ? lane : (lane % GW));
-          if (sel[g] > best) {
-            best = sel[g];
-            best_e = e;
-          }
-        }
-        if (best == -INFINITY) best_e = 0x7fffffff;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-          const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-          const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
-          if (ov > best || (ov == best && oe < best_e)) {
-            best = ov;
-            best_e = oe;
-          }
-        }
-        // the holder of best_e publishes the unbiased value and retires the expert
-        float v_pub = 0.0f;
-#pragma unroll
-        for (int g = 0; g < NG; ++g) {
-          const int e = g * GW + (NG > 1 ? lane : (lane % GW));
-          if (holder_lane && e == best_e) {
-            v_pub = val[g];
-            sel[g] = -INFINITY;
-          }
-        }
-        const int holder = (NG > 1) ? (best_e & 31) : best_e;
-        v_pub = __shfl_sync(0xffffffffu, v_pub, holder & 31);
-        if (lane == j) {
-          my_val = v_pub;
-          my_idx = best_e;
-        }
-      }
-
-      // ---- weights over the k selected values (lanes 0..k-1) ----
-      float w;
-      if (gating == FFM_GATING_SOFTMAX) {
-        float m = (lane < top_k) ? my_val : -INFINITY;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-        const float ex = (lane < top_k) ? __expf(my_val - m) : 0.0f;
-        const float den = warp_sum(ex);
-        w = ex / den;
-      } else {
-        const float sc = (lane < top_k) ? my_val : 0.0f;
-        const float den = warp_sum(sc) + 1e-6f;
-        w = sc / den;
-      }
-      w *= weight_scale;
-      if (lane < top_k) {
-        topk_w[n * top_k + lane] = w;
-        topk_idx[n * top_k + lane] = my_idx;
-      }
-      // ---- per-warp statistics: lane (e % 32) owns expert e ----
-      for (int j = 0; j < top_k; ++j) {
-        const int ej = __shfl_sync(0xffffffffu, my_idx, j);
-        const float wj = __shfl_sync(0xffffffffu, w, j);
-        const int own_lane = (NG > 1) ? (ej & 31) : ej;
-#pragma unroll
-        for (int g = 0; g < NG; ++g) {
-          if (lane == own_lane && g == ((NG > 1) ? (ej >> 5) : 0)) {
-            cnt[g] += 1;
-            if (gating == FFM_GATING_SOFTMAX) mass[g] += wj;
-          }
-        }
-      }
+    route_token<GW, NG>(logit0, t0, lane, E, top_k, opts, bias, logits_out, topk_w, topk_idx, lse_out, mass, cnt, zsum);
+    if (has1) {
+      route_token<GW, NG>(logit1, t0 + 1, lane, E, top_k, opts, bias, logits_out, topk_w, topk_idx, lse_out, mass, cnt,
+                          zsum);
     }
   }
 
@@ -467,11 +549,41 @@ RouteWorkspace carve_workspace(void* base, int blocks, int E) {
 
 template <int GW, int NG>
 void launch_route(int blocks, cudaStream_t s, const bf16* hidden, const bf16* gate_w, const float* bias, long long N,
-                  int D, int E, int top_k, int gating, float weight_scale, int tpb, bf16* logits, float* topk_w,
+                  int D, int E, int top_k, const RouteOpts& opts, int tpb, bf16* logits, float* topk_w,
                   int32_t* topk_idx, float* lse, const RouteWorkspace& w) {
-  route_gate_topk<GW, NG><<<blocks, ROUTE_THREADS, 0, s>>>(hidden, gate_w, bias, N, D, E, top_k, gating, weight_scale,
-                                                           tpb, logits, topk_w, topk_idx, lse, w.block_hist,
-                                                           w.block_mass, w.block_z);
+  route_gate_topk<GW, NG><<<blocks, ROUTE_THREADS, 0, s>>>(hidden, gate_w, bias, N, D, E, top_k, opts, tpb, logits,
+                                                           topk_w, topk_idx, lse, w.block_hist, w.block_mass,
+                                                           w.block_z);
+}
+
+// Expert capacity: a routed slot whose rank inside its expert segment is >= capacity is dropped. One thread
+// per token: dropped slots get weight 0 and their grouped row becomes a padding row (src = -1, so every later
+// kernel sees zeros there); the kept weights are renormalised by their sum, or left at zero when nothing is kept.
+__global__ void __launch_bounds__(ROUTE_THREADS)
+route_capacity_kernel(float* __restrict__ topk_w, const int32_t* __restrict__ topk_idx, const int32_t* __restrict__ pos,
+                      int32_t* __restrict__ src, const int32_t* __restrict__ tile_start, long long N, int top_k, int E,
+                      int capacity, int32_t* __restrict__ dropped) {
+  const long long n = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (n >= N) return;
+  float sum = 0.0f;
+  int ndrop = 0;
+  for (int j = 0; j < top_k; ++j) {
+    const long long i = n * top_k + j;
+    const int e = topk_idx[i];
+    if (e < 0 || e >= E) continue;
+    const int r = pos[i] - tile_start[e] * 128;
+    float w = topk_w[i];
+    if (r >= capacity) {
+      w = 0.0f;
+      src[pos[i]] = -1;
+      ++ndrop;
+    }
+    topk_w[i] = w;
+    sum += w;
+  }
+  const float denom = sum + (sum > 0.0f ? 0.0f : 1.0f);
+  for (int j = 0; j < top_k; ++j) topk_w[n * top_k + j] /= denom;
+  if (ndrop > 0) atomicAdd(dropped, ndrop);
 }
 
 // ---- scratch for the allocation-free entry point ---------------------------------------------
@@ -523,7 +635,8 @@ extern "C" size_t ffm_route_workspace_bytes(int64_t N, int E, int top_k) {
 }
 
 extern "C" int ffm_route_forward(const void* hidden, const void* gate_w, const float* expert_bias, int64_t N, int D,
-                                 int E, int top_k, int gating, float weight_scale, void* logits, float* topk_w,
+                                 int E, int top_k, int gating, float weight_scale, int pre_softmax, int n_group,
+                                 int topk_group, void* logits, float* topk_w,
                                  int32_t* topk_idx, float* lse, int32_t* counts, int32_t* tile_start, int32_t* pos,
                                  int32_t* src, int64_t rows_cap, float* stats, void* workspace,
                                  size_t workspace_bytes, int32_t* status, ffm_stream_t stream) {
@@ -533,7 +646,15 @@ extern "C" int ffm_route_forward(const void* hidden, const void* gate_w, const f
   if (N < 0 || D <= 0 || E < 1 || top_k < 1) return FFM_ERR_BAD_ARG;
   if (gating != FFM_GATING_SOFTMAX && gating != FFM_GATING_SIGMOID) return FFM_ERR_BAD_ARG;
   if (D % 8 != 0 || E > MAX_E || top_k > E || top_k > 32) return FFM_ERR_UNSUPPORTED;
+  if (n_group < 0 || (n_group > 0 && (topk_group < 1 || topk_group > n_group))) return FFM_ERR_BAD_ARG;
+  if (n_group > 32 || (n_group > 0 && E % n_group != 0)) return FFM_ERR_UNSUPPORTED;
   if (rows_cap < ffm_rows_capacity(N * top_k, E)) return FFM_ERR_BAD_ARG;
+  RouteOpts opts;
+  opts.gating = gating;
+  opts.weight_scale = weight_scale;
+  opts.pre_softmax = (gating == FFM_GATING_SOFTMAX && pre_softmax) ? 1 : 0;
+  opts.n_group = n_group;
+  opts.topk_group = topk_group;
   if (workspace_bytes < ffm_route_workspace_bytes(N, E, top_k)) return FFM_ERR_WORKSPACE;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (cudaMemsetAsync(src, 0xFF, static_cast<size_t>(rows_cap) * 4, s) != cudaSuccess) return FFM_ERR_LAUNCH;
@@ -543,8 +664,8 @@ extern "C" int ffm_route_forward(const void* hidden, const void* gate_w, const f
   const bf16* gw = static_cast<const bf16*>(gate_w);
   bf16* lg = static_cast<bf16*>(logits);
 #define FFM_ROUTE_CASE(GW, NG)                                                                                 \
-  launch_route<GW, NG>(g.blocks, s, h, gw, expert_bias, N, D, E, top_k, gating, weight_scale, g.tokens_per_block, \
-                       lg, topk_w, topk_idx, lse, w)
+  launch_route<GW, NG>(g.blocks, s, h, gw, expert_bias, N, D, E, top_k, opts, g.tokens_per_block, lg, topk_w, \
+                       topk_idx, lse, w)
   if (E <= 8) {
     FFM_ROUTE_CASE(8, 1);
   } else if (E <= 16) {
@@ -610,5 +731,19 @@ extern "C" int ffm_group_rows_static(const int32_t* expert_ids, int64_t T, int E
                                          nullptr);
   route_rank<<<g.blocks, ROUTE_THREADS, 0, s>>>(expert_ids, T, E, g.tokens_per_block, block_off, tile_start, rows_cap,
                                                 pos, src, status);
+  return cudaGetLastError() == cudaSuccess ? FFM_OK : FFM_ERR_LAUNCH;
+}
+
+extern "C" int ffm_route_apply_capacity(float* topk_w, const int32_t* topk_idx, const int32_t* pos, int32_t* src,
+                                        const int32_t* tile_start, int64_t N, int top_k, int E, int capacity,
+                                        int32_t* dropped_count, ffm_stream_t stream) {
+  if (!topk_w || !topk_idx || !pos || !src || !tile_start || !dropped_count) return FFM_ERR_BAD_ARG;
+  if (N < 0 || top_k < 1 || E < 1 || capacity < 0) return FFM_ERR_BAD_ARG;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (cudaMemsetAsync(dropped_count, 0, 4, s) != cudaSuccess) return FFM_ERR_LAUNCH;
+  if (N == 0) return FFM_OK;
+  const int blocks = static_cast<int>((N + ROUTE_THREADS - 1) / ROUTE_THREADS);
+  route_capacity_kernel<<<blocks, ROUTE_THREADS, 0, s>>>(topk_w, topk_idx, pos, src, tile_start, N, top_k, E, capacity,
+                                                         dropped_count);
   return cudaGetLastError() == cudaSuccess ? FFM_OK : FFM_ERR_LAUNCH;
 }

@@ -112,6 +112,11 @@ class _Cfg:
     shared_activation: str = "swiglu"
     ep_group: object = None
     ep_full_input_grad: bool = False
+    pre_softmax: bool = False
+    n_group: int = 0
+    topk_group: int = 0
+    capacity: Optional[int] = None
+    input_jitter: float = 0.0
 
 
 def _to(t, dtype):
@@ -127,6 +132,17 @@ def _dense_ts(rows, device):
         t = torch.tensor([0, (rows + 127) // 128], dtype=torch.int32, device=device)
         _dense_tile_start[key] = t
     return t
+
+
+def _route(h, g, cfg, training):
+    """Routing kernels for one call. With input_jitter the logits see h * U(1 - j, 1 + j) in training, exactly as
+    the reference draws it (fused_moe.py:329-332); everything downstream uses the clean h."""
+    h_route = h
+    if cfg.input_jitter > 0.0 and training:
+        noise = torch.empty_like(h).uniform_(1.0 - cfg.input_jitter, 1.0 + cfg.input_jitter)
+        h_route = h * noise
+    return ops.route_forward(h_route, g, cfg.top_k, cfg.gating, cfg.expert_bias, cfg.weight_scale,
+                             pre_softmax=cfg.pre_softmax, n_group=cfg.n_group, topk_group=cfg.topk_group)
 
 
 def _loss_tensors(routing, N, E, cfg):
@@ -225,7 +241,12 @@ class _FusedMoEFunction(torch.autograd.Function):
         wd = _to(w_down, dtype)
         add = None if addend is None else _to(addend, dtype)
 
-        routing = ops.route_forward(h, g, k, cfg.gating, cfg.expert_bias, cfg.weight_scale)
+        routing = _route(h, g, cfg, hidden_states.requires_grad)
+        aux, z = _loss_tensors(routing, N, E, cfg)  # from the routing before any capacity dropping
+        if cfg.capacity is not None:
+            dropped = ops.route_apply_capacity(routing, cfg.capacity)
+        else:
+            dropped = torch.zeros(1, dtype=torch.int32, device=h.device)
         Xg = ops.permute_rows(h, routing.src, routing.rows_cap, k)
         need_grad = any(ctx.needs_input_grad[:5])
         keep = need_grad and not cfg.recompute
@@ -233,7 +254,6 @@ class _FusedMoEFunction(torch.autograd.Function):
                                         cfg.activation, want_preact=keep)
         Y = ops.grouped_gemm(act, wd, _lib.B_KMAJOR, E, routing.tile_start, H, D)
         out = ops.combine_forward(Y, routing.pos, routing.topk_w, N, k, addend=add)
-        aux, z = _loss_tensors(routing, N, E, cfg)
 
         ctx.set_materialize_grads(False)
         ctx.cfg = cfg
@@ -248,11 +268,11 @@ class _FusedMoEFunction(torch.autograd.Function):
         ctx.kept = keep
         ctx.save_for_backward(*saved)
         counts = routing.counts
-        ctx.mark_non_differentiable(counts)
-        return out, aux, z, counts
+        ctx.mark_non_differentiable(counts, dropped)
+        return out, aux, z, counts, dropped
 
     @staticmethod
-    def backward(ctx, grad_out, grad_aux, grad_z, _grad_counts):
+    def backward(ctx, grad_out, grad_aux, grad_z, _grad_counts, _grad_dropped):
         cfg = ctx.cfg
         N, D, E, H = ctx.shape
         k = cfg.top_k
@@ -329,7 +349,7 @@ class _FusedMoEEPFunction(torch.autograd.Function):
         wd = _to(w_down, dtype)
         need_grad = any(ctx.needs_input_grad[:9])
 
-        routing = ops.route_forward(h, g, k, cfg.gating, cfg.expert_bias, cfg.weight_scale)
+        routing = _route(h, g, cfg, hidden_states.requires_grad)
 
         # shared expert on a side stream: queued before the host waits for the split sizes
         shared = None
@@ -401,7 +421,7 @@ class _FusedMoEEPFunction(torch.autograd.Function):
                               (hidden_states, gate_weight, w_up, w_down, sw_gate, sw_up, sw_down, lw_down, lw_up))
         ctx.routing_meta = (routing.rows_cap,)
         tensors = dict(h=h, g=g, wu=wu, wd=wd, topk_w=routing.topk_w, topk_idx=routing.topk_idx,
-                       logits=routing.logits, lse=routing.lse, counts=routing.counts, src_c=src_c,
+                       logits=routing.logits, lse=routing.lse, counts=routing.counts, src_c=src_c, cpos=cpos,
                        returned=returned, ts_l=ts_l, src_l=src_l, pos_l=pos_l, Xg=Xg, act=act, pre=pre)
         if has_shared:
             tensors.update(s_act=shared[1], s_pre=shared[2], swg=shared[3], swu=shared[4], swd=shared[5])
@@ -410,11 +430,12 @@ class _FusedMoEEPFunction(torch.autograd.Function):
         ctx.names = [n for n, t in tensors.items() if t is not None]
         ctx.save_for_backward(*[tensors[n] for n in ctx.names])
         counts = routing.counts
-        ctx.mark_non_differentiable(counts)
-        return out, aux, z, counts
+        dropped = torch.zeros(1, dtype=torch.int32, device=h.device)
+        ctx.mark_non_differentiable(counts, dropped)
+        return out, aux, z, counts, dropped
 
     @staticmethod
-    def backward(ctx, grad_out, grad_aux, grad_z, _grad_counts):
+    def backward(ctx, grad_out, grad_aux, grad_z, _grad_counts, _grad_dropped):
         cfg = ctx.cfg
         group = cfg.ep_group
         N, D, E, El, H, k, M, ep, rows_l = ctx.dims
@@ -477,6 +498,13 @@ class _FusedMoEEPFunction(torch.autograd.Function):
             gU = ops.glu_backward(d_act, t["pre"], t["ts_l"], El, cfg.activation)
             d_wd = ops.grouped_gemm_wgrad(gYg, t["act"], El, t["ts_l"], scale=inv_ep)
             d_wu = ops.grouped_gemm_wgrad(gU, t["Xg"], El, t["ts_l"], scale=inv_ep)
+            if cfg.ep_full_input_grad:
+                # opt-in: the expert input gradient the reference leaves out (fused_moe.py:1001-1005) travels back
+                # through a reverse dispatch exchange and is summed over each token's k slots
+                dXg = ops.grouped_gemm(gU, wu, _lib.B_NMAJOR, El, t["ts_l"], 2 * H, D)
+                dx_recv = ops.combine_forward(dXg, t["pos_l"], None, M, 1)
+                if has_latent:
+                    dx_recv = ops.grouped_gemm(dx_recv, t["lwu"], _lib.B_NMAJOR, 1, None, D, L)
         else:
             d_wd = torch.zeros_like(wd)
             d_wu = torch.zeros_like(wu)
@@ -490,6 +518,14 @@ class _FusedMoEEPFunction(torch.autograd.Function):
             else:
                 d_lwd = torch.zeros_like(t["lwd"])
 
+        if cfg.ep_full_input_grad:
+            W = L if has_latent else D
+            back = dx_recv if M > 0 else h.new_empty(0, W)
+            d_send = all_to_all_rows(back, send_splits, recv_splits, group)       # [T, W], send order
+            d_disp = ops.combine_forward(d_send, t["cpos"], None, N, k)            # sum over the k slots
+            if has_latent:
+                d_disp = ops.grouped_gemm(d_disp, t["lwd"], _lib.B_NMAJOR, 1, None, L, D)
+            dH = dH + d_disp
         s_grads = (None, None, None)
         if has_shared:
             torch.cuda.current_stream().wait_event(shared_done)
@@ -552,6 +588,7 @@ def fused_moe(
     pre_softmax=False,
     input_jitter=0.0,
     expert_bias=None,
+    ep_full_input_grad=False,
     _addend=None,
 ):
     """Fused MoE forward; returns (output [N, D], losses dict). Arguments as in the reference
@@ -567,31 +604,35 @@ def fused_moe(
         assert 1 <= top_k <= gate_weight.shape[0], f"top_k must be in [1, {gate_weight.shape[0]}], got {top_k}"
         assert activation in ("swiglu", "geglu", "relu_squared"), f"Unknown activation: {activation}"
         assert gating in ("softmax", "sigmoid"), f"Unknown gating: {gating}"
-    if capacity_factor is not None:
-        raise NotImplementedError("capacity_factor (token dropping) is not implemented in flashfusedmoe_b200 yet")
-    if n_group is not None or topk_group is not None or pre_softmax:
-        raise NotImplementedError("group-limited and pre-softmax routing are not implemented in flashfusedmoe_b200 yet")
-    if input_jitter and input_jitter > 0.0:
-        raise NotImplementedError("input_jitter is not implemented in flashfusedmoe_b200 yet")
     if not hidden_states.is_cuda:
         raise RuntimeError("flashfusedmoe_b200 runs on CUDA (sm_100a) tensors only; there is no CPU path")
 
     N, D = hidden_states.shape
     E = gate_weight.shape[0]
     dtype = _require_bf16(_get_compute_dtype(hidden_states.dtype))
+    use_groups = n_group is not None and topk_group is not None
+    if use_groups:
+        assert E % n_group == 0, f"E ({E}) must be divisible by n_group ({n_group})"
+    capacity = None
+    if capacity_factor is not None and group is None:
+        capacity = max(int((N / E) * capacity_factor), top_k)  # fused_moe.py:352-353
     cfg = _Cfg(top_k=top_k, activation=activation, gating=gating, aux_loss_coeff=float(aux_loss_coeff),
                z_loss_coeff=float(z_loss_coeff), recompute=bool(recompute_activations), expert_bias=expert_bias,
                weight_scale=1.0 if scoring_factor is None else float(scoring_factor) / top_k,
-               aux_grad=_AUX_LOSS_GRAD, ep_group=group)
+               aux_grad=_AUX_LOSS_GRAD, ep_group=group, ep_full_input_grad=bool(ep_full_input_grad),
+               pre_softmax=bool(pre_softmax) and gating == "softmax", n_group=int(n_group) if use_groups else 0,
+               topk_group=int(topk_group) if use_groups else 0, capacity=capacity,
+               input_jitter=float(input_jitter or 0.0))
 
     if group is not None:
         sw = shared_expert_weights if shared_expert_weights is not None else (None, None, None)
         lw = latent_weights if latent_weights is not None else (None, None)
-        out, aux, z, counts = _FusedMoEEPFunction.apply(hidden_states, gate_weight, w_up, w_down, sw[0], sw[1],
-                                                        sw[2], lw[0], lw[1], cfg, dtype)
+        out, aux, z, counts, dropped = _FusedMoEEPFunction.apply(hidden_states, gate_weight, w_up, w_down, sw[0],
+                                                                 sw[1], sw[2], lw[0], lw[1], cfg, dtype)
     else:
-        out, aux, z, counts = _FusedMoEFunction.apply(hidden_states, gate_weight, w_up, w_down, _addend, cfg, dtype)
-        if max_tokens_per_expert is not None and not allow_dropped_tokens:
+        out, aux, z, counts, dropped = _FusedMoEFunction.apply(hidden_states, gate_weight, w_up, w_down, _addend, cfg,
+                                                               dtype)
+        if max_tokens_per_expert is not None and not allow_dropped_tokens and capacity is None:
             actual_max = int(counts.max().item())
             if actual_max > max_tokens_per_expert:
                 raise RuntimeError(
@@ -608,4 +649,7 @@ def fused_moe(
         losses["z_loss"] = z
     if return_metrics:
         _metrics(losses, counts, N, top_k, capacity_factor, E)
+        if capacity_factor is not None:
+            losses["dropped_token_count"] = dropped.reshape(()).to(torch.int64)
+            losses["dropped_token_fraction"] = dropped.reshape(()).float() / (N * top_k)
     return out, losses

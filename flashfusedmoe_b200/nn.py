@@ -39,12 +39,14 @@ class MoELayer(nn.Module):
 
     `shared_ffn_dim` (extension, default None = ffn_dim as in the reference, nn.py:103-104) sets the width of
     the single shared GLU FFN, e.g. num_shared_experts * ffn_dim for models whose shared experts are merged.
+    `ep_full_input_grad` (extension, default False = the reference's contract) adds the expert input gradient to
+    the expert-parallel backward through a reverse dispatch exchange.
     """
 
     def __init__(self, d_model, ffn_dim, num_experts, top_k=2, activation="swiglu", gating="softmax",
                  num_shared_experts=0, latent_dim=None, capacity_factor=None, max_tokens_per_expert=None,
                  allow_dropped_tokens=True, aux_loss_coeff=0.0, z_loss_coeff=0.0, recompute_activations=False,
-                 shared_ffn_dim=None):
+                 shared_ffn_dim=None, ep_full_input_grad=False):
         super().__init__()
         self.d_model = d_model
         self.ffn_dim = ffn_dim
@@ -59,6 +61,7 @@ class MoELayer(nn.Module):
         self.z_loss_coeff = z_loss_coeff
         self.capacity_factor = capacity_factor
         self.recompute_activations = recompute_activations
+        self.ep_full_input_grad = ep_full_input_grad
         self._ep_group = None
         self._ep_size = 1
 
@@ -109,7 +112,8 @@ class MoELayer(nn.Module):
             aux_loss_coeff=self.aux_loss_coeff, z_loss_coeff=self.z_loss_coeff,
             recompute_activations=self.recompute_activations,
             max_tokens_per_expert=self.max_tokens_per_expert, allow_dropped_tokens=self.allow_dropped_tokens,
-            shared_expert_weights=shared_weights, latent_weights=latent_weights, _addend=addend)
+            shared_expert_weights=shared_weights, latent_weights=latent_weights,
+            ep_full_input_grad=self.ep_full_input_grad, _addend=addend)
         return out.reshape(*leading, D), losses
 
     def shard_experts(self, ep_group, ep_backend="nccl"):

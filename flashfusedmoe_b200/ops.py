@@ -128,7 +128,8 @@ class Routing:
     num_experts: int
 
 
-def route_forward(hidden, gate_w, top_k, gating="softmax", expert_bias=None, weight_scale=1.0):
+def route_forward(hidden, gate_w, top_k, gating="softmax", expert_bias=None, weight_scale=1.0, pre_softmax=False,
+                  n_group=0, topk_group=0):
     lib = _lib.load()
     _req(hidden, torch.bfloat16, "hidden")
     _req(gate_w, torch.bfloat16, "gate_w")
@@ -154,12 +155,27 @@ def route_forward(hidden, gate_w, top_k, gating="softmax", expert_bias=None, wei
     ws = _workspace(dev, ws_bytes, "route")
     with _Launch("route_forward", 3):
         rc = lib.ffm_route_forward(_ptr(hidden), _ptr(gate_w), _ptr(expert_bias), N, D, E, top_k,
-                                   _lib.GATING[gating], float(weight_scale), _ptr(r.logits), _ptr(r.topk_w),
+                                   _lib.GATING[gating], float(weight_scale), 1 if pre_softmax else 0, int(n_group or 0),
+                                   int(topk_group or 0), _ptr(r.logits), _ptr(r.topk_w),
                                    _ptr(r.topk_idx), _ptr(r.lse), _ptr(r.counts), _ptr(r.tile_start), _ptr(r.pos),
                                    _ptr(r.src), rows_cap, _ptr(r.stats), _ptr(ws), ws.numel(),
                                    _ptr(status_tensor(dev)), _stream())
     _lib.check(rc, "ffm_route_forward")
     return r
+
+
+def route_apply_capacity(r, capacity):
+    """Drop slots beyond `capacity` per expert in place (weights renormalised, rows turned into padding).
+    Returns the int32 [1] count of dropped slots."""
+    lib = _lib.load()
+    dropped = torch.empty(1, dtype=torch.int32, device=r.topk_w.device)
+    N = r.topk_w.shape[0]
+    with _Launch("route_capacity", 1):
+        rc = lib.ffm_route_apply_capacity(_ptr(r.topk_w), _ptr(r.topk_idx), _ptr(r.pos), _ptr(r.src),
+                                          _ptr(r.tile_start), N, r.top_k, r.num_experts, int(capacity), _ptr(dropped),
+                                          _stream())
+    _lib.check(rc, "ffm_route_apply_capacity")
+    return dropped
 
 
 def group_rows(expert_ids, num_experts):

@@ -89,6 +89,11 @@ int ffm_set_gemm_cta_pair(int enable);
  * bf16 GEMM output is. Selection uses logit (+ expert_bias) for softmax gating and sigmoid(logit)
  * (+ expert_bias) for sigmoid gating; weights always come from the unbiased values and are multiplied by
  * weight_scale (scoring_factor / top_k, or 1).
+ * pre_softmax != 0 (softmax gating): scores are the softmax probabilities over all experts, selection on
+ * probability (+ bias), weights = p / (sum p + 1e-6)                          (fused_moe.py:146-162).
+ * n_group > 0: group-limited selection (fused_moe.py:203-251): experts form n_group contiguous groups, a group's
+ * score is the sum of its top (top_k / topk_group) selection values (its maximum if that count is 1 or exceeds
+ * the group size), the topk_group best groups stay eligible. Limits: n_group <= 32, E % n_group == 0.
  *
  *   hidden [N, D] bf16, gate_w [E, D] bf16, expert_bias [E] f32 or NULL
  *   logits [N, E] bf16 out (may be NULL), topk_w [N, k] f32 out, topk_idx [N, k] int32 out, lse [N] f32 out
@@ -100,10 +105,19 @@ int ffm_set_gemm_cta_pair(int enable);
  * ------------------------------------------------------------------------------------------------- */
 size_t ffm_route_workspace_bytes(int64_t N, int E, int top_k);
 int ffm_route_forward(const void* hidden, const void* gate_w, const float* expert_bias, int64_t N, int D, int E,
-                      int top_k, int gating, float weight_scale, void* logits, float* topk_w, int32_t* topk_idx,
+                      int top_k, int gating, float weight_scale, int pre_softmax, int n_group, int topk_group,
+                      void* logits, float* topk_w, int32_t* topk_idx,
                       float* lse, int32_t* counts, int32_t* tile_start, int32_t* pos, int32_t* src,
                       int64_t rows_cap, float* stats, void* workspace, size_t workspace_bytes, int32_t* status,
                       ffm_stream_t stream);
+
+/* Expert capacity with token dropping (fused_moe.py:351-390): a slot whose rank inside its expert is >= capacity
+ * is dropped: its weight becomes 0, its grouped row a padding row (src = -1), and each token's kept weights are
+ * renormalised by their sum (left at zero when nothing is kept). Call after ffm_route_forward, before
+ * ffm_permute_rows. dropped_count [1] int32 out: number of dropped slots. */
+int ffm_route_apply_capacity(float* topk_w, const int32_t* topk_idx, const int32_t* pos, int32_t* src,
+                             const int32_t* tile_start, int64_t N, int top_k, int E, int capacity,
+                             int32_t* dropped_count, ffm_stream_t stream);
 
 /* Grouped-row map from given expert ids (no gate GEMM): used on the receiving side of expert parallelism,
  * where rows arrive already tagged with a local expert id. Replaces fused_moe.py:704-707.

@@ -54,26 +54,49 @@ def lowest_index_topk(sel, k):
     return torch.stack(cols, dim=1)
 
 
-def route(logits, gating, top_k, expert_bias=None, scoring_factor=None):
+def group_limited_mask(sel, top_k, n_group, topk_group):
+    """fused_moe.py:203-245 — eligibility mask [N, E]: the topk_group groups (of E / n_group contiguous experts)
+    with the best sum of their top (top_k // topk_group) selection values (the maximum when that count is 1 or
+    larger than the group) stay eligible. Ties between groups go to the lower group index."""
+    N, E = sel.shape
+    epg = E // n_group
+    grouped = sel.view(N, n_group, epg)
+    per_group = top_k // topk_group
+    if 1 < per_group <= epg:
+        gscore = grouped.topk(per_group, dim=-1).values.sum(dim=-1)
+    else:
+        gscore = grouped.max(dim=-1).values
+    gidx = lowest_index_topk(gscore, topk_group)
+    gmask = torch.zeros(N, n_group, dtype=torch.bool)
+    gmask.scatter_(1, gidx, True)
+    return gmask.unsqueeze(-1).expand(-1, -1, epg).reshape(N, E)
+
+
+def route(logits, gating, top_k, expert_bias=None, scoring_factor=None, pre_softmax=False, n_group=None,
+          topk_group=None):
     """Top-k weights and indices.
 
     Without bias: kernels/fused_topk.py:31-136 (the CUDA fast path, fused_moe.py:139-142).
     With expert_bias: fused_moe.py:165-179 (softmax) and :181-195 (sigmoid): selection on the biased values,
-    weights from the unbiased ones; ties resolved by the same lowest-index rule.
+    weights from the unbiased ones. pre_softmax: fused_moe.py:146-162. n_group / topk_group: :203-251.
+    Ties are resolved by the lowest-index rule everywhere.
     """
     lg = logits.float()
     if gating == "softmax":
-        sel = lg if expert_bias is None else lg + expert_bias.float().unsqueeze(0)
-        idx = lowest_index_topk(sel, top_k)
-        w = torch.softmax(lg.gather(1, idx), dim=-1)
+        val = torch.softmax(lg, dim=-1) if pre_softmax else lg
     elif gating == "sigmoid":
-        sc = torch.sigmoid(lg)
-        sel = sc if expert_bias is None else sc + expert_bias.float().unsqueeze(0)
-        idx = lowest_index_topk(sel, top_k)
-        ts = sc.gather(1, idx)
-        w = ts / (ts.sum(dim=-1, keepdim=True) + WEIGHT_EPS)
+        val = torch.sigmoid(lg)
     else:
         raise ValueError(f"Unknown gating: {gating}")
+    sel = val if expert_bias is None else val + expert_bias.float().unsqueeze(0)
+    if n_group is not None and topk_group is not None:
+        sel = sel.masked_fill(~group_limited_mask(sel, top_k, n_group, topk_group), float("-inf"))
+    idx = lowest_index_topk(sel, top_k)
+    picked = val.gather(1, idx)
+    if gating == "softmax" and not pre_softmax:
+        w = torch.softmax(picked, dim=-1)
+    else:
+        w = picked / (picked.sum(dim=-1, keepdim=True) + WEIGHT_EPS)
     if scoring_factor is not None:
         w = w * (scoring_factor / top_k)  # fused_moe.py:197-198
     return w, idx
@@ -187,7 +210,8 @@ def glu_backward(ga, x, activation, dtype):
 # ----------------------------------------------------------------------------------------------
 
 def fused_moe_forward(hidden, gate_w, w_up, w_down, top_k, activation="swiglu", gating="softmax",
-                      aux_loss_coeff=0.0, z_loss_coeff=0.0, dtype=None, expert_bias=None, scoring_factor=None):
+                      aux_loss_coeff=0.0, z_loss_coeff=0.0, dtype=None, expert_bias=None, scoring_factor=None,
+                      pre_softmax=False, n_group=None, topk_group=None, capacity_factor=None):
     """Returns a dict with the output, the losses and every intermediate the backward needs."""
     dtype = dtype or hidden.dtype
     h = hidden.to(dtype)
@@ -197,9 +221,21 @@ def fused_moe_forward(hidden, gate_w, w_up, w_down, top_k, activation="swiglu", 
     N, D = h.shape
     E = g.shape[0]
     logits = gate_logits(h, g, dtype)
-    topk_w, topk_idx = route(logits, gating, top_k, expert_bias, scoring_factor)
+    topk_w, topk_idx = route(logits, gating, top_k, expert_bias, scoring_factor, pre_softmax, n_group, topk_group)
+    ls = losses(logits, topk_w, topk_idx, gating, aux_loss_coeff, z_loss_coeff)  # before any dropping (:1160-1194)
     order, counts, starts = sort_metadata(topk_idx, E)
     T = N * top_k
+    keep = torch.ones(N, top_k)
+    if capacity_factor is not None:
+        # fused_moe.py:351-390: first-come capacity per expert, dropped weights zeroed, the rest renormalised
+        capacity = max(int((N / E) * capacity_factor), top_k)
+        rank_sorted = torch.arange(T) - starts[topk_idx.reshape(-1)[order]]
+        rank = torch.empty(T, dtype=torch.long)
+        rank[order] = rank_sorted
+        keep = (rank < capacity).view(N, top_k).float()
+        topk_w = topk_w * keep
+        wsum = topk_w.sum(dim=-1, keepdim=True)
+        topk_w = topk_w / (wsum + (1.0 - (wsum > 0).float()))
     tok = order // top_k                     # token of each sorted row
     xs = h[tok]                              # [T, D]   (fused_routing_scatter, moe_ops.py:53-106)
     up = torch.empty(T, wu.shape[1], dtype=dtype)
@@ -217,8 +253,7 @@ def fused_moe_forward(hidden, gate_w, w_up, w_down, top_k, activation="swiglu", 
     inv[order] = torch.arange(T)                                # sorted row of each flat slot
     gathered = down[inv].float() * flat_w.float().unsqueeze(-1)  # moe_ops.py:190-199
     out = gathered.view(N, top_k, D).sum(1).to(dtype)
-    ls = losses(logits, topk_w, topk_idx, gating, aux_loss_coeff, z_loss_coeff)
-    return dict(out=out, losses=ls, logits=logits, topk_w=topk_w, topk_idx=topk_idx, order=order, counts=counts,
+    return dict(out=out, losses=ls, keep=keep, logits=logits, topk_w=topk_w, topk_idx=topk_idx, order=order, counts=counts,
                 starts=starts, inv=inv, xs=xs, up=up, act=act, down=down, flat_w=flat_w,
                 h=h, g=g, wu=wu, wd=wd, dtype=dtype, activation=activation, gating=gating, top_k=top_k,
                 aux_loss_coeff=aux_loss_coeff, z_loss_coeff=z_loss_coeff)
@@ -245,7 +280,7 @@ def fused_moe_backward(fw, grad_out, grad_aux=1.0, grad_z=1.0, aux_loss_grad="an
     # routing-weight gradient, fused_moe.py:533-535
     gathered_down = fw["down"][inv]
     go_exp = go.unsqueeze(1).expand(-1, k, -1).reshape(T, D)
-    gw = (gathered_down.float() * go_exp.float()).sum(-1).view(N, k)
+    gw = (gathered_down.float() * go_exp.float()).sum(-1).view(N, k) * fw["keep"]  # dropped slots read a zero row
     # weighted scatter, moe_ops.py:258-288 (sorted rows)
     gyw = (go[tok].float() * fw["flat_w"][order].float().unsqueeze(-1)).to(dtype)
     d_act = torch.empty_like(fw["act"])

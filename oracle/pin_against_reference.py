@@ -77,11 +77,13 @@ def make_inputs(seed, N, D, E, F, dtype):
     return [t.to(dtype) for t in (h, g, wu, wd, go)]
 
 
-def run_reference(h, g, wu, wd, go, k, activation, gating, aux, z):
+def run_reference(h, g, wu, wd, go, k, activation, gating, aux, z, **extra):
     h, g, wu, wd = [t.clone().requires_grad_() for t in (h, g, wu, wd)]
+    kw = dict(allow_dropped_tokens=True, max_tokens_per_expert=h.shape[0] * k)
+    if "capacity_factor" in extra:
+        kw = dict(allow_dropped_tokens=True)
     out, losses = ref_mod.fused_moe(h, g, wu, wd, top_k=k, activation=activation, gating=gating,
-                                    aux_loss_coeff=aux, z_loss_coeff=z, return_metrics=True,
-                                    allow_dropped_tokens=True, max_tokens_per_expert=h.shape[0] * k)
+                                    aux_loss_coeff=aux, z_loss_coeff=z, return_metrics=True, **kw, **extra)
     loss = (out.float() * go.float()).sum()
     for name in ("aux_loss", "z_loss"):
         if name in losses:
@@ -91,8 +93,8 @@ def run_reference(h, g, wu, wd, go, k, activation, gating, aux, z):
                 dH=h.grad, dGate=g.grad, dW_up=wu.grad, dW_down=wd.grad)
 
 
-def run_oracle(h, g, wu, wd, go, k, activation, gating, aux, z, dtype):
-    fw = orc.fused_moe_forward(h, g, wu, wd, k, activation, gating, aux, z, dtype=dtype)
+def run_oracle(h, g, wu, wd, go, k, activation, gating, aux, z, dtype, **extra):
+    fw = orc.fused_moe_forward(h, g, wu, wd, k, activation, gating, aux, z, dtype=dtype, **extra)
     bw = orc.fused_moe_backward(fw, go)
     return fw, bw
 
@@ -126,8 +128,48 @@ def pin_layer(tag, seed, N, D, E, F, k, dtype, tol, combos, save_full=True):
     torch.save(gold, os.path.join(GOLD, f"{tag}.pt"))
 
 
+def pin_variants():
+    """Routing enhancements and capacity dropping (reference slow path, fp32): indices, outputs and gradients."""
+    N, D, E, F, k = 96, 64, 16, 128, 4
+    h, g, wu, wd, go = make_inputs(21, N, D, E, F, torch.float32)
+    g = g * 20.0  # spread the logits so that the softmax probabilities differ clearly
+    torch.manual_seed(5)
+    bias = torch.randn(E) * 0.3
+    variants = {
+        "capacity_1.0": dict(capacity_factor=1.0),
+        "capacity_0.5_sigmoid": dict(capacity_factor=0.5, gating="sigmoid"),
+        "expert_bias": dict(expert_bias=bias),
+        "pre_softmax": dict(pre_softmax=True),
+        "pre_softmax_bias_scale": dict(pre_softmax=True, expert_bias=bias * 0.05, scoring_factor=2.5),
+        "groups_4_2": dict(n_group=4, topk_group=2),
+        "groups_4_2_sigmoid_bias": dict(n_group=4, topk_group=2, gating="sigmoid", expert_bias=bias * 0.2),
+        "groups_8_4_pre_softmax": dict(n_group=8, topk_group=4, pre_softmax=True),
+    }
+    gold = dict(seed=21, shape=(N, D, E, F, k), gate_scale=20.0, bias=bias, cases={})
+    for name, extra in variants.items():
+        extra = dict(extra)
+        gating = extra.pop("gating", "softmax")
+        ref = run_reference(h, g, wu, wd, go, k, "swiglu", gating, 0.0, 0.0, **extra)
+        fw, bw = run_oracle(h, g, wu, wd, go, k, "swiglu", gating, 0.0, 0.0, torch.float32, **extra)
+        errs = dict(out=rel(fw["out"], ref["out"]), dH=rel(bw["dH"], ref["dH"]), dGate=rel(bw["dGate"], ref["dGate"]),
+                    dW_up=rel(bw["dW_up"], ref["dW_up"]), dW_down=rel(bw["dW_down"], ref["dW_down"]))
+        print(f"variant {name:26s}: " + " ".join(f"{n}={v:.1e}" for n, v in errs.items()))
+        for n, v in errs.items():
+            assert v <= 2e-5, f"variant {name}: {n} off by {v}"
+        case = dict(gating=gating, extra={a: b for a, b in extra.items() if a != "expert_bias"},
+                    has_bias="expert_bias" in extra, bias_scale=float((extra["expert_bias"] / bias).mean()) if "expert_bias" in extra else 0.0,
+                    out=ref["out"], dH=ref["dH"], dGate=ref["dGate"], topk_idx=fw["topk_idx"].to(torch.int32),
+                    topk_w=fw["topk_w"])
+        if "capacity_factor" in extra:
+            case["dropped"] = int(ref["losses"]["dropped_token_count"])
+            assert case["dropped"] == int((fw["keep"] == 0).sum()), name
+        gold["cases"][name] = case
+    torch.save(gold, os.path.join(GOLD, "layer_variants_fp32.pt"))
+
+
 if __name__ == "__main__":
     pin_routing_rule()
+    pin_variants()
     combos = [("swiglu", "softmax", 0.01, 0.001), ("geglu", "softmax", 0.0, 0.0), ("relu_squared", "sigmoid", 0.01, 0.001),
               ("swiglu", "sigmoid", 0.0, 0.0)]
     pin_layer("layer_small_fp32", 11, 96, 64, 8, 128, 2, torch.float32, 2e-5, combos)

@@ -77,6 +77,15 @@ def main():
     route_only = orc.mm(bw["gl"], g.cpu(), torch.bfloat16)
     assert rel(hp.grad, route_only) <= 5e-2, f"routing-only dH {rel(hp.grad, route_only)}"
 
+    # opt-in complete input gradient: equals the single-GPU dH
+    hf = h.clone().requires_grad_()
+    out_f, _ = ffm.fused_moe(hf, g, wu_l, wd_l, top_k=k, ep_group=group, ep_full_input_grad=True)
+    (out_f.float() * go.float()).sum().backward()
+    hs2 = h.clone().requires_grad_()
+    out_2, _ = ffm.fused_moe(hs2, g, wu, wd, top_k=k)
+    (out_2.float() * go.float()).sum().backward()
+    assert rel(hf.grad, hs2.grad) <= TOL, f"full EP input gradient {rel(hf.grad, hs2.grad)}"
+
     # ---- shared expert inside the EP call ----------------------------------------------------
     hq = h.clone().requires_grad_()
     sgp, sup, sdp = [t.clone().requires_grad_() for t in (sg, su, sd)]
@@ -113,6 +122,12 @@ def main():
     assert rel(out_l, ref) <= TOL, f"latent output {rel(out_l, ref)}"
     for t in (lwdp.grad, lwup.grad, wul.grad, wdl.grad):
         assert t is not None and torch.isfinite(t).all()
+    hl = h.clone().requires_grad_()
+    out_lf, _ = ffm.fused_moe(hl, g, wu_l, wd_l, top_k=k, ep_group=group, latent_weights=(lwd, lwu),
+                              ep_full_input_grad=True)
+    (out_lf.float() * go.float()).sum().backward()
+    assert torch.equal(out_lf, out_l.detach()) and torch.isfinite(hl.grad).all()
+    assert (hl.grad.float() - route_only.to(dev).float()).abs().max() > 0, "latent path adds the expert input gradient"
 
     # ---- MoELayer.shard_experts ----------------------------------------------------------------
     torch.manual_seed(3)

@@ -125,3 +125,33 @@ def test_grouped_layout_properties():
     for e in range(8):
         rows = pos[flat == e]
         assert (rows[1:] > rows[:-1]).all()
+
+
+def _variant_inputs(gold):
+    N, D, E, F, k = gold["shape"]
+    torch.manual_seed(gold["seed"])
+    h = torch.randn(N, D)
+    g = torch.randn(E, D) * 0.02 * gold["gate_scale"]
+    wu = torch.randn(E, F, D) * 0.02
+    wd = torch.randn(E, D, F // 2) * 0.02
+    go = torch.randn(N, D)
+    return h, g, wu, wd, go
+
+
+def test_routing_variants_and_capacity_golden():
+    """Group-limited / pre-softmax / biased routing and capacity dropping against the reference's slow path."""
+    gold = torch.load(os.path.join(GOLD, "layer_variants_fp32.pt"))
+    N, D, E, F, k = gold["shape"]
+    h, g, wu, wd, go = _variant_inputs(gold)
+    assert len(gold["cases"]) == 8
+    for name, case in gold["cases"].items():
+        extra = dict(case["extra"])
+        if case["has_bias"]:
+            extra["expert_bias"] = gold["bias"] * case["bias_scale"]
+        fw = orc.fused_moe_forward(h, g, wu, wd, k, "swiglu", case["gating"], dtype=torch.float32, **extra)
+        bw = orc.fused_moe_backward(fw, go)
+        assert torch.equal(fw["topk_idx"].to(torch.int32), case["topk_idx"]), name
+        assert rel(fw["out"], case["out"]) < 2e-5, name
+        assert rel(bw["dH"], case["dH"]) < 2e-5 and rel(bw["dGate"], case["dGate"]) < 2e-5, name
+        if "dropped" in case:
+            assert int((fw["keep"] == 0).sum()) == case["dropped"] > 0, name
