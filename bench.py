@@ -234,6 +234,7 @@ def main():
     if sampler:
         sampler.start()
     launches0 = ops.launch_count
+    a2a_bytes0 = ops.a2a_bytes_sent
     ops.set_timer(timer)
     t0 = torch.cuda.Event(enable_timing=True)
     t1 = torch.cuda.Event(enable_timing=True)
@@ -244,6 +245,7 @@ def main():
     fence()
     ops.set_timer(None)
     launches = ops.launch_count - launches0
+    a2a_bytes = ops.a2a_bytes_sent - a2a_bytes0
     ms = t0.elapsed_time(t1)
     clocks = sampler.stop() if sampler else None
     ops.check_status()
@@ -342,9 +344,21 @@ def main():
                 "frac_of_nominal_2250": (achieved / 2250.0) if achieved else None,
                 "gemm_launches": gemm_launches, "gemm_ms_per_step": gemm_ms / K,
                 "algorithmic_tflop_per_step": fl["gemm"] / 1e12,
-                "other_kernels_ms_per_step": {n: v[1] / K for n, v in kt.items() if n not in gemm_names},
+                "other_kernels_ms_per_step": {n: v[1] / K for n, v in kt.items()
+                                              if n not in gemm_names and n != "all_to_all"},
             },
         }
+        if world > 1 and "all_to_all" in kt:
+            # expert-parallel exchange on this rank: three all-to-alls per step (dispatch, combine, backward).
+            # Time is from CUDA events around each call on its issuing stream, so it includes waiting for peers;
+            # the NVLink fraction is against the 770 GB/s per-direction peer-copy figure measured on this pool.
+            n_a2a, a2a_ms = kt["all_to_all"]
+            gbs = a2a_bytes / (a2a_ms * 1e-3) / 1e9 if a2a_ms > 0 else None
+            line["expert_parallel"] = {"all_to_all_calls_per_step": n_a2a / K, "all_to_all_ms_per_step": a2a_ms / K,
+                                       "bytes_sent_per_step": a2a_bytes / K, "achieved_gbs_per_direction": gbs,
+                                       "nvlink_frac_of_770": (gbs / 770.0) if gbs else None,
+                                       "share_of_step": (a2a_ms / K) / (ms / K),
+                                       "transport": os.environ.get("FFM_EP_TRANSPORT", "p2p")}
         if world == 1 and not args.no_cpu_baseline:
             threads = os.cpu_count() or 1
             v, secs = oracle_sample_tokens_per_s(2048, threads, repeats=2)

@@ -17,6 +17,7 @@ extern "C" const char* ffm_error_string(int code) {
     case FFM_STATUS_WAIT_MMA: return "device: MMA issuer wait ran out";
     case FFM_STATUS_WAIT_EPILOGUE: return "device: epilogue wait ran out";
     case FFM_STATUS_BAD_INDEX: return "device: expert index or row position out of range";
+    case FFM_STATUS_WAIT_PEER: return "device: a peer GPU did not signal within the wait budget";
     default: return "unknown code";
   }
 }

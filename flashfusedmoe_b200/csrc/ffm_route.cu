@@ -26,12 +26,16 @@ struct RouteGrid {
   int tokens_per_block;
 };
 
-RouteGrid route_grid(long long N) {
-  // Contiguous token chunks, a multiple of 16 tokens (8 warps x 2 tokens), about four blocks per SM.
+// Tokens a block of the gate kernel handles per iteration: 8 warps x 2 tokens when a warp owns all experts
+// (E <= 32), 16 / NG when the warps of a block share NG groups of 32 experts.
+int route_granule(int E) { return E <= 32 ? 16 : (E <= 64 ? 8 : (E <= 128 ? 4 : 2)); }
+
+RouteGrid route_grid(long long N, int granule = 16) {
+  // Contiguous token chunks, a multiple of the granule, about four blocks per SM.
   long long target_blocks = 148 * 4;
   long long tpb = (N + target_blocks - 1) / target_blocks;
-  tpb = ((tpb + 15) / 16) * 16;
-  if (tpb < 16) tpb = 16;
+  tpb = ((tpb + granule - 1) / granule) * granule;
+  if (tpb < granule) tpb = granule;
   RouteGrid g;
   g.tokens_per_block = static_cast<int>(tpb);
   g.blocks = static_cast<int>((N + tpb - 1) / tpb);
@@ -271,7 +275,7 @@ __device__ __forceinline__ void route_token(const float (&logit)[NG], long long 
 
 // Expert e = g * 32 + lane for NG > 1 (GW == 32); e = lane % GW for NG == 1.
 template <int GW, int NG>
-__global__ void __launch_bounds__(ROUTE_THREADS)
+__global__ void __launch_bounds__(ROUTE_THREADS, (GW <= 8 ? 4 : (GW <= 16 ? 2 : 1)))
 route_gate_topk(const bf16* __restrict__ hidden, const bf16* __restrict__ gate_w, const float* __restrict__ bias,
                 long long N, int D, int E, int top_k, RouteOpts opts, int tokens_per_block,
                 bf16* __restrict__ logits_out, float* __restrict__ topk_w, int32_t* __restrict__ topk_idx,
@@ -297,46 +301,96 @@ route_gate_topk(const bf16* __restrict__ hidden, const bf16* __restrict__ gate_w
   }
   float zsum = 0.0f;
 
-  for (long long t0 = tok_begin + warp * TPW; t0 < tok_end; t0 += ROUTE_WARPS * TPW) {
-    const bool has1 = (t0 + 1) < tok_end;
-    const uint4* h0p = reinterpret_cast<const uint4*>(hidden + t0 * D);
-    const uint4* h1p = reinterpret_cast<const uint4*>(hidden + (has1 ? t0 + 1 : t0) * D);
-
-    // ---- gate GEMM: logit[tk][g] for expert g * 32 + lane (or lane % GW) ----
-    float logit0[NG], logit1[NG];
+  if constexpr (NG > 1) {
+    // Many experts: the warps of a block share the gate GEMM of a few token pairs. Warp w computes the 32 experts
+    // of group (w % NG) for pair (w / NG) and leaves the logits in shared memory; then warp t routes token t of the
+    // iteration. 8 / NG pairs per iteration keep every warp busy in the GEMM phase for any NG in {2, 4, 8}.
+    constexpr int PAIRS = ROUTE_WARPS / NG;
+    __shared__ float s_logit[2 * PAIRS][NG * 32];
+    const int my_pair = warp / NG;
+    const int my_group = warp % NG;
+    for (long long it0 = tok_begin; it0 < tok_end; it0 += 2 * PAIRS) {
+      const long long t0 = it0 + 2 * my_pair;
+      if (t0 < tok_end) {
+        const bool has1 = (t0 + 1) < tok_end;
+        const uint4* h0p = reinterpret_cast<const uint4*>(hidden + t0 * D);
+        const uint4* h1p = reinterpret_cast<const uint4*>(hidden + (has1 ? t0 + 1 : t0) * D);
+        float acc0[32], acc1[32];
 #pragma unroll
-    for (int g = 0; g < NG; ++g) {
-      float acc0[GW], acc1[GW];
+        for (int e = 0; e < 32; ++e) {
+          acc0[e] = 0.0f;
+          acc1[e] = 0.0f;
+        }
+        for (int c = lane; c < chunks; c += 32) {
+          const uint4 a0 = __ldg(h0p + c);
+          const uint4 a1 = __ldg(h1p + c);
 #pragma unroll
-      for (int e = 0; e < GW; ++e) {
-        acc0[e] = 0.0f;
-        acc1[e] = 0.0f;
-      }
-      // unrolled so that the loads of several chunks are in flight together (the kernel is latency-bound)
-#pragma unroll(GW <= 16 ? 4 : 1)
-      for (int c = lane; c < chunks; c += 32) {
-        const uint4 a0 = __ldg(h0p + c);
-        const uint4 a1 = __ldg(h1p + c);
-#pragma unroll
-        for (int e = 0; e < GW; ++e) {
-          const int ee = g * GW + e;
-          if (ee < E) {
-            const uint4 w = __ldg(reinterpret_cast<const uint4*>(gate_w + static_cast<long long>(ee) * D) + c);
-            acc0[e] = dot8(a0, w, acc0[e]);
-            acc1[e] = dot8(a1, w, acc1[e]);
+          for (int e = 0; e < 32; ++e) {
+            const int ee = my_group * 32 + e;
+            if (ee < E) {
+              const uint4 w = __ldg(reinterpret_cast<const uint4*>(gate_w + static_cast<long long>(ee) * D) + c);
+              acc0[e] = dot8(a0, w, acc0[e]);
+              acc1[e] = dot8(a1, w, acc1[e]);
+            }
           }
         }
+        transpose_reduce<32>(acc0, lane);
+        transpose_reduce<32>(acc1, lane);
+        s_logit[2 * my_pair][my_group * 32 + lane] = bf16_round(acc0[0]);
+        s_logit[2 * my_pair + 1][my_group * 32 + lane] = bf16_round(acc1[0]);
       }
-      transpose_reduce<GW>(acc0, lane);
-      transpose_reduce<GW>(acc1, lane);
-      logit0[g] = bf16_round(acc0[0]);
-      logit1[g] = bf16_round(acc1[0]);
+      __syncthreads();
+      if (warp < 2 * PAIRS && it0 + warp < tok_end) {
+        float logit[NG];
+#pragma unroll
+        for (int g = 0; g < NG; ++g) logit[g] = s_logit[warp][g * 32 + lane];
+        route_token<GW, NG>(logit, it0 + warp, lane, E, top_k, opts, bias, logits_out, topk_w, topk_idx, lse_out, mass,
+                            cnt, zsum);
+      }
+      __syncthreads();
     }
+  } else {
+    for (long long t0 = tok_begin + warp * TPW; t0 < tok_end; t0 += ROUTE_WARPS * TPW) {
+      const bool has1 = (t0 + 1) < tok_end;
+      const uint4* h0p = reinterpret_cast<const uint4*>(hidden + t0 * D);
+      const uint4* h1p = reinterpret_cast<const uint4*>(hidden + (has1 ? t0 + 1 : t0) * D);
 
-    route_token<GW, NG>(logit0, t0, lane, E, top_k, opts, bias, logits_out, topk_w, topk_idx, lse_out, mass, cnt, zsum);
-    if (has1) {
-      route_token<GW, NG>(logit1, t0 + 1, lane, E, top_k, opts, bias, logits_out, topk_w, topk_idx, lse_out, mass, cnt,
-                          zsum);
+      // ---- gate GEMM: logit[tk][g] for expert g * 32 + lane (or lane % GW) ----
+      float logit0[NG], logit1[NG];
+  #pragma unroll
+      for (int g = 0; g < NG; ++g) {
+        float acc0[GW], acc1[GW];
+  #pragma unroll
+        for (int e = 0; e < GW; ++e) {
+          acc0[e] = 0.0f;
+          acc1[e] = 0.0f;
+        }
+        // unrolled so that the loads of several chunks are in flight together (the kernel is latency-bound)
+  #pragma unroll(GW <= 16 ? 4 : 1)
+        for (int c = lane; c < chunks; c += 32) {
+          const uint4 a0 = __ldg(h0p + c);
+          const uint4 a1 = __ldg(h1p + c);
+  #pragma unroll
+          for (int e = 0; e < GW; ++e) {
+            const int ee = g * GW + e;
+            if (ee < E) {
+              const uint4 w = __ldg(reinterpret_cast<const uint4*>(gate_w + static_cast<long long>(ee) * D) + c);
+              acc0[e] = dot8(a0, w, acc0[e]);
+              acc1[e] = dot8(a1, w, acc1[e]);
+            }
+          }
+        }
+        transpose_reduce<GW>(acc0, lane);
+        transpose_reduce<GW>(acc1, lane);
+        logit0[g] = bf16_round(acc0[0]);
+        logit1[g] = bf16_round(acc1[0]);
+      }
+
+      route_token<GW, NG>(logit0, t0, lane, E, top_k, opts, bias, logits_out, topk_w, topk_idx, lse_out, mass, cnt, zsum);
+      if (has1) {
+        route_token<GW, NG>(logit1, t0 + 1, lane, E, top_k, opts, bias, logits_out, topk_w, topk_idx, lse_out, mass, cnt,
+                            zsum);
+      }
     }
   }
 
@@ -346,6 +400,67 @@ route_gate_topk(const bf16* __restrict__ hidden, const bf16* __restrict__ gate_w
     const int e = g * GW + (NG > 1 ? lane : (lane % GW));
     const bool holder_lane = (NG > 1) || (lane < GW);
     if (holder_lane && e < E) {
+      s_mass[warp][e] = mass[g];
+      s_cnt[warp][e] = cnt[g];
+    }
+  }
+  if (lane == 0) s_z[warp] = zsum;
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += ROUTE_THREADS) {
+    float m = 0.0f;
+    int c = 0;
+    for (int w = 0; w < ROUTE_WARPS; ++w) {
+      m += s_mass[w][e];
+      c += s_cnt[w][e];
+    }
+    block_mass[static_cast<long long>(blockIdx.x) * E + e] = m;
+    block_hist[static_cast<long long>(blockIdx.x) * E + e] = c;
+  }
+  if (threadIdx.x == 0) {
+    float z = 0.0f;
+    for (int w = 0; w < ROUTE_WARPS; ++w) z += s_z[w];
+    block_z[blockIdx.x] = z;
+  }
+}
+
+// Scoring / top-k / statistics from logits that a GEMM already wrote (bf16 [N, E]): one warp per token, lane holds
+// experts g * 32 + lane. Used when the gate GEMM runs on the tensor cores (many experts), where a CUDA-core dot
+// product per (token, expert) would dominate the routing time.
+template <int NG>
+__global__ void __launch_bounds__(ROUTE_THREADS)
+route_from_logits(const bf16* __restrict__ logits, const float* __restrict__ bias, long long N, int E, int top_k,
+                  RouteOpts opts, int tokens_per_block, float* __restrict__ topk_w, int32_t* __restrict__ topk_idx,
+                  float* __restrict__ lse_out, int32_t* __restrict__ block_hist, float* __restrict__ block_mass,
+                  float* __restrict__ block_z) {
+  __shared__ float s_mass[ROUTE_WARPS][MAX_E];
+  __shared__ int s_cnt[ROUTE_WARPS][MAX_E];
+  __shared__ float s_z[ROUTE_WARPS];
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long tok_begin = static_cast<long long>(blockIdx.x) * tokens_per_block;
+  long long tok_end = tok_begin + tokens_per_block;
+  if (tok_end > N) tok_end = N;
+  float mass[NG];
+  int cnt[NG];
+#pragma unroll
+  for (int g = 0; g < NG; ++g) {
+    mass[g] = 0.0f;
+    cnt[g] = 0;
+  }
+  float zsum = 0.0f;
+  for (long long n = tok_begin + warp; n < tok_end; n += ROUTE_WARPS) {
+    float logit[NG];
+#pragma unroll
+    for (int g = 0; g < NG; ++g) {
+      const int e = g * 32 + lane;
+      logit[g] = (e < E) ? __bfloat162float(logits[n * E + e]) : 0.0f;
+    }
+    route_token<32, NG>(logit, n, lane, E, top_k, opts, bias, nullptr, topk_w, topk_idx, lse_out, mass, cnt, zsum);
+  }
+#pragma unroll
+  for (int g = 0; g < NG; ++g) {
+    const int e = g * 32 + lane;
+    if (e < E) {
       s_mass[warp][e] = mass[g];
       s_cnt[warp][e] = cnt[g];
     }
@@ -628,7 +743,7 @@ extern "C" size_t ffm_route_workspace_bytes(int64_t N, int E, int top_k) {
   (void)top_k;
   if (N < 0 || E < 1) return 0;
   // The same workspace serves ffm_group_rows over N * top_k slots, whose grid is never larger.
-  RouteGrid g = route_grid(N > 0 ? N : 1);
+  RouteGrid g = route_grid(N > 0 ? N : 1, route_granule(E));
   RouteGrid g2 = route_grid(N > 0 ? N * (top_k > 0 ? top_k : 1) : 1);
   int blocks = g.blocks > g2.blocks ? g.blocks : g2.blocks;
   return carve_workspace(nullptr, blocks, E).bytes;
@@ -658,11 +773,29 @@ extern "C" int ffm_route_forward(const void* hidden, const void* gate_w, const f
   if (workspace_bytes < ffm_route_workspace_bytes(N, E, top_k)) return FFM_ERR_WORKSPACE;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (cudaMemsetAsync(src, 0xFF, static_cast<size_t>(rows_cap) * 4, s) != cudaSuccess) return FFM_ERR_LAUNCH;
-  const RouteGrid g = route_grid(N > 0 ? N : 1);
+  const RouteGrid g = route_grid(N > 0 ? N : 1, route_granule(E));
   RouteWorkspace w = carve_workspace(workspace, g.blocks, E);
   const bf16* h = static_cast<const bf16*>(hidden);
   const bf16* gw = static_cast<const bf16*>(gate_w);
   bf16* lg = static_cast<bf16*>(logits);
+  // Many experts: gate GEMM on the tensor cores (dense tcgen05 GEMM, fp32 accumulate, bf16 logits), then one
+  // scoring kernel. Few experts: everything in one warp-level kernel.
+  const bool tensor_gate = E > 32 && D % 64 == 0 && E % 32 == 0 && logits != nullptr;
+  if (tensor_gate) {
+    const int rc = ffm_grouped_gemm(hidden, gate_w, FFM_B_KMAJOR, 1, nullptr, N, D, E, 1.0f, logits, status, stream);
+    if (rc != FFM_OK) return rc;
+#define FFM_LOGIT_CASE(NG)                                                                                      \
+  route_from_logits<NG><<<g.blocks, ROUTE_THREADS, 0, s>>>(lg, expert_bias, N, E, top_k, opts, g.tokens_per_block, \
+                                                           topk_w, topk_idx, lse, w.block_hist, w.block_mass, w.block_z)
+    if (E <= 64) {
+      FFM_LOGIT_CASE(2);
+    } else if (E <= 128) {
+      FFM_LOGIT_CASE(4);
+    } else {
+      FFM_LOGIT_CASE(8);
+    }
+#undef FFM_LOGIT_CASE
+  } else {
 #define FFM_ROUTE_CASE(GW, NG)                                                                                 \
   launch_route<GW, NG>(g.blocks, s, h, gw, expert_bias, N, D, E, top_k, opts, g.tokens_per_block, lg, topk_w, \
                        topk_idx, lse, w)
@@ -680,6 +813,7 @@ extern "C" int ffm_route_forward(const void* hidden, const void* gate_w, const f
     FFM_ROUTE_CASE(32, 8);
   }
 #undef FFM_ROUTE_CASE
+  }
   route_scan<<<1, ROUTE_THREADS, 0, s>>>(w.block_hist, w.block_mass, w.block_z, g.blocks, E, w.block_off, counts,
                                          tile_start, stats);
   route_rank<<<g.blocks, ROUTE_THREADS, 0, s>>>(topk_idx, N * top_k, E, g.tokens_per_block * top_k, w.block_off,

@@ -25,7 +25,10 @@ from typing import Optional
 import torch
 
 from . import _lib, ops
-from .expert_parallel import all_to_all_rows, exchange_counts, local_ids_from_counts
+import os
+
+from . import p2p
+from .expert_parallel import all_to_all_rows, local_ids_from_counts
 
 _WEIGHT_EPS = 1e-6
 
@@ -36,6 +39,11 @@ _EP_BACKEND = "nccl"
 
 # "analytic": aux loss back-propagates into the gate; "reference_cuda": constant for softmax gating.
 _AUX_LOSS_GRAD = "analytic"
+
+# Expert-parallel transport: "p2p" = peer stores into symmetric receive buffers (libffmoe kernels), "nccl" =
+# torch.distributed all_to_all_single. Chosen by FFM_EP_TRANSPORT at import; p2p falls back to nccl per call when
+# symmetric memory is unavailable or a receive would not fit.
+_EP_TRANSPORT = os.environ.get("FFM_EP_TRANSPORT", "p2p")
 
 _side_streams = {}
 _dense_tile_start = {}
@@ -311,6 +319,45 @@ class _FusedMoEFunction(torch.autograd.Function):
 # Expert-parallel layer
 # ----------------------------------------------------------------------------------------------
 
+class _EPPlan:
+    """Row counts of one expert-parallel call, identical on every rank: cnt[s][d] = rows rank s sends to rank d.
+    Built from one all-gather of the per-expert counts and the call's only host synchronisation."""
+
+    def __init__(self, counts, ep, e_local, group, row_bytes):
+        self.group = group
+        self.rank = torch.distributed.get_rank(group)
+        self.ep = ep
+        all_counts = torch.empty(ep, counts.numel(), dtype=counts.dtype, device=counts.device)
+        torch.distributed.all_gather_into_tensor(all_counts, counts.contiguous(), group=group)
+        self.recv_counts = all_counts[:, self.rank * e_local:(self.rank + 1) * e_local].to(torch.int64)  # [ep, E_local]
+        host = all_counts.view(ep, ep, e_local).sum(-1).tolist()
+        self.cnt = [[int(v) for v in row] for row in host]
+        self.cnt_t = [[self.cnt[d][s] for d in range(ep)] for s in range(ep)]
+        self.send_splits = self.cnt[self.rank]
+        self.recv_splits = [self.cnt[s][self.rank] for s in range(ep)]
+        self.M = sum(self.recv_splits)
+        # peer-store transport when the symmetric buffer can hold the largest receive of any rank, either direction
+        self.px = None
+        if _EP_TRANSPORT == "p2p" and p2p.available() and ep <= 16:
+            worst = max(max(sum(self.cnt[s][d] for s in range(ep)) for d in range(ep)),
+                        max(sum(self.cnt[s]) for s in range(ep)))
+            need = 1 << max(20, (2 * worst * row_bytes - 1).bit_length())  # twice the worst case, power of two
+            self.px = p2p.get_exchange(group, counts.device, need)
+
+    def exchange(self, rows, reverse, region):
+        """Dispatch direction (reverse=False: rows ordered by destination rank) or its inverse. The result may be a
+        view of a receive region that the next exchange on the same region overwrites: copy it to keep it."""
+        cnt = self.cnt_t if reverse else self.cnt
+        if self.px is not None and self.px.fits(max(sum(cnt[s][d] for s in range(self.ep)) for d in range(self.ep)),
+                                                rows.shape[1] * rows.element_size()):
+            return self.px.exchange(rows, cnt, region), True
+        in_splits = cnt[self.rank]
+        out_splits = [cnt[s][self.rank] for s in range(self.ep)]
+        ops.a2a_bytes_sent += (sum(in_splits) - in_splits[self.rank]) * rows.shape[1] * rows.element_size()
+        with ops._Launch("all_to_all", 0):
+            return all_to_all_rows(rows, out_splits, in_splits, self.group), False
+
+
 def _compact_send_map(routing, T):
     """Send-buffer position of every flat slot: the grouped order with the 128-row padding squeezed out.
     Rows are expert-major, hence destination-rank-major (each rank owns a contiguous block of experts)."""
@@ -372,11 +419,14 @@ class _FusedMoEEPFunction(torch.autograd.Function):
         else:
             disp = h
 
-        recv_counts, send_splits, recv_splits = exchange_counts(routing.counts, ep, group)
-        M = sum(recv_splits)
+        W_bytes = disp.shape[1] * disp.element_size()
+        plan = _EPPlan(routing.counts, ep, El, group, max(W_bytes, D * 2))
+        recv_counts, M = plan.recv_counts, plan.M
         cpos, src_c = _compact_send_map(routing, T)
         send = ops.permute_rows(disp, src_c, T, k)
-        recv = all_to_all_rows(send, recv_splits, send_splits, group)        # [M, W]
+        recv, is_view = plan.exchange(send, False, 0)                          # [M, W]
+        if is_view and has_latent and need_grad:
+            recv = recv.clone()  # saved for the latent weight gradients
 
         if M > 0:
             local_ids = local_ids_from_counts(recv_counts, M).to(torch.int32)
@@ -402,7 +452,9 @@ class _FusedMoEEPFunction(torch.autograd.Function):
             local_out = ops.grouped_gemm(local_out, lwd, _lib.B_KMAJOR, 1, None, D, L)
         elif has_latent:
             local_out = h.new_empty(0, L)
-        returned = all_to_all_rows(local_out, send_splits, recv_splits, group)  # [T, W], send order
+        returned, is_view = plan.exchange(local_out, True, 1)                  # [T, W], send order
+        if is_view and need_grad:
+            returned = returned.clone()  # saved for backward; the region is overwritten by the next call
         returned_lat = None
         if has_latent:
             returned_lat = returned
@@ -416,7 +468,7 @@ class _FusedMoEEPFunction(torch.autograd.Function):
         ctx.cfg = cfg
         ctx.dims = (N, D, E, El, H, k, M, ep, rows_l)
         ctx.flags = (has_shared, has_latent)
-        ctx.splits = (send_splits, recv_splits)
+        ctx.plan = plan
         ctx.in_dtypes = tuple(None if t is None else t.dtype for t in
                               (hidden_states, gate_weight, w_up, w_down, sw_gate, sw_up, sw_down, lw_down, lw_up))
         ctx.routing_meta = (routing.rows_cap,)
@@ -440,7 +492,7 @@ class _FusedMoEEPFunction(torch.autograd.Function):
         group = cfg.ep_group
         N, D, E, El, H, k, M, ep, rows_l = ctx.dims
         has_shared, has_latent = ctx.flags
-        send_splits, recv_splits = ctx.splits
+        plan = ctx.plan
         t = dict(zip(ctx.names, ctx.saved_tensors))
         h, g, wu, wd = t["h"], t["g"], t["wu"], t["wd"]
         T = N * k
@@ -475,7 +527,7 @@ class _FusedMoEEPFunction(torch.autograd.Function):
         ready2.record()
         with torch.cuda.stream(a2a):
             a2a.wait_event(ready2)
-            recv_grad = all_to_all_rows(send, recv_splits, send_splits, group)
+            recv_grad, grad_is_view = plan.exchange(send, False, 2)
         a2a_done = torch.cuda.Event()
         a2a_done.record(a2a)
         send.record_stream(a2a)
@@ -486,7 +538,8 @@ class _FusedMoEEPFunction(torch.autograd.Function):
         dH, d_gate = ops.route_backward(gw, routing, gaux, gz, h, g, cfg.gating, dH=None)
 
         torch.cuda.current_stream().wait_event(a2a_done)
-        recv_grad.record_stream(torch.cuda.current_stream())
+        if not grad_is_view:
+            recv_grad.record_stream(torch.cuda.current_stream())
         d_lwd = d_lwu = None
         if has_latent:
             recv_grad_lat = recv_grad
@@ -521,7 +574,7 @@ class _FusedMoEEPFunction(torch.autograd.Function):
         if cfg.ep_full_input_grad:
             W = L if has_latent else D
             back = dx_recv if M > 0 else h.new_empty(0, W)
-            d_send = all_to_all_rows(back, send_splits, recv_splits, group)       # [T, W], send order
+            d_send, _ = plan.exchange(back, True, 1)                               # [T, W], send order
             d_disp = ops.combine_forward(d_send, t["cpos"], None, N, k)            # sum over the k slots
             if has_latent:
                 d_disp = ops.grouped_gemm(d_disp, t["lwd"], _lib.B_NMAJOR, 1, None, L, D)

@@ -17,6 +17,7 @@ _workspaces = {}
 # Instrumentation used by bench.py: a launch counter (kernels of this library enqueued so far) and an
 # optional per-kernel CUDA-event timer on the launching stream.
 launch_count = 0
+a2a_bytes_sent = 0
 _timer = None
 
 

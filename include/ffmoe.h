@@ -48,6 +48,7 @@ extern "C" {
 #define FFM_STATUS_WAIT_MMA 102      /* MMA issuer gave up waiting for operands or a free accumulator */
 #define FFM_STATUS_WAIT_EPILOGUE 103 /* epilogue gave up waiting for an accumulator */
 #define FFM_STATUS_BAD_INDEX 104     /* an expert index or row position was out of range */
+#define FFM_STATUS_WAIT_PEER 105     /* a peer GPU's flag did not arrive within the wait budget */
 
 /* Gating */
 #define FFM_GATING_SOFTMAX 0
@@ -228,6 +229,25 @@ int ffm_route_backward(const float* gw, const float* topk_w, const int32_t* topk
                        const float* lse, const float* gaux, const float* gz, const void* hidden, const void* gate_w,
                        int64_t N, int D, int E, int top_k, int gating, int accumulate, void* dH, void* dGate,
                        void* workspace, size_t workspace_bytes, ffm_stream_t stream);
+
+/* -------------------------------------------------------------------------------------------------
+ * Expert-parallel exchange over NVLink with plain peer stores. Replaces the c10d all_to_all_single calls of the
+ * reference's dispatcher (expert_parallel.py:253-258, :290-292; fused_moe.py:901-910).
+ * The caller owns the receive buffers and the flag arrays, which must be mapped on every GPU of the group
+ * (CUDA IPC / virtual-memory handles; the Python package uses torch's symmetric memory for this).
+ *
+ * ffm_p2p_push: copy n_segments (<= FFM_P2P_MAX_PEERS) contiguous byte ranges src[i] -> dst[i], dst[i] usually in a
+ *   peer's memory. Ranges and sizes must be multiples of 16 bytes; empty segments are skipped.
+ * ffm_p2p_signal_wait: all ranks call it with the same, growing epoch after their pushes: stores epoch into
+ *   slot [my_rank] of every rank's flag array (release), then waits (bounded by wait_cycles, 0 = default) until its
+ *   own array holds epoch in every slot (acquire). Kernels enqueued after it may read what the peers pushed.
+ *   flag_arrays[r] points at rank r's array of `world` uint32 flags, zero-initialised once.
+ * ------------------------------------------------------------------------------------------------- */
+#define FFM_P2P_MAX_PEERS 16
+int ffm_p2p_push(int n_segments, const void* const* src, void* const* dst, const int64_t* bytes,
+                 ffm_stream_t stream);
+int ffm_p2p_signal_wait(void* const* flag_arrays, int my_rank, int world, uint32_t epoch, int32_t* status,
+                        long long wait_cycles, ffm_stream_t stream);
 
 #ifdef __cplusplus
 }

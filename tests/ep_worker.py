@@ -63,6 +63,16 @@ def main():
     (out_1.float() * go.float()).sum().backward()
     assert torch.equal(losses["tokens_per_expert"], losses_1["tokens_per_expert"])
     assert rel(out_ep, out_1) <= 1e-6, f"EP output differs from single GPU: {rel(out_ep, out_1)}"
+    # the other transport gives bit-identical results
+    fm = sys.modules["flashfusedmoe_b200.fused_moe"]  # the package rebinds the name fused_moe to the function
+    this_transport = fm._EP_TRANSPORT
+    fm._EP_TRANSPORT = "nccl" if this_transport == "p2p" else "p2p"
+    ho, go_, wuo, wdo = [t.clone().requires_grad_() for t in (h, g, wu_l, wd_l)]
+    out_o, _ = ffm.fused_moe(ho, go_, wuo, wdo, top_k=k, ep_group=group, aux_loss_coeff=0.01)
+    (out_o.float() * go.float()).sum().backward()
+    fm._EP_TRANSPORT = this_transport
+    assert torch.equal(out_o, out_ep) and torch.equal(wuo.grad, wup.grad) and torch.equal(ho.grad, hp.grad), \
+        "p2p and nccl transports must agree bit for bit"
     assert rel(gp.grad, gs.grad) <= 1e-3, "gate gradient"
     assert abs(float(losses["aux_loss"]) - float(losses_1["aux_loss"])) < 1e-6
     # expert weight gradients: sum over all ranks' tokens, scaled by 1 / ep (reference: fused_moe.py:961-966)

@@ -13,8 +13,9 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_expert_parallel_two_ranks():
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+@pytest.mark.parametrize("transport", ["p2p", "nccl"])
+def test_expert_parallel_two_ranks(transport):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", FFM_EP_TRANSPORT=transport, TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
            "127.0.0.1", "--master-port", "29511", os.path.join(ROOT, "tests", "ep_worker.py")]
     p = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)

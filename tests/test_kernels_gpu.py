@@ -58,8 +58,12 @@ def test_route_forward(N, D, E, k, gating):
     gate = (torch.randn(E, D, device=DEV) * 0.5).bfloat16()
     r = ops.route_forward(hidden, gate, k, gating)
     ops.check_status()
-    ref_logits = (hidden.float() @ gate.float().T).bfloat16()
-    assert bf16_ulp_close(r.logits, ref_logits, 1).all(), "gate GEMM logits differ by more than 1 bf16 ulp"
+    ref32 = hidden.float() @ gate.float().T
+    ref_logits = ref32.bfloat16()
+    # one bf16 unit in the last place, or (for logits that cancel to nearly zero) the fp32 accumulation-order error
+    acc_err = 4e-6 * (hidden.float().abs() @ gate.float().abs().T)
+    close = bf16_ulp_close(r.logits, ref_logits, 1) | ((r.logits.float() - ref32).abs() <= acc_err + ref32.abs() * 2.0 ** -8)
+    assert close.all(), "gate GEMM logits differ by more than 1 bf16 ulp"
     lg = r.logits.float()
     sel = torch.sigmoid(lg) if gating == "sigmoid" else lg
     idx_ref = triton_rule_topk(sel, k)
