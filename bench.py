@@ -234,8 +234,6 @@ def main():
     if sampler:
         sampler.start()
     launches0 = ops.launch_count
-    a2a_bytes0 = ops.a2a_bytes_sent
-    ops.set_timer(timer)
     t0 = torch.cuda.Event(enable_timing=True)
     t1 = torch.cuda.Event(enable_timing=True)
     t0.record()
@@ -243,12 +241,19 @@ def main():
         step()
     t1.record()
     fence()
-    ops.set_timer(None)
     launches = ops.launch_count - launches0
-    a2a_bytes = ops.a2a_bytes_sent - a2a_bytes0
     ms = t0.elapsed_time(t1)
-    clocks = sampler.stop() if sampler else None
     ops.check_status()
+
+    # ---- per-kernel pass: the same K steps again with a CUDA-event pair around every launch of this library ----
+    # (kept out of the timed region above: the ~60 extra event records per step cost about 5 % of a 2 ms step)
+    a2a_bytes0 = ops.a2a_bytes_sent
+    ops.set_timer(timer)
+    for _ in range(K):
+        step()
+    fence()
+    ops.set_timer(None)
+    a2a_bytes = ops.a2a_bytes_sent - a2a_bytes0
 
     # ---- end to end: pinned host input in, loss scalar out, every step ------------------------
     # The loop a training script would run around the public API: the next step's input is uploaded on a copy
@@ -304,6 +309,7 @@ def main():
     fence()
     assert len(read) == K and all(v == v for v in read)
     e2e_ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if sampler else None  # sampled from the start of the timed region to here
 
     t = torch.tensor([ms, e2e_ms], device=device, dtype=torch.float64)
     if world > 1:
@@ -314,7 +320,7 @@ def main():
         peaks = measured_peaks()
         fl = algorithmic_flops(tokens, world)
         kt = timer.totals_ms()
-        gemm_names = ("gemm_up_glu", "gemm", "gemm_wgrad")
+        gemm_names = ("gemm_up_glu", "gemm", "gemm_wgrad", "gemm_dact_glu")
         gemm_ms = sum(kt[n][1] for n in gemm_names if n in kt)
         gemm_launches = sum(kt[n][0] for n in gemm_names if n in kt)
         achieved = fl["gemm"] * K / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else None
@@ -339,6 +345,8 @@ def main():
                 # from the ncu capture summarised in profiles/gemm_up_glu_pair_config2_ncu_full.md
                 "traffic": 484.8e6 if world == 1 else None,
                 "kernel": "ffm_gemm_kernel (tcgen05 grouped GEMM, all instantiations)",
+                "measured_in": "a second pass of the same K steps, right after the timed region, with a CUDA-event pair "
+                               "around every kernel launch of the library on its launching stream",
                 "peak_source": f"{peaks['source']} sustained cuBLAS bf16 (burst {peaks['tflops_burst']})",
                 "frac_of_burst": (achieved / peaks["tflops_burst"]) if achieved else None,
                 "frac_of_nominal_2250": (achieved / 2250.0) if achieved else None,
@@ -357,7 +365,7 @@ def main():
             line["expert_parallel"] = {"all_to_all_calls_per_step": n_a2a / K, "all_to_all_ms_per_step": a2a_ms / K,
                                        "bytes_sent_per_step": a2a_bytes / K, "achieved_gbs_per_direction": gbs,
                                        "nvlink_frac_of_770": (gbs / 770.0) if gbs else None,
-                                       "share_of_step": (a2a_ms / K) / (ms / K),
+                                       "share_of_step_in_kernel_pass": (a2a_ms / K) / (ms / K),
                                        "transport": os.environ.get("FFM_EP_TRANSPORT", "p2p")}
         if world == 1 and not args.no_cpu_baseline:
             threads = os.cpu_count() or 1

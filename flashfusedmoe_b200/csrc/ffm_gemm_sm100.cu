@@ -48,21 +48,23 @@ constexpr int EPI_WARPS = 4;
 constexpr int MAX_GROUPS = 256;
 constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KiB
 constexpr int STG_ARRAY_BYTES = 32 * 64;    // one staged block: 32 rows x 32 bf16
-constexpr int STG_WARP_BYTES = 3 * STG_ARRAY_BYTES;
-constexpr int STG_BYTES = EPI_WARPS * STG_WARP_BYTES;  // 24 KiB
 constexpr int SMEM_CTRL_BYTES = 2048;
 constexpr int MAX_STAGES = 6;
 
-template <int CTA2>
+enum { EPI_PLAIN = 0, EPI_GLU = 1, EPI_GLUBWD = 2 };
+
+// Shared-memory budget per tile shape and epilogue. The GLU-backward epilogue also streams the saved
+// pre-activations in (two double-buffered blocks per warp), so it gives up one ring stage for staging space.
+template <int CTA2, int EPI>
 struct Shape {
-  static constexpr int STAGES = CTA2 ? 6 : 4;
+  static constexpr int STAGES = (CTA2 ? 6 : 4) - (EPI == EPI_GLUBWD ? 1 : 0);
   static constexpr int B_STAGE_BYTES = (CTA2 ? 128 : 256) * BK * 2;
   static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
-  static constexpr int RING_BYTES = STAGES * STAGE_BYTES;  // 192 KiB either way
+  static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
+  static constexpr int STG_WARP_BYTES = (EPI == EPI_GLUBWD ? 6 : 3) * STG_ARRAY_BYTES;
+  static constexpr int STG_BYTES = EPI_WARPS * STG_WARP_BYTES;
   static constexpr int SMEM_BYTES = RING_BYTES + STG_BYTES + SMEM_CTRL_BYTES + 1024;  // + 1 KiB alignment slack
 };
-
-enum { EPI_PLAIN = 0, EPI_GLU = 1 };
 
 struct GemmParams {
   const int32_t* tile_start;  // [groups + 1] cumulative 128-row tiles, or null (dense)
@@ -87,6 +89,7 @@ struct Ctrl {
   unsigned long long empty_bar[MAX_STAGES];
   unsigned long long acc_full_bar[NUM_ACC];
   unsigned long long acc_empty_bar[NUM_ACC];
+  unsigned long long epi_load_bar[EPI_WARPS][2];  // GLU-backward epilogue: pre-activation blocks have landed
   uint32_t tmem_base;
   int abort_flag;
   int tile_start[MAX_GROUPS + 1];
@@ -234,6 +237,26 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t cluster_bar) {
 // 16-byte chunk q of row r inside a 32-row x 64-byte block with the 64-byte TMA swizzle
 __device__ __forceinline__ uint32_t stg_offset(int r, int q) { return r * 64 + ((q ^ ((r >> 1) & 3)) << 4); }
 
+__device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+  return v;
+}
+
+// 3-D TMA load of one {32 columns, 32 rows, 1} block into this CTA's shared memory, completing on a local mbarrier
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* map, uint32_t bar, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(dst),
+      "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+
+// Ask for one {32, 32, 1} block of a tensor map to be brought into L2 (no shared-memory destination).
+__device__ __forceinline__ void tma_prefetch_l2_3d(const void* map, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];" ::"l"(map), "r"(c0), "r"(c1), "r"(c2)
+               : "memory");
+}
+
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
@@ -243,7 +266,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
 ffm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB0,
                 const __grid_constant__ CUtensorMap tmB1, const __grid_constant__ CUtensorMap tmC,
                 const __grid_constant__ CUtensorMap tmC2, const GemmParams p) {
-  using S = Shape<CTA2>;
+  using S = Shape<CTA2, EPI>;
   constexpr int STAGES = S::STAGES;
   constexpr int STAGE_BYTES = S::STAGE_BYTES;
 
@@ -253,7 +276,7 @@ ffm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   uint8_t* smem = smem_raw + pad;
   const uint32_t smem_base = raw_addr + pad;
   const uint32_t stg_base = smem_base + S::RING_BYTES;
-  Ctrl* ctrl = reinterpret_cast<Ctrl*>(smem + S::RING_BYTES + STG_BYTES);
+  Ctrl* ctrl = reinterpret_cast<Ctrl*>(smem + S::RING_BYTES + S::STG_BYTES);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -269,6 +292,10 @@ ffm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     for (int a = 0; a < NUM_ACC; ++a) {
       mbar_init(smem_u32(&ctrl->acc_full_bar[a]), 1);
       mbar_init(smem_u32(&ctrl->acc_empty_bar[a]), EPI_WARPS * (CTA2 ? 2 : 1));  // one arrival per epilogue warp
+    }
+    for (int w = 0; w < EPI_WARPS; ++w) {
+      mbar_init(smem_u32(&ctrl->epi_load_bar[w][0]), 1);
+      mbar_init(smem_u32(&ctrl->epi_load_bar[w][1]), 1);
     }
     ctrl->abort_flag = 0;
     fence_barrier_init();
@@ -437,16 +464,45 @@ ffm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   } else {
     // ================= epilogue (warps 2..5) =================
     const int quarter = warp & 3;  // TMEM lanes [32 * quarter, 32 * quarter + 32) belong to this warp
-    const uint32_t stg = stg_base + (warp - 2) * STG_WARP_BYTES;
+    const uint32_t stg = stg_base + (warp - 2) * S::STG_WARP_BYTES;
+    uint32_t lphase0 = 0, lphase1 = 0;  // GLU backward: phases of this warp's two load barriers
     TileWalker<GROUPK, CTA2> walker(p, ctrl->tile_start, rank);
-    TileCoord t;
+    TileCoord t, t_next;
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
-    while (ok && walker.next(t)) {
+    bool has_tile = walker.next(t);
+    // GLU backward: the pre-activation blocks of a tile are requested into L2 one tile ahead of their use, so the
+    // epilogue's small TMA loads find them there instead of paying DRAM latency eight times per tile
+    auto prefetch_preact = [&](const TileCoord& tc) {
+      if (EPI == EPI_GLUBWD && lane < 16) {
+        const int c = lane & 7;
+        const int col = tc.n_block * BN + c * 32;
+        if (col < p.n_cols) {
+          tma_prefetch_l2_3d(&tmC2, (lane < 8 ? 0 : p.glu_h) + col, tc.m_tile * BM + quarter * 32, 0);
+        }
+      }
+    };
+    if (has_tile) prefetch_preact(t);
+    while (ok && has_tile) {
+      const bool has_next = walker.next(t_next);
+      if (has_next) prefetch_preact(t_next);
       const int row0 = t.m_tile * BM + quarter * 32;  // first row of this warp's 32-row slab
       const int zdim = GROUPK ? t.group : 0;
       const bool have_acc = t.k_blocks > 0;
+      if (EPI == EPI_GLUBWD && lane == 0) {
+        // both load buffers are free at a tile boundary: request chunks 0 and 1 before waiting for the MMAs
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          const int col = t.n_block * BN + c * 32;
+          if (col < p.n_cols) {
+            const uint32_t lb = smem_u32(&ctrl->epi_load_bar[warp - 2][c]);
+            mbar_expect_tx(lb, 2 * STG_ARRAY_BYTES);
+            tma_load_3d(stg + c * 2 * STG_ARRAY_BYTES, &tmC2, lb, col, row0, 0);
+            tma_load_3d(stg + (c * 2 + 1) * STG_ARRAY_BYTES, &tmC2, lb, p.glu_h + col, row0, 0);
+          }
+        }
+      }
       if (have_acc) {
         ok = mbar_wait_bounded(smem_u32(&ctrl->acc_full_bar[acc]), acc_phase, abort_flag, p.status,
                                FFM_STATUS_WAIT_EPILOGUE, p.wait_cycles);
@@ -503,6 +559,74 @@ ffm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             }
           }
         }
+      } else if (EPI == EPI_GLUBWD) {
+        // dAct tile -> (d gate | d up): per 32-column chunk the saved gate and up pre-activations stream in by TMA
+        // (double-buffered, one chunk ahead), the accumulator is rounded to bf16 as the unfused path stores it,
+        // and the two gradient blocks leave through the staging buffers.
+        // staging per warp: [load0 gate][load0 up][load1 gate][load1 up][store d_gate][store d_up]
+        const int n0 = t.n_block * BN;
+        const uint32_t lbar[2] = {smem_u32(&ctrl->epi_load_bar[warp - 2][0]), smem_u32(&ctrl->epi_load_bar[warp - 2][1])};
+        uint32_t v[2][32];
+        tmem_ld_32x32(taddr, v[0]);
+#pragma unroll
+        for (int c = 0; c < BN / 32; ++c) {
+          tmem_ld_wait();
+          if (c + 1 < BN / 32) tmem_ld_32x32(taddr + (c + 1) * 32, v[(c + 1) & 1]);
+          if (ok && n0 + c * 32 < p.n_cols) {
+            uint32_t& lph = (c & 1) ? lphase1 : lphase0;
+            ok = mbar_wait_bounded(lbar[c & 1], lph, abort_flag, p.status, FFM_STATUS_WAIT_EPILOGUE, p.wait_cycles);
+            ok = __all_sync(0xffffffffu, ok ? 1 : 0) != 0;
+            lph ^= 1u;
+            if (ok) {
+              const uint32_t lb = stg + (c & 1) * 2 * STG_ARRAY_BYTES;
+              uint4 gq[4], uq[4];
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                gq[q] = ld_shared_v4(lb + stg_offset(lane, q));
+                uq[q] = ld_shared_v4(lb + STG_ARRAY_BYTES + stg_offset(lane, q));
+              }
+              __syncwarp();  // the whole warp holds this buffer's rows in registers: it can be refilled
+              if (lane == 0 && c + 2 < BN / 32 && n0 + (c + 2) * 32 < p.n_cols) {
+                mbar_expect_tx(lbar[c & 1], 2 * STG_ARRAY_BYTES);
+                tma_load_3d(lb, &tmC2, lbar[c & 1], n0 + (c + 2) * 32, row0, 0);
+                tma_load_3d(lb + STG_ARRAY_BYTES, &tmC2, lbar[c & 1], p.glu_h + n0 + (c + 2) * 32, row0, 0);
+              }
+              uint32_t dg[16], du[16];
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const uint32_t gw4[4] = {gq[q].x, gq[q].y, gq[q].z, gq[q].w};
+                const uint32_t uw4[4] = {uq[q].x, uq[q].y, uq[q].z, uq[q].w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  const int j = q * 8 + 2 * i;
+                  const float2 a = unpack_bf16x2(pack_bf16x2(__uint_as_float(v[c & 1][j]), __uint_as_float(v[c & 1][j + 1])));
+                  const float2 gg = unpack_bf16x2(gw4[i]);
+                  const float2 uu = unpack_bf16x2(uw4[i]);
+                  const float2 r0 = glu_bwd(p.act, a.x, gg.x, uu.x);
+                  const float2 r1 = glu_bwd(p.act, a.y, gg.y, uu.y);
+                  dg[q * 4 + i] = pack_bf16x2(r0.x, r1.x);
+                  du[q * 4 + i] = pack_bf16x2(r0.y, r1.y);
+                }
+              }
+              if (lane == 0) bulk_wait_read0();
+              __syncwarp();
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const uint32_t o = stg_offset(lane, q);
+                st_shared_v4(stg + 4 * STG_ARRAY_BYTES + o, dg[4 * q], dg[4 * q + 1], dg[4 * q + 2], dg[4 * q + 3]);
+                st_shared_v4(stg + 5 * STG_ARRAY_BYTES + o, du[4 * q], du[4 * q + 1], du[4 * q + 2], du[4 * q + 3]);
+              }
+              fence_proxy_async();
+              __syncwarp();
+              if (lane == 0) {
+                tma_store_3d(&tmC, stg + 4 * STG_ARRAY_BYTES, n0 + c * 32, row0, 0);
+                tma_store_3d(&tmC, stg + 5 * STG_ARRAY_BYTES, p.glu_h + n0 + c * 32, row0, 0);
+                bulk_commit();
+              }
+            }
+          }
+        }
+        if (!ok) break;
       } else {
         // eight 32-column chunks, TMEM loads one chunk ahead, two staging buffers in rotation
         const int n0 = t.n_block * BN;
@@ -558,6 +682,8 @@ ffm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           acc_phase ^= 1u;
         }
       }
+      t = t_next;
+      has_tile = has_next;
     }
     if (lane == 0) bulk_wait0();  // this lane's bulk stores have landed before the CTA's shared memory goes away
   }
@@ -658,7 +784,7 @@ int launch_gemm_shape(const CUtensorMap& tmA, const CUtensorMap& tmB0, const CUt
                       const CUtensorMap& tmC2, const GemmParams& p, long long max_units, cudaStream_t stream) {
   static int max_ctas = 0;  // persistent grid size, found once per instantiation
   auto kernel = ffm_gemm_kernel<A_MN, B_MN, EPI, GROUPK, CTA2>;
-  constexpr int smem_bytes = Shape<CTA2>::SMEM_BYTES;
+  constexpr int smem_bytes = Shape<CTA2, EPI>::SMEM_BYTES;
   if (max_ctas == 0) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess) {
       cudaGetLastError();
@@ -840,4 +966,36 @@ extern "C" int ffm_grouped_gemm_wgrad(const void* A, const void* B, int groups, 
   return launch_gemm<1, 1, EPI_PLAIN, 1>(tmA, tmB, tmB, tmC, tmC, p, p.m_tiles_per_group,
                                          static_cast<long long>(groups) * p.n_tiles,
                                          static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int ffm_grouped_gemm_dact_glu(const void* A, const void* w_down, int groups, const int32_t* tile_start,
+                                         int64_t rows, int K, int H, int activation, const void* preact, void* gU,
+                                         int32_t* status, ffm_stream_t stream) {
+  if (!A || !w_down || !preact || !gU || !status) return FFM_ERR_BAD_ARG;
+  if (groups < 1 || groups > MAX_GROUPS || rows < 0 || K <= 0 || H <= 0) return FFM_ERR_BAD_ARG;
+  if (activation < 0 || activation > 3) return FFM_ERR_BAD_ARG;
+  if (tile_start == nullptr && groups != 1) return FFM_ERR_BAD_ARG;
+  if (K % 64 != 0 || H % 64 != 0) return FFM_ERR_UNSUPPORTED;
+  if (rows == 0) return FFM_OK;
+  CUtensorMap tmA, tmB, tmC, tmC2;
+  int rc;
+  if ((rc = make_map_2d(&tmA, A, rows, K, 64, 128)) != FFM_OK) return rc;
+  if ((rc = make_map_2d(&tmB, w_down, static_cast<long long>(groups) * K, H, 64, 64)) != FFM_OK) return rc;
+  if ((rc = make_out_map(&tmC, gU, 1, rows, 2LL * H)) != FFM_OK) return rc;
+  if ((rc = make_out_map(&tmC2, const_cast<void*>(preact), 1, rows, 2LL * H)) != FFM_OK) return rc;
+  GemmParams p = {};
+  p.tile_start = tile_start;
+  p.groups = groups;
+  p.dense_m_tiles = static_cast<int>((rows + BM - 1) / BM);
+  p.n_cols = H;
+  p.k_blocks = K / BK;
+  p.b_group_rows = K;
+  p.glu_h = H;
+  p.scale = 1.0f;
+  p.act = activation;
+  p.n_tiles = (H + BN - 1) / BN;
+  p.status = status;
+  p.wait_cycles = g_wait_cycles;
+  return launch_gemm<0, 1, EPI_GLUBWD, 0>(tmA, tmB, tmB, tmC, tmC2, p, (rows + BM - 1) / BM, p.n_tiles,
+                                          static_cast<cudaStream_t>(stream));
 }

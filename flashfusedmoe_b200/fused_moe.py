@@ -132,12 +132,14 @@ def _to(t, dtype):
     return t if t.is_contiguous() else t.contiguous()
 
 
-def _dense_ts(rows, device):
-    """tile_start for a single dense group of `rows` rows (cached per size; a tiny host-to-device copy)."""
-    key = (torch.device(device).index, int(rows))
+def _dense_ts(rows, device, split=1):
+    """tile_start for dense rows treated as `split` consecutive groups of 128-row tiles (cached per size; a tiny
+    host-to-device copy)."""
+    key = (torch.device(device).index, int(rows), split)
     t = _dense_tile_start.get(key)
     if t is None:
-        t = torch.tensor([0, (rows + 127) // 128], dtype=torch.int32, device=device)
+        tiles = (rows + 127) // 128
+        t = torch.tensor([tiles * i // split for i in range(split + 1)], dtype=torch.int32, device=device)
         _dense_tile_start[key] = t
     return t
 
@@ -190,7 +192,13 @@ def _glu_ffn_backward(go, x, act, pre, w_gate, w_up, w_down, activation):
     dx = ops.grouped_gemm(gU, w_cat, _lib.B_NMAJOR, 1, None, 2 * Hs, D)
     ts = _dense_ts(x.shape[0], x.device)
     d_wcat = ops.grouped_gemm_wgrad(gU, x, 1, ts)[0]
-    d_wdown = ops.grouped_gemm_wgrad(go, act, 1, ts)[0]
+    # [D, Hs] has few output tiles (32 CTA-pair tiles at D = 1024, Hs = 2048 for 74 pairs): split the token
+    # dimension in two halves, each accumulated in fp32, and add the two bf16 results
+    tiles = (x.shape[0] + 127) // 128
+    if tiles >= 64 and (D // 256) * ((Hs + 255) // 256) <= 40:
+        d_wdown = ops.grouped_gemm_wgrad(go, act, 2, _dense_ts(x.shape[0], x.device, split=2)).sum(dim=0)
+    else:
+        d_wdown = ops.grouped_gemm_wgrad(go, act, 1, ts)[0]
     return dx, d_wcat[:Hs], d_wcat[Hs:], d_wdown
 
 
@@ -299,6 +307,8 @@ class _FusedMoEFunction(torch.autograd.Function):
         go = _to(grad_out, h.dtype)  # also densifies expanded (stride-0) gradients
 
         gYw, gw = ops.combine_backward(go, Y, topk_w, src, ctx.rows_cap, k)
+        # (ops.grouped_gemm_dact_glu fuses these two, bit-identically, but is slower today: its epilogue issues
+        # four small TMA transfers per 32-column chunk and becomes TMA-issue-bound)
         d_act = ops.grouped_gemm(gYw, wd, _lib.B_NMAJOR, E, tile_start, D, H)
         gU = ops.glu_backward(d_act, pre, tile_start, E, cfg.activation)
         dXg = ops.grouped_gemm(gU, wu, _lib.B_NMAJOR, E, tile_start, 2 * H, D)
