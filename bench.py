@@ -53,14 +53,48 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clock / throttle-reason samples every 200 ms while the timed region runs."""
+    """SM clock, power and throttle reasons of one GPU, sampled while the timed regions run.
+
+    NVML from a thread every 10 ms (the device is looked up by the UUID torch reports, so CUDA_VISIBLE_DEVICES
+    does not matter); `nvidia-smi -lms 200` as a fallback where the NVML binding is missing. Read-only."""
+
+    REASONS = (("hw_slowdown", "nvmlClocksEventReasonHwSlowdown"),
+               ("hw_thermal_slowdown", "nvmlClocksEventReasonHwThermalSlowdown"),
+               ("sw_thermal_slowdown", "nvmlClocksEventReasonSwThermalSlowdown"),
+               ("sw_power_cap", "nvmlClocksEventReasonSwPowerCap"))
 
     def __init__(self, gpu_index):
-        self.proc = None
         self.gpu_index = gpu_index
+        self.proc = None
+        self.thread = None
+        self.samples = []     # (sm_mhz, power_w, reason bit mask)
         self.path = f"/tmp/ffm_bench_clocks_{os.getpid()}.csv"
 
+    def _nvml_loop(self, nv, handle):
+        while not self.stop_flag.is_set():
+            try:
+                self.samples.append((nv.nvmlDeviceGetClockInfo(handle, nv.NVML_CLOCK_SM),
+                                     nv.nvmlDeviceGetPowerUsage(handle) / 1000.0,
+                                     nv.nvmlDeviceGetCurrentClocksEventReasons(handle)))
+            except nv.NVMLError:
+                pass
+            self.stop_flag.wait(0.01)
+
     def start(self):
+        try:
+            import threading
+            import pynvml as nv
+            nv.nvmlInit()
+            uuid = "GPU-" + str(torch.cuda.get_device_properties(self.gpu_index).uuid)
+            handle = nv.nvmlDeviceGetHandleByUUID(uuid)
+            self.nv, self.handle = nv, handle
+            self.sm_max = nv.nvmlDeviceGetMaxClockInfo(handle, nv.NVML_CLOCK_SM)
+            self.stop_flag = threading.Event()
+            self.thread = threading.Thread(target=self._nvml_loop, args=(nv, handle), daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.thread = None
         try:
             self.out = open(self.path, "w")
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={SMI_QUERY}", "--format=csv,noheader,nounits",
@@ -70,6 +104,20 @@ class ClockSampler:
             self.proc = None
 
     def stop(self):
+        if self.thread is not None:
+            self.stop_flag.set()
+            self.thread.join(timeout=2)
+            nv = self.nv
+            sm = [s[0] for s in self.samples]
+            # samples taken while the GPU drew real power are the ones "under load"
+            busy = [s[0] for s in self.samples if s[1] >= 300.0] or sm
+            mask = 0
+            for s in self.samples:
+                mask |= s[2]
+            reasons = sorted(name for name, const in self.REASONS if mask & getattr(nv, const))
+            return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": float(self.sm_max),
+                    "sm_mhz_min": min(sm) if sm else None, "power_w_max": max((s[1] for s in self.samples), default=None),
+                    "samples": len(sm), "samples_under_load": len(busy), "source": "nvml 10 ms", "reasons": reasons}
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         time.sleep(0.25)
@@ -97,7 +145,7 @@ class ClockSampler:
         except OSError:
             pass
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+                "samples": len(sm), "source": "nvidia-smi 200 ms", "reasons": sorted(reasons)}
 
 
 def build_layer(device, ep_group):
@@ -320,7 +368,7 @@ def main():
         peaks = measured_peaks()
         fl = algorithmic_flops(tokens, world)
         kt = timer.totals_ms()
-        gemm_names = ("gemm_up_glu", "gemm", "gemm_wgrad", "gemm_dact_glu")
+        gemm_names = ("gemm_up_glu", "gemm", "gemm_wgrad")
         gemm_ms = sum(kt[n][1] for n in gemm_names if n in kt)
         gemm_launches = sum(kt[n][0] for n in gemm_names if n in kt)
         achieved = fl["gemm"] * K / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else None

@@ -9,7 +9,7 @@
 // Two tile shapes from one template:
 //   CTA2 = 0   one CTA per 128 x 256 tile, tcgen05.mma.cta_group::1, 4 stages of (A 16 KiB + B 32 KiB)
 //   CTA2 = 1   a cluster of two CTAs per 256 x 256 tile, tcgen05.mma.cta_group::2 issued by the even CTA.
-//              Each CTA stages its own 128 rows of A and its own 128-column half of B (6 stages of 32 KiB), so
+//              Each CTA stages its own 128 rows of A and its own 128-column half of B (5-6 stages of 32 KiB), so
 //              every byte of B is read from shared memory once for 256 rows of output instead of once for 128.
 //              Both CTAs' loads complete on the even CTA's "full" barrier; MMA completion is committed to the
 //              "empty" and "accumulator full" barriers of both CTAs; the odd CTA's epilogue hands its
@@ -26,9 +26,10 @@
 //   MN-major operand (rows = K index, 64 contiguous M/N elements per row):    box {64, 64 rows} per 64 columns
 //       descriptor: LBO = 8192 B between 64-column blocks, SBO = 1024 B between 8-row K groups;
 //       K step of 16 rows = +2048 B on the start address
-// Output staging: per epilogue warp three 32-row x 64-byte buffers with the 64-byte swizzle
-// (16-byte chunk index ^= (row >> 1) & 3), stored with box {32 columns, 32 rows, 1}; stores clip at the
-// tensor extents, so ragged row and column edges need no masking.
+// Output staging: every epilogue warp owns a few 32-row x 128-byte boxes (64 bf16 columns) with the 128-byte
+// swizzle (16-byte chunk index ^= row & 7), stored with box {64 columns, 32 rows, 1}; stores clip at the tensor
+// extents, so ragged row and column edges need no masking. A plain epilogue rotates two boxes per warp; the GLU
+// epilogue fills three (activation, gate, up) per 64-column step.
 #include <stdlib.h>
 
 #include "ffm_common.cuh"
@@ -47,23 +48,41 @@ constexpr int GEMM_THREADS = 192;
 constexpr int EPI_WARPS = 4;
 constexpr int MAX_GROUPS = 256;
 constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KiB
-constexpr int STG_ARRAY_BYTES = 32 * 64;    // one staged block: 32 rows x 32 bf16
+constexpr int BOX_BYTES = 32 * 128;  // one staged box: 32 rows x 64 bf16
 constexpr int SMEM_CTRL_BYTES = 2048;
 constexpr int MAX_STAGES = 6;
+constexpr int SMEM_LIMIT = 232448;  // 227 KiB of dynamic shared memory per CTA
 
-enum { EPI_PLAIN = 0, EPI_GLU = 1, EPI_GLUBWD = 2 };
+enum { EPI_PLAIN = 0, EPI_GLU = 1 };
 
-// Shared-memory budget per tile shape and epilogue. The GLU-backward epilogue also streams the saved
-// pre-activations in (two double-buffered blocks per warp), so it gives up one ring stage for staging space.
+// Ring depth against staging depth for CTA pairs (measured at 8 x 4096 rows, D 1024, H 2048: every split from
+// 4 to 6 stages runs within 2 % of the others; the GEMMs sit at the board's power limit, not at a pipeline limit).
+#ifndef FFM_TUNE_PP_STAGES
+#define FFM_TUNE_PP_STAGES 6
+#define FFM_TUNE_PP_STEPS 2
+#endif
+#ifndef FFM_TUNE_PG_STAGES
+#define FFM_TUNE_PG_STAGES 5
+#define FFM_TUNE_PG_STEPS 1
+#endif
+
+// Shared-memory budget per tile shape and epilogue: ring stages against staging boxes per epilogue warp.
+//   CTA pair, plain: 6 stages x 32 KiB + 2 boxes    CTA pair, GLU: 5 stages x 32 KiB + 3 boxes
+//   one CTA,  plain: 4 stages x 48 KiB + 2 boxes    one CTA,  GLU: 3 stages x 48 KiB + 3 boxes
+// A GLU step stores three boxes (activation, gate, up) as one bulk group; a plain step stores one box.
 template <int CTA2, int EPI>
 struct Shape {
-  static constexpr int STAGES = (CTA2 ? 6 : 4) - (EPI == EPI_GLUBWD ? 1 : 0);
+  static constexpr int STAGES = EPI == EPI_GLU ? (CTA2 ? FFM_TUNE_PG_STAGES : 3) : (CTA2 ? FFM_TUNE_PP_STAGES : 4);
   static constexpr int B_STAGE_BYTES = (CTA2 ? 128 : 256) * BK * 2;
   static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
   static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
-  static constexpr int STG_WARP_BYTES = (EPI == EPI_GLUBWD ? 6 : 3) * STG_ARRAY_BYTES;
+  static constexpr int BOXES_PER_STEP = EPI == EPI_GLU ? 3 : 1;
+  static constexpr int STEPS_BUFFERED = EPI == EPI_GLU ? (CTA2 ? FFM_TUNE_PG_STEPS : 1) : (CTA2 ? FFM_TUNE_PP_STEPS : 2);
+  static constexpr int STG_WARP_BYTES = BOXES_PER_STEP * STEPS_BUFFERED * BOX_BYTES;
   static constexpr int STG_BYTES = EPI_WARPS * STG_WARP_BYTES;
   static constexpr int SMEM_BYTES = RING_BYTES + STG_BYTES + SMEM_CTRL_BYTES + 1024;  // + 1 KiB alignment slack
+  static_assert(SMEM_BYTES <= SMEM_LIMIT, "tile shape does not fit in shared memory");
+  static_assert(STAGES <= MAX_STAGES, "ring deeper than the barrier arrays");
 };
 
 struct GemmParams {
@@ -89,7 +108,6 @@ struct Ctrl {
   unsigned long long empty_bar[MAX_STAGES];
   unsigned long long acc_full_bar[NUM_ACC];
   unsigned long long acc_empty_bar[NUM_ACC];
-  unsigned long long epi_load_bar[EPI_WARPS][2];  // GLU-backward epilogue: pre-activation blocks have landed
   uint32_t tmem_base;
   int abort_flag;
   int tile_start[MAX_GROUPS + 1];
@@ -201,8 +219,11 @@ __device__ __forceinline__ void tma_store_3d(const void* map, uint32_t src, int 
                : "memory");
 }
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait_read1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
+// wait until at most N of this thread's bulk store groups have not finished reading shared memory
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
 __device__ __forceinline__ void bulk_wait0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
 __device__ __forceinline__ void tmem_alloc2(uint32_t slot_smem_addr, uint32_t cols) {
@@ -234,28 +255,8 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t cluster_bar) {
                : "memory");
 }
 
-// 16-byte chunk q of row r inside a 32-row x 64-byte block with the 64-byte TMA swizzle
-__device__ __forceinline__ uint32_t stg_offset(int r, int q) { return r * 64 + ((q ^ ((r >> 1) & 3)) << 4); }
-
-__device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
-  uint4 v;
-  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
-  return v;
-}
-
-// 3-D TMA load of one {32 columns, 32 rows, 1} block into this CTA's shared memory, completing on a local mbarrier
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* map, uint32_t bar, int c0, int c1, int c2) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(dst),
-      "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
-      : "memory");
-}
-
-// Ask for one {32, 32, 1} block of a tensor map to be brought into L2 (no shared-memory destination).
-__device__ __forceinline__ void tma_prefetch_l2_3d(const void* map, int c0, int c1, int c2) {
-  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];" ::"l"(map), "r"(c0), "r"(c1), "r"(c2)
-               : "memory");
-}
+// 16-byte chunk q (0..7) of row r inside a 32-row x 128-byte box with the 128-byte TMA swizzle
+__device__ __forceinline__ uint32_t box_offset(int r, int q) { return r * 128 + ((q ^ (r & 7)) << 4); }
 
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
@@ -292,10 +293,6 @@ ffm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     for (int a = 0; a < NUM_ACC; ++a) {
       mbar_init(smem_u32(&ctrl->acc_full_bar[a]), 1);
       mbar_init(smem_u32(&ctrl->acc_empty_bar[a]), EPI_WARPS * (CTA2 ? 2 : 1));  // one arrival per epilogue warp
-    }
-    for (int w = 0; w < EPI_WARPS; ++w) {
-      mbar_init(smem_u32(&ctrl->epi_load_bar[w][0]), 1);
-      mbar_init(smem_u32(&ctrl->epi_load_bar[w][1]), 1);
     }
     ctrl->abort_flag = 0;
     fence_barrier_init();
@@ -465,44 +462,17 @@ ffm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     // ================= epilogue (warps 2..5) =================
     const int quarter = warp & 3;  // TMEM lanes [32 * quarter, 32 * quarter + 32) belong to this warp
     const uint32_t stg = stg_base + (warp - 2) * S::STG_WARP_BYTES;
-    uint32_t lphase0 = 0, lphase1 = 0;  // GLU backward: phases of this warp's two load barriers
+    constexpr int STEP_BYTES = S::BOXES_PER_STEP * BOX_BYTES;
+    int step_slot = 0;  // staging slot of the next store step; advances per step actually stored
     TileWalker<GROUPK, CTA2> walker(p, ctrl->tile_start, rank);
-    TileCoord t, t_next;
+    TileCoord t;
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
-    bool has_tile = walker.next(t);
-    // GLU backward: the pre-activation blocks of a tile are requested into L2 one tile ahead of their use, so the
-    // epilogue's small TMA loads find them there instead of paying DRAM latency eight times per tile
-    auto prefetch_preact = [&](const TileCoord& tc) {
-      if (EPI == EPI_GLUBWD && lane < 16) {
-        const int c = lane & 7;
-        const int col = tc.n_block * BN + c * 32;
-        if (col < p.n_cols) {
-          tma_prefetch_l2_3d(&tmC2, (lane < 8 ? 0 : p.glu_h) + col, tc.m_tile * BM + quarter * 32, 0);
-        }
-      }
-    };
-    if (has_tile) prefetch_preact(t);
-    while (ok && has_tile) {
-      const bool has_next = walker.next(t_next);
-      if (has_next) prefetch_preact(t_next);
+    while (ok && walker.next(t)) {
       const int row0 = t.m_tile * BM + quarter * 32;  // first row of this warp's 32-row slab
       const int zdim = GROUPK ? t.group : 0;
       const bool have_acc = t.k_blocks > 0;
-      if (EPI == EPI_GLUBWD && lane == 0) {
-        // both load buffers are free at a tile boundary: request chunks 0 and 1 before waiting for the MMAs
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          const int col = t.n_block * BN + c * 32;
-          if (col < p.n_cols) {
-            const uint32_t lb = smem_u32(&ctrl->epi_load_bar[warp - 2][c]);
-            mbar_expect_tx(lb, 2 * STG_ARRAY_BYTES);
-            tma_load_3d(stg + c * 2 * STG_ARRAY_BYTES, &tmC2, lb, col, row0, 0);
-            tma_load_3d(stg + (c * 2 + 1) * STG_ARRAY_BYTES, &tmC2, lb, p.glu_h + col, row0, 0);
-          }
-        }
-      }
       if (have_acc) {
         ok = mbar_wait_bounded(smem_u32(&ctrl->acc_full_bar[acc]), acc_phase, abort_flag, p.status,
                                FFM_STATUS_WAIT_EPILOGUE, p.wait_cycles);
@@ -513,7 +483,8 @@ ffm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
 
       if (EPI == EPI_GLU) {
-        // four 32-column chunks of gate and up; the TMEM loads of chunk c + 1 fly while chunk c is processed
+        // two steps of 64 GLU columns, each two 32-column chunks of gate and up; the TMEM loads of chunk c + 1 fly
+        // while chunk c is processed. A step fills three boxes (activation, gate, up) and stores them as one group.
         const int h0 = t.n_block * 128;
         uint32_t g[2][32], u[2][32];
         tmem_ld_32x32(taddr, g[0]);
@@ -525,114 +496,54 @@ ffm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             tmem_ld_32x32(taddr + (c + 1) * 32, g[(c + 1) & 1]);
             tmem_ld_32x32(taddr + 128 + (c + 1) * 32, u[(c + 1) & 1]);
           }
-          if (h0 + c * 32 < p.n_cols) {
-            uint32_t pg[16], pu[16], pa[16];
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              pg[i] = pack_bf16x2(__uint_as_float(g[c & 1][2 * i]), __uint_as_float(g[c & 1][2 * i + 1]));
-              pu[i] = pack_bf16x2(__uint_as_float(u[c & 1][2 * i]), __uint_as_float(u[c & 1][2 * i + 1]));
-              const float2 gf = unpack_bf16x2(pg[i]);
-              const float2 uf = unpack_bf16x2(pu[i]);
-              pa[i] = pack_bf16x2(glu_fwd(p.act, gf.x, uf.x), glu_fwd(p.act, gf.y, uf.y));
+          const int col = h0 + (c >> 1) * 64;  // first GLU column of this step's boxes
+          if (col < p.n_cols) {
+            const uint32_t buf = stg + step_slot * STEP_BYTES;
+            if ((c & 1) == 0) {
+              // the slot is free once the step stored STEPS_BUFFERED steps ago has been read out
+              if (lane == 0) bulk_wait_read<S::STEPS_BUFFERED - 1>();
+              __syncwarp();
             }
-            // the staging buffers are free once the previous chunk's bulk stores have read them
-            if (lane == 0) bulk_wait_read0();
-            __syncwarp();
+            if (h0 + c * 32 < p.n_cols) {
+              uint32_t pg[16], pu[16], pa[16];
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const uint32_t o = stg_offset(lane, q);
-              st_shared_v4(stg + o, pa[4 * q], pa[4 * q + 1], pa[4 * q + 2], pa[4 * q + 3]);
-              if (p.has_c2) {
-                st_shared_v4(stg + STG_ARRAY_BYTES + o, pg[4 * q], pg[4 * q + 1], pg[4 * q + 2], pg[4 * q + 3]);
-                st_shared_v4(stg + 2 * STG_ARRAY_BYTES + o, pu[4 * q], pu[4 * q + 1], pu[4 * q + 2], pu[4 * q + 3]);
+              for (int i = 0; i < 16; ++i) {
+                pg[i] = pack_bf16x2(__uint_as_float(g[c & 1][2 * i]), __uint_as_float(g[c & 1][2 * i + 1]));
+                pu[i] = pack_bf16x2(__uint_as_float(u[c & 1][2 * i]), __uint_as_float(u[c & 1][2 * i + 1]));
+                const float2 gf = unpack_bf16x2(pg[i]);
+                const float2 uf = unpack_bf16x2(pu[i]);
+                pa[i] = pack_bf16x2(glu_fwd(p.act, gf.x, uf.x), glu_fwd(p.act, gf.y, uf.y));
               }
-            }
-            fence_proxy_async();
-            __syncwarp();
-            if (lane == 0) {
-              tma_store_3d(&tmC, stg, h0 + c * 32, row0, 0);
-              if (p.has_c2) {
-                tma_store_3d(&tmC2, stg + STG_ARRAY_BYTES, h0 + c * 32, row0, 0);
-                tma_store_3d(&tmC2, stg + 2 * STG_ARRAY_BYTES, p.glu_h + h0 + c * 32, row0, 0);
-              }
-              bulk_commit();
-            }
-          }
-        }
-      } else if (EPI == EPI_GLUBWD) {
-        // dAct tile -> (d gate | d up): per 32-column chunk the saved gate and up pre-activations stream in by TMA
-        // (double-buffered, one chunk ahead), the accumulator is rounded to bf16 as the unfused path stores it,
-        // and the two gradient blocks leave through the staging buffers.
-        // staging per warp: [load0 gate][load0 up][load1 gate][load1 up][store d_gate][store d_up]
-        const int n0 = t.n_block * BN;
-        const uint32_t lbar[2] = {smem_u32(&ctrl->epi_load_bar[warp - 2][0]), smem_u32(&ctrl->epi_load_bar[warp - 2][1])};
-        uint32_t v[2][32];
-        tmem_ld_32x32(taddr, v[0]);
-#pragma unroll
-        for (int c = 0; c < BN / 32; ++c) {
-          tmem_ld_wait();
-          if (c + 1 < BN / 32) tmem_ld_32x32(taddr + (c + 1) * 32, v[(c + 1) & 1]);
-          if (ok && n0 + c * 32 < p.n_cols) {
-            uint32_t& lph = (c & 1) ? lphase1 : lphase0;
-            ok = mbar_wait_bounded(lbar[c & 1], lph, abort_flag, p.status, FFM_STATUS_WAIT_EPILOGUE, p.wait_cycles);
-            ok = __all_sync(0xffffffffu, ok ? 1 : 0) != 0;
-            lph ^= 1u;
-            if (ok) {
-              const uint32_t lb = stg + (c & 1) * 2 * STG_ARRAY_BYTES;
-              uint4 gq[4], uq[4];
 #pragma unroll
               for (int q = 0; q < 4; ++q) {
-                gq[q] = ld_shared_v4(lb + stg_offset(lane, q));
-                uq[q] = ld_shared_v4(lb + STG_ARRAY_BYTES + stg_offset(lane, q));
-              }
-              __syncwarp();  // the whole warp holds this buffer's rows in registers: it can be refilled
-              if (lane == 0 && c + 2 < BN / 32 && n0 + (c + 2) * 32 < p.n_cols) {
-                mbar_expect_tx(lbar[c & 1], 2 * STG_ARRAY_BYTES);
-                tma_load_3d(lb, &tmC2, lbar[c & 1], n0 + (c + 2) * 32, row0, 0);
-                tma_load_3d(lb + STG_ARRAY_BYTES, &tmC2, lbar[c & 1], p.glu_h + n0 + (c + 2) * 32, row0, 0);
-              }
-              uint32_t dg[16], du[16];
-#pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                const uint32_t gw4[4] = {gq[q].x, gq[q].y, gq[q].z, gq[q].w};
-                const uint32_t uw4[4] = {uq[q].x, uq[q].y, uq[q].z, uq[q].w};
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                  const int j = q * 8 + 2 * i;
-                  const float2 a = unpack_bf16x2(pack_bf16x2(__uint_as_float(v[c & 1][j]), __uint_as_float(v[c & 1][j + 1])));
-                  const float2 gg = unpack_bf16x2(gw4[i]);
-                  const float2 uu = unpack_bf16x2(uw4[i]);
-                  const float2 r0 = glu_bwd(p.act, a.x, gg.x, uu.x);
-                  const float2 r1 = glu_bwd(p.act, a.y, gg.y, uu.y);
-                  dg[q * 4 + i] = pack_bf16x2(r0.x, r1.x);
-                  du[q * 4 + i] = pack_bf16x2(r0.y, r1.y);
+                const uint32_t o = box_offset(lane, (c & 1) * 4 + q);
+                st_shared_v4(buf + o, pa[4 * q], pa[4 * q + 1], pa[4 * q + 2], pa[4 * q + 3]);
+                if (p.has_c2) {
+                  st_shared_v4(buf + BOX_BYTES + o, pg[4 * q], pg[4 * q + 1], pg[4 * q + 2], pg[4 * q + 3]);
+                  st_shared_v4(buf + 2 * BOX_BYTES + o, pu[4 * q], pu[4 * q + 1], pu[4 * q + 2], pu[4 * q + 3]);
                 }
               }
-              if (lane == 0) bulk_wait_read0();
-              __syncwarp();
-#pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                const uint32_t o = stg_offset(lane, q);
-                st_shared_v4(stg + 4 * STG_ARRAY_BYTES + o, dg[4 * q], dg[4 * q + 1], dg[4 * q + 2], dg[4 * q + 3]);
-                st_shared_v4(stg + 5 * STG_ARRAY_BYTES + o, du[4 * q], du[4 * q + 1], du[4 * q + 2], du[4 * q + 3]);
-              }
+            }
+            if (c & 1) {
               fence_proxy_async();
               __syncwarp();
               if (lane == 0) {
-                tma_store_3d(&tmC, stg + 4 * STG_ARRAY_BYTES, n0 + c * 32, row0, 0);
-                tma_store_3d(&tmC, stg + 5 * STG_ARRAY_BYTES, p.glu_h + n0 + c * 32, row0, 0);
+                tma_store_3d(&tmC, buf, col, row0, 0);
+                if (p.has_c2) {
+                  tma_store_3d(&tmC2, buf + BOX_BYTES, col, row0, 0);
+                  tma_store_3d(&tmC2, buf + 2 * BOX_BYTES, p.glu_h + col, row0, 0);
+                }
                 bulk_commit();
               }
+              if (++step_slot == S::STEPS_BUFFERED) step_slot = 0;
             }
           }
         }
-        if (!ok) break;
       } else {
-        // eight 32-column chunks, TMEM loads one chunk ahead, two staging buffers in rotation
+        // four steps of 64 columns (one box each), two 32-column chunks per step, TMEM loads one chunk ahead
         const int n0 = t.n_block * BN;
         const float scale = p.scale;
         uint32_t v[2][32];
-        int slot = 0;  // staging buffer of the next store; toggles per store actually issued
         if (have_acc) tmem_ld_32x32(taddr, v[0]);
 #pragma unroll
         for (int c = 0; c < BN / 32; ++c) {
@@ -640,27 +551,34 @@ ffm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             tmem_ld_wait();
             if (c + 1 < BN / 32) tmem_ld_32x32(taddr + (c + 1) * 32, v[(c + 1) & 1]);
           }
-          if (n0 + c * 32 < p.n_cols) {
-            uint32_t o[16];
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              o[i] = have_acc ? pack_bf16x2(__uint_as_float(v[c & 1][2 * i]) * scale,
-                                            __uint_as_float(v[c & 1][2 * i + 1]) * scale)
-                              : 0u;
+          const int col = n0 + (c >> 1) * 64;  // first column of this step's box
+          if (col < p.n_cols) {
+            const uint32_t buf = stg + step_slot * STEP_BYTES;
+            if ((c & 1) == 0) {
+              if (lane == 0) bulk_wait_read<S::STEPS_BUFFERED - 1>();
+              __syncwarp();
             }
-            const uint32_t buf = stg + slot * STG_ARRAY_BYTES;
-            slot ^= 1;
-            if (lane == 0) bulk_wait_read1();  // the store issued two stores ago has read this buffer
-            __syncwarp();
+            if (n0 + c * 32 < p.n_cols) {
+              uint32_t o[16];
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              st_shared_v4(buf + stg_offset(lane, q), o[4 * q], o[4 * q + 1], o[4 * q + 2], o[4 * q + 3]);
+              for (int i = 0; i < 16; ++i) {
+                o[i] = have_acc ? pack_bf16x2(__uint_as_float(v[c & 1][2 * i]) * scale,
+                                              __uint_as_float(v[c & 1][2 * i + 1]) * scale)
+                                : 0u;
+              }
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                st_shared_v4(buf + box_offset(lane, (c & 1) * 4 + q), o[4 * q], o[4 * q + 1], o[4 * q + 2], o[4 * q + 3]);
+              }
             }
-            fence_proxy_async();
-            __syncwarp();
-            if (lane == 0) {
-              tma_store_3d(&tmC, buf, n0 + c * 32, row0, zdim);
-              bulk_commit();
+            if (c & 1) {
+              fence_proxy_async();
+              __syncwarp();
+              if (lane == 0) {
+                tma_store_3d(&tmC, buf, col, row0, zdim);
+                bulk_commit();
+              }
+              if (++step_slot == S::STEPS_BUFFERED) step_slot = 0;
             }
           }
         }
@@ -682,8 +600,6 @@ ffm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           acc_phase ^= 1u;
         }
       }
-      t = t_next;
-      has_tile = has_next;
     }
     if (lane == 0) bulk_wait0();  // this lane's bulk stores have landed before the CTA's shared memory goes away
   }
@@ -741,7 +657,7 @@ int make_map_2d(CUtensorMap* map, const void* base, long long rows, long long co
   return r == CUDA_SUCCESS ? FFM_OK : FFM_ERR_LAUNCH;
 }
 
-// 3-D bf16 output map over [groups, rows, cols] (row-major, contiguous), 64-byte swizzle, box {32, 32, 1}.
+// 3-D bf16 output map over [groups, rows, cols] (row-major, contiguous), 128-byte swizzle, box {64, 32, 1}.
 int make_out_map(CUtensorMap* map, void* base, long long groups, long long rows, long long cols) {
   EncodeTiledFn fn = get_encode_fn();
   if (fn == nullptr) return FFM_ERR_NO_DRIVER;
@@ -749,10 +665,10 @@ int make_out_map(CUtensorMap* map, void* base, long long groups, long long rows,
   if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0 || (cols * 2) % 16 != 0) return FFM_ERR_UNSUPPORTED;
   cuuint64_t dims[3] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(groups)};
   cuuint64_t strides[2] = {static_cast<cuuint64_t>(cols) * 2, static_cast<cuuint64_t>(cols) * rows * 2};
-  cuuint32_t box[3] = {32, 32, 1};
+  cuuint32_t box[3] = {64, 32, 1};
   cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, base, dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? FFM_OK : FFM_ERR_LAUNCH;
 }
@@ -873,7 +789,7 @@ extern "C" int ffm_grouped_gemm_glu(const void* A, const void* w_gate, const voi
   if (groups < 1 || groups > MAX_GROUPS || rows < 0 || K <= 0 || H <= 0 || group_rows < H) return FFM_ERR_BAD_ARG;
   if (activation < 0 || activation > 3) return FFM_ERR_BAD_ARG;
   if (tile_start == nullptr && groups != 1) return FFM_ERR_BAD_ARG;
-  if (K % 64 != 0 || H % 32 != 0) return FFM_ERR_UNSUPPORTED;
+  if (K % 64 != 0 || H % 64 != 0) return FFM_ERR_UNSUPPORTED;  // a 64-column box of gate must not reach into up
   if (rows == 0) return FFM_OK;
   CUtensorMap tmA, tmB0, tmB1, tmC, tmC2;
   int rc;
@@ -966,36 +882,4 @@ extern "C" int ffm_grouped_gemm_wgrad(const void* A, const void* B, int groups, 
   return launch_gemm<1, 1, EPI_PLAIN, 1>(tmA, tmB, tmB, tmC, tmC, p, p.m_tiles_per_group,
                                          static_cast<long long>(groups) * p.n_tiles,
                                          static_cast<cudaStream_t>(stream));
-}
-
-extern "C" int ffm_grouped_gemm_dact_glu(const void* A, const void* w_down, int groups, const int32_t* tile_start,
-                                         int64_t rows, int K, int H, int activation, const void* preact, void* gU,
-                                         int32_t* status, ffm_stream_t stream) {
-  if (!A || !w_down || !preact || !gU || !status) return FFM_ERR_BAD_ARG;
-  if (groups < 1 || groups > MAX_GROUPS || rows < 0 || K <= 0 || H <= 0) return FFM_ERR_BAD_ARG;
-  if (activation < 0 || activation > 3) return FFM_ERR_BAD_ARG;
-  if (tile_start == nullptr && groups != 1) return FFM_ERR_BAD_ARG;
-  if (K % 64 != 0 || H % 64 != 0) return FFM_ERR_UNSUPPORTED;
-  if (rows == 0) return FFM_OK;
-  CUtensorMap tmA, tmB, tmC, tmC2;
-  int rc;
-  if ((rc = make_map_2d(&tmA, A, rows, K, 64, 128)) != FFM_OK) return rc;
-  if ((rc = make_map_2d(&tmB, w_down, static_cast<long long>(groups) * K, H, 64, 64)) != FFM_OK) return rc;
-  if ((rc = make_out_map(&tmC, gU, 1, rows, 2LL * H)) != FFM_OK) return rc;
-  if ((rc = make_out_map(&tmC2, const_cast<void*>(preact), 1, rows, 2LL * H)) != FFM_OK) return rc;
-  GemmParams p = {};
-  p.tile_start = tile_start;
-  p.groups = groups;
-  p.dense_m_tiles = static_cast<int>((rows + BM - 1) / BM);
-  p.n_cols = H;
-  p.k_blocks = K / BK;
-  p.b_group_rows = K;
-  p.glu_h = H;
-  p.scale = 1.0f;
-  p.act = activation;
-  p.n_tiles = (H + BN - 1) / BN;
-  p.status = status;
-  p.wait_cycles = g_wait_cycles;
-  return launch_gemm<0, 1, EPI_GLUBWD, 0>(tmA, tmB, tmB, tmC, tmC2, p, (rows + BM - 1) / BM, p.n_tiles,
-                                          static_cast<cudaStream_t>(stream));
 }

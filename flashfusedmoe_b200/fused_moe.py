@@ -307,8 +307,6 @@ class _FusedMoEFunction(torch.autograd.Function):
         go = _to(grad_out, h.dtype)  # also densifies expanded (stride-0) gradients
 
         gYw, gw = ops.combine_backward(go, Y, topk_w, src, ctx.rows_cap, k)
-        # (ops.grouped_gemm_dact_glu fuses these two, bit-identically, but is slower today: its epilogue issues
-        # four small TMA transfers per 32-column chunk and becomes TMA-issue-bound)
         d_act = ops.grouped_gemm(gYw, wd, _lib.B_NMAJOR, E, tile_start, D, H)
         gU = ops.glu_backward(d_act, pre, tile_start, E, cfg.activation)
         dXg = ops.grouped_gemm(gU, wu, _lib.B_NMAJOR, E, tile_start, 2 * H, D)

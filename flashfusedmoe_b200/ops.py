@@ -254,22 +254,6 @@ def grouped_gemm_wgrad(A, B, groups, tile_start, scale=1.0):
     return out
 
 
-def grouped_gemm_dact_glu(A, w_down, groups, tile_start, K, H, activation, preact):
-    """gU = glu_backward(A @ w_down[e], preact) in one kernel; A [rows, K], w_down [groups, K, H] -> [rows, 2H]."""
-    lib = _lib.load()
-    _req(A, torch.bfloat16, "A")
-    _req(w_down, torch.bfloat16, "w_down")
-    _req(preact, torch.bfloat16, "preact")
-    rows = A.shape[0]
-    gU = torch.empty(rows, 2 * H, dtype=torch.bfloat16, device=A.device)
-    with _Launch("gemm_dact_glu", 1):
-        rc = lib.ffm_grouped_gemm_dact_glu(_ptr(A), _ptr(w_down), groups, _ptr(tile_start), rows, K, H,
-                                           _lib.ACTIVATION[activation], _ptr(preact), _ptr(gU),
-                                           _ptr(status_tensor(A.device)), _stream())
-    _lib.check(rc, "ffm_grouped_gemm_dact_glu")
-    return gU
-
-
 def combine_forward(Y, pos, w, N, top_k, addend=None):
     lib = _lib.load()
     _req(Y, torch.bfloat16, "Y")

@@ -52,7 +52,6 @@ def main():
                         4.0 * T * D * H),
         "gemm_down": (lambda: ops.grouped_gemm(act, Wd, _lib.B_KMAJOR, E, ts, H, D), 2.0 * T * D * H),
         "gemm_dact": (lambda: ops.grouped_gemm(X, Wd, _lib.B_NMAJOR, E, ts, D, H), 2.0 * T * D * H),
-        "gemm_dact_glu": (lambda: ops.grouped_gemm_dact_glu(X, Wd, E, ts, D, H, "swiglu", pre), 2.0 * T * D * H),
         "gemm_dx": (lambda: ops.grouped_gemm(gU, Wu, _lib.B_NMAJOR, E, ts, 2 * H, D), 4.0 * T * D * H),
         "gemm_wgrad_down": (lambda: ops.grouped_gemm_wgrad(X, act, E, ts), 2.0 * T * D * H),
         "gemm_wgrad_up": (lambda: ops.grouped_gemm_wgrad(gU, X, E, ts), 4.0 * T * D * H),

@@ -168,7 +168,7 @@ int ffm_permute_rows(const void* x, const int32_t* src, int64_t rows_cap, int to
  *   as the reference's bf16 bmm output is. w_gate / w_up are [groups * group_rows, K] row-major with the
  *   group's gate rows starting at row e * group_rows of w_gate and its up rows at e * group_rows of w_up;
  *   for stacked expert weights pass w_gate = w_up_tensor, w_up = w_up_tensor + H * K, group_rows = 2H.
- *   Limits: K % 64 == 0, H % 32 == 0.
+ *   Limits: K % 64 == 0, H % 64 == 0.
  *
  * ffm_grouped_gemm: out[r, 0:Nout] = scale * A[r, :] * op(B[e]).
  *   Replaces the down-projection bmm (fused_moe.py:441) and the input-gradient bmms (:547, :553).
@@ -186,18 +186,6 @@ int ffm_grouped_gemm(const void* A, const void* B, int b_major, int groups, cons
                      int64_t rows, int K, int Nout, float scale, void* out, int32_t* status, ffm_stream_t stream);
 int ffm_grouped_gemm_wgrad(const void* A, const void* B, int groups, const int32_t* tile_start, int64_t rows_cap,
                            int M, int Nout, float scale, void* dW, int32_t* status, ffm_stream_t stream);
-
-/* ffm_grouped_gemm_dact_glu: gU[r, 0:H] = d gate, gU[r, H:2H] = d up of dAct[r, :] = A[r, :] * w_down[e]
- *   (w_down stored [groups * K, H], i.e. FFM_B_NMAJOR) through the GLU backward, with the saved pre-activations
- *   streamed into the epilogue. One kernel for the bmm + activation_backward pair of the reference
- *   (fused_moe.py:547-550, kernels/activations.py:78-142); dAct is rounded to bf16 before the activation gradient, as
- *   the reference's bf16 bmm output is, so the result equals ffm_grouped_gemm followed by ffm_glu_backward bit for
- *   bit. Measured slower than the two-kernel sequence at the benchmark shapes (0.37 ms against 0.21 ms at
- *   configs[1]): the epilogue's 64-byte-wide TMA transfers are issue-bound. Kept for callers that prefer one launch
- *   and less memory traffic; the Python layer uses the two-kernel sequence. Limits: K % 64 == 0, H % 64 == 0. */
-int ffm_grouped_gemm_dact_glu(const void* A, const void* w_down, int groups, const int32_t* tile_start, int64_t rows,
-                              int K, int H, int activation, const void* preact, void* gU, int32_t* status,
-                              ffm_stream_t stream);
 
 /* -------------------------------------------------------------------------------------------------
  * Combine forward: out[n, :] = sum_j w[n, j] * Y[pos[n k + j], :] (+ addend[n, :]), fp32 accumulation.

@@ -221,7 +221,7 @@ def glu_ref(act, g, u):
 
 
 @pytest.mark.parametrize("activation", ["swiglu", "geglu", "relu_squared", "geglu_erf"])
-@pytest.mark.parametrize("counts,K,H", [([5, 0, 200, 128], 64, 64), ([300, 17, 129, 64], 128, 160),
+@pytest.mark.parametrize("counts,K,H", [([5, 0, 200, 128], 64, 64), ([300, 17, 129, 64], 128, 192),
                                         ([2048] * 8, 1024, 2048)])
 def test_grouped_gemm_glu(counts, K, H, activation):
     if activation != "swiglu" and H > 1000:
@@ -331,35 +331,3 @@ def test_route_backward(N, D, E, k, gating):
     dG_ref = gl.T @ hidden.float()
     assert rel_err(dH, dH_ref) < 2e-2
     assert rel_err(dGate, dG_ref) < 2e-2
-
-
-@pytest.mark.parametrize("activation", ["swiglu", "geglu", "relu_squared", "geglu_erf"])
-@pytest.mark.parametrize("counts,K,H", [([5, 0, 200, 128], 64, 64), ([300, 17, 129, 64], 128, 192),
-                                        ([2048] * 8, 1024, 2048)])
-def test_grouped_gemm_dact_glu_equals_unfused(counts, K, H, activation):
-    """The fused dAct + GLU-backward GEMM is bit-identical to the GEMM followed by the stand-alone GLU backward."""
-    if activation != "swiglu" and H > 1000:
-        pytest.skip("large shape once")
-    torch.manual_seed(H + 3)
-    A, ts, row_expert, rows_cap = _grouped_case(counts, K)
-    E = len(counts)
-    Wd = (torch.randn(E, K, H, device=DEV) * 0.05).bfloat16()
-    pre = torch.randn(rows_cap, 2 * H, device=DEV).bfloat16()
-    fused = ops.grouped_gemm_dact_glu(A, Wd, E, ts, K, H, activation, pre)
-    d_act = ops.grouped_gemm(A, Wd, _lib.B_NMAJOR, E, ts, K, H)
-    ref = ops.glu_backward(d_act, pre, ts, E, activation)
-    ops.check_status()
-    used = int(ts[-1].item()) * 128
-    assert torch.equal(fused[:used], ref[:used])
-
-
-def test_dense_dact_glu_ragged_rows():
-    torch.manual_seed(9)
-    rows, K, H = 300, 128, 320
-    A = torch.randn(rows, K, device=DEV).bfloat16()
-    Wd = (torch.randn(K, H, device=DEV) * 0.05).bfloat16()
-    pre = torch.randn(rows, 2 * H, device=DEV).bfloat16()
-    fused = ops.grouped_gemm_dact_glu(A, Wd, 1, None, K, H, "swiglu", pre)
-    ref = ops.glu_backward(ops.grouped_gemm(A, Wd, _lib.B_NMAJOR, 1, None, K, H), pre, None, 1, "swiglu")
-    ops.check_status()
-    assert torch.equal(fused, ref)
