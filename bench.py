@@ -52,80 +52,104 @@ def measured_peaks():
     return dict(tflops=1400.0, tflops_burst=1590.0, hbm_gbs=6650.0, source="fallback")
 
 
+_SAMPLER_SCRIPT = r"""
+import sys, time
+import pynvml as nv
+nv.nvmlInit()
+h = nv.nvmlDeviceGetHandleByUUID(sys.argv[1])
+out = open(sys.argv[2], "w")
+out.write("max,%d\n" % nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM))
+out.flush()
+while True:
+    try:
+        out.write("%.4f,%d,%.1f,%d\n" % (time.time(), nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM),
+                                          nv.nvmlDeviceGetPowerUsage(h) / 1000.0,
+                                          nv.nvmlDeviceGetCurrentClocksEventReasons(h)))
+        out.flush()
+    except nv.NVMLError:
+        pass
+    time.sleep(0.01)
+"""
+
+
 class ClockSampler:
-    """SM clock, power and throttle reasons of one GPU, sampled while the timed regions run.
+    """SM clock, power and throttle reasons of one GPU while the timed regions run. Read-only.
 
-    NVML from a thread every 10 ms (the device is looked up by the UUID torch reports, so CUDA_VISIBLE_DEVICES
-    does not matter); `nvidia-smi -lms 200` as a fallback where the NVML binding is missing. Read-only."""
+    A child process polls NVML every 10 ms from before the warm-up (the device is looked up by the UUID torch
+    reports, so CUDA_VISIBLE_DEVICES does not matter) and stamps every sample with the wall clock; begin() and
+    stop() bracket the timed regions and only samples between them are used. A child process rather than a thread:
+    the step loop is close to CPU-bound at N > 1 and must not share the interpreter lock with the sampler.
+    `nvidia-smi -lms 200` is the fallback where the NVML binding is missing."""
 
-    REASONS = (("hw_slowdown", "nvmlClocksEventReasonHwSlowdown"),
-               ("hw_thermal_slowdown", "nvmlClocksEventReasonHwThermalSlowdown"),
-               ("sw_thermal_slowdown", "nvmlClocksEventReasonSwThermalSlowdown"),
-               ("sw_power_cap", "nvmlClocksEventReasonSwPowerCap"))
+    REASON_BITS = (("hw_slowdown", 0x8), ("hw_thermal_slowdown", 0x40), ("sw_thermal_slowdown", 0x20),
+                   ("sw_power_cap", 0x4))
 
     def __init__(self, gpu_index):
         self.gpu_index = gpu_index
         self.proc = None
-        self.thread = None
-        self.samples = []     # (sm_mhz, power_w, reason bit mask)
+        self.mode = None
+        self.t_begin = None
         self.path = f"/tmp/ffm_bench_clocks_{os.getpid()}.csv"
-
-    def _nvml_loop(self, nv, handle):
-        while not self.stop_flag.is_set():
-            try:
-                self.samples.append((nv.nvmlDeviceGetClockInfo(handle, nv.NVML_CLOCK_SM),
-                                     nv.nvmlDeviceGetPowerUsage(handle) / 1000.0,
-                                     nv.nvmlDeviceGetCurrentClocksEventReasons(handle)))
-            except nv.NVMLError:
-                pass
-            self.stop_flag.wait(0.01)
 
     def start(self):
         try:
-            import threading
-            import pynvml as nv
-            nv.nvmlInit()
+            import pynvml  # noqa: F401  (only to know whether the child can import it)
             uuid = "GPU-" + str(torch.cuda.get_device_properties(self.gpu_index).uuid)
-            handle = nv.nvmlDeviceGetHandleByUUID(uuid)
-            self.nv, self.handle = nv, handle
-            self.sm_max = nv.nvmlDeviceGetMaxClockInfo(handle, nv.NVML_CLOCK_SM)
-            self.stop_flag = threading.Event()
-            self.thread = threading.Thread(target=self._nvml_loop, args=(nv, handle), daemon=True)
-            self.thread.start()
+            self.proc = subprocess.Popen([sys.executable, "-c", _SAMPLER_SCRIPT, uuid, self.path],
+                                         stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL)
+            self.mode = "nvml"
             return
         except Exception:
-            self.thread = None
+            self.proc = None
         try:
             self.out = open(self.path, "w")
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={SMI_QUERY}", "--format=csv,noheader,nounits",
                                           "-lms", "200", "-i", str(self.gpu_index)], stdout=self.out,
                                          stderr=subprocess.DEVNULL)
+            self.mode = "smi"
         except OSError:
             self.proc = None
 
-    def stop(self):
-        if self.thread is not None:
-            self.stop_flag.set()
-            self.thread.join(timeout=2)
-            nv = self.nv
-            sm = [s[0] for s in self.samples]
-            # samples taken while the GPU drew real power are the ones "under load"
-            busy = [s[0] for s in self.samples if s[1] >= 300.0] or sm
-            mask = 0
-            for s in self.samples:
-                mask |= s[2]
-            reasons = sorted(name for name, const in self.REASONS if mask & getattr(nv, const))
-            return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": float(self.sm_max),
-                    "sm_mhz_min": min(sm) if sm else None, "power_w_max": max((s[1] for s in self.samples), default=None),
-                    "samples": len(sm), "samples_under_load": len(busy), "source": "nvml 10 ms", "reasons": reasons}
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.25)
+    def begin(self):
+        self.t_begin = time.time()
+
+    def _end_child(self):
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
+
+    def stop(self):
+        t_end = time.time()
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no clock source available"]}
+        if self.mode == "nvml":
+            self._end_child()
+            sm_max, samples = None, []
+            try:
+                for line in open(self.path):
+                    f = line.strip().split(",")
+                    if f[0] == "max":
+                        sm_max = float(f[1])
+                    elif len(f) == 4 and (self.t_begin or 0.0) <= float(f[0]) <= t_end:
+                        samples.append((int(f[1]), float(f[2]), int(f[3])))
+                os.remove(self.path)
+            except (OSError, ValueError):
+                pass
+            if sm_max is not None and samples:
+                sm = [s[0] for s in samples]
+                busy = [s[0] for s in samples if s[1] >= 300.0] or sm   # samples taken while the GPU drew real power
+                mask = 0
+                for s in samples:
+                    mask |= s[2]
+                return {"sm_mhz": statistics.median(busy), "sm_max_mhz": sm_max, "sm_mhz_min": min(sm),
+                        "power_w_max": max(s[1] for s in samples), "samples": len(sm), "samples_under_load": len(busy),
+                        "source": "nvml, child process, 10 ms",
+                        "reasons": sorted(n for n, bit in self.REASON_BITS if mask & bit)}
+            return {"sm_mhz": None, "sm_max_mhz": sm_max, "samples": 0, "reasons": ["no NVML samples in the timed window"]}
+        time.sleep(0.25)
+        self._end_child()
         self.out.close()
         sm, smax, reasons = [], [], set()
         for line in open(self.path):
@@ -273,14 +297,16 @@ def main():
             torch.cuda.synchronize()
 
     # ---- device-resident timing --------------------------------------------------------------
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.start()   # the child starts polling during the warm-up; only samples after begin() count
     for _ in range(W):
         step()
     ops.check_status()
-    sampler = ClockSampler(local_rank) if rank == 0 else None
     timer = ops.KernelTimer()
     fence()
     if sampler:
-        sampler.start()
+        sampler.begin()
     launches0 = ops.launch_count
     t0 = torch.cuda.Event(enable_timing=True)
     t1 = torch.cuda.Event(enable_timing=True)
@@ -302,6 +328,28 @@ def main():
     fence()
     ops.set_timer(None)
     a2a_bytes = ops.a2a_bytes_sent - a2a_bytes0
+
+    # ---- expert parallel only: K steps whose row exchanges move nothing (everything else runs) -----------------
+    # step time minus this = the exchange time that compute did not hide
+    dry_ms = None
+    if world > 1:
+        import sys as _sys
+        fm = _sys.modules["flashfusedmoe_b200.fused_moe"]
+        fm.set_ep_dry_exchange(True)
+        for _ in range(2):
+            step()
+        fence()
+        d0 = torch.cuda.Event(enable_timing=True)
+        d1 = torch.cuda.Event(enable_timing=True)
+        d0.record()
+        for _ in range(K):
+            step()
+        d1.record()
+        fence()
+        fm.set_ep_dry_exchange(False)
+        dry_ms = d0.elapsed_time(d1)
+        step()   # one real step: the receive buffers hold real rows again
+        fence()
 
     # ---- end to end: pinned host input in, loss scalar out, every step ------------------------
     # The loop a training script would run around the public API: the next step's input is uploaded on a copy
@@ -359,10 +407,10 @@ def main():
     e2e_ms = e0.elapsed_time(e1)
     clocks = sampler.stop() if sampler else None  # sampled from the start of the timed region to here
 
-    t = torch.tensor([ms, e2e_ms], device=device, dtype=torch.float64)
+    t = torch.tensor([ms, e2e_ms, dry_ms if dry_ms is not None else 0.0], device=device, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms, e2e_ms = float(t[0]), float(t[1])
+    ms, e2e_ms, dry_ms = float(t[0]), float(t[1]), float(t[2])
 
     if rank == 0:
         peaks = measured_peaks()
@@ -414,6 +462,12 @@ def main():
                                        "bytes_sent_per_step": a2a_bytes / K, "achieved_gbs_per_direction": gbs,
                                        "nvlink_frac_of_770": (gbs / 770.0) if gbs else None,
                                        "share_of_step_in_kernel_pass": (a2a_ms / K) / (ms / K),
+                                       # exposed = step time minus the time of the same step with exchanges that move
+                                       # nothing; hidden = 1 - exposed / (event time of the exchanges)
+                                       "ms_per_step_without_exchange_payload": dry_ms / K,
+                                       "exposed_exchange_ms_per_step": max(0.0, (ms - dry_ms) / K),
+                                       "hidden_frac": (min(1.0, max(0.0, 1.0 - (ms - dry_ms) / a2a_ms))
+                                                       if a2a_ms > 0 else None),
                                        "transport": os.environ.get("FFM_EP_TRANSPORT", "p2p")}
         if world == 1 and not args.no_cpu_baseline:
             threads = os.cpu_count() or 1

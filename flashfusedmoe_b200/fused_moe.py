@@ -44,6 +44,15 @@ _AUX_LOSS_GRAD = "analytic"
 # torch.distributed all_to_all_single. Chosen by FFM_EP_TRANSPORT at import; p2p falls back to nccl per call when
 # symmetric memory is unavailable or a receive would not fit.
 _EP_TRANSPORT = os.environ.get("FFM_EP_TRANSPORT", "p2p")
+# Measurement aid: when set, the row exchanges move nothing (the receive buffers keep whatever they held) while
+# every other kernel of the step still runs; the difference against a normal step is the exposed exchange time.
+_EP_DRY_EXCHANGE = False
+
+
+def set_ep_dry_exchange(enable):
+    """Benchmark switch: skip the payload of the expert-parallel exchanges (results are then meaningless)."""
+    global _EP_DRY_EXCHANGE
+    _EP_DRY_EXCHANGE = bool(enable)
 
 _side_streams = {}
 _dense_tile_start = {}
@@ -224,6 +233,7 @@ class _GLUFFNFunction(torch.autograd.Function):
         return dx.to(dt[0]), dwg.to(dt[1]), dwu.to(dt[2]), dwd.to(dt[3]), None, None
 
 
+@torch.compiler.disable
 def glu_ffn(x, w_gate, w_up, w_down, activation="swiglu"):
     """Dense GLU feed-forward on the library's GEMM kernels. x [N, D] -> [N, D]."""
     dtype = _require_bf16(_get_compute_dtype(x.dtype))
@@ -358,9 +368,11 @@ class _EPPlan:
         cnt = self.cnt_t if reverse else self.cnt
         if self.px is not None and self.px.fits(max(sum(cnt[s][d] for s in range(self.ep)) for d in range(self.ep)),
                                                 rows.shape[1] * rows.element_size()):
-            return self.px.exchange(rows, cnt, region), True
+            return self.px.exchange(rows, cnt, region, dry=_EP_DRY_EXCHANGE), True
         in_splits = cnt[self.rank]
         out_splits = [cnt[s][self.rank] for s in range(self.ep)]
+        if _EP_DRY_EXCHANGE:
+            return rows.new_zeros(sum(out_splits), rows.shape[1]), False
         ops.a2a_bytes_sent += (sum(in_splits) - in_splits[self.rank]) * rows.shape[1] * rows.element_size()
         with ops._Launch("all_to_all", 0):
             return all_to_all_rows(rows, out_splits, in_splits, self.group), False

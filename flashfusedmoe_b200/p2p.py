@@ -59,14 +59,18 @@ class PeerExchange:
     def fits(self, max_rows, row_bytes):
         return max_rows * row_bytes <= self.region_bytes
 
-    def exchange(self, rows, counts, region):
+    def exchange(self, rows, counts, region, dry=False):
         """rows [sum_d counts[rank][d], W] ordered by destination; counts[s][d] = rows rank s sends to rank d
         (host lists, identical on every rank). Returns a [M, W] view of this rank's receive region, valid until the
-        next exchange that uses the same region."""
+        next exchange that uses the same region. dry=True (measurement aid) launches nothing and returns the view."""
         lib = _lib.load()
         W = rows.shape[1]
         row_bytes = W * rows.element_size()
         r, n = self.rank, self.world
+        if dry:
+            M = sum(counts[s][r] for s in range(n))
+            lo = FLAG_BYTES + region * self.region_bytes
+            return self.buf[lo:lo + M * row_bytes].view(rows.dtype).view(M, W)
         src = (ctypes.c_void_p * n)()
         dst = (ctypes.c_void_p * n)()
         nbytes = (ctypes.c_int64 * n)()
@@ -81,7 +85,7 @@ class PeerExchange:
             send_off += cnt
         ops.a2a_bytes_sent += (send_off - counts[r][r]) * row_bytes
         M = sum(counts[s][r] for s in range(n))
-        stream = torch.cuda.current_stream().cuda_stream
+        stream = ops._stream()
         with ops._Launch("all_to_all", 2):
             if send_off > 0:
                 _lib.check(lib.ffm_p2p_push(n, src, dst, nbytes, stream), "ffm_p2p_push")

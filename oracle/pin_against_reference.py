@@ -7,7 +7,8 @@ through Triton's CPU interpreter; its autotuner is told to run each candidate on
     python oracle/pin_against_reference.py [reference_dir]
 
 Outputs: tests/golden/routing_rule.pt, tests/golden/layer_small_fp32.pt, tests/golden/layer_small_bf16.pt,
-tests/golden/layer_config1_fp32.pt (sub-sampled weight gradients), and a printed table of oracle-vs-reference
+tests/golden/layer_config1_fp32.pt (sub-sampled weight gradients), tests/golden/layer_variants_fp32.pt,
+tests/golden/module_state_dict_layout.json, tests/golden/module_checkpoint_bf16.pt, and a printed table of oracle-vs-reference
 errors that must all be within the bounds asserted below.
 """
 
@@ -167,8 +168,48 @@ def pin_variants():
     torch.save(gold, os.path.join(GOLD, "layer_variants_fp32.pt"))
 
 
+def pin_module():
+    """Reference MoELayer: parameter names and shapes per constructor variant, and one bf16 checkpoint with a shared
+    expert run forward + backward through the unmodified module (checkpoint interchange, nn.py:56-176)."""
+    import json
+    from flashfusemoe import MoELayer as RefLayer
+    variants = {
+        "base": dict(),
+        "shared": dict(num_shared_experts=1),
+        "latent": dict(latent_dim=32),
+        "shared_latent_sigmoid": dict(num_shared_experts=2, latent_dim=32, gating="sigmoid", activation="geglu"),
+    }
+    layout = {}
+    for name, kw in variants.items():
+        layer = RefLayer(64, 128, 8, 2, **kw)
+        layout[name] = dict(kwargs=kw, params={n: list(t.shape) for n, t in layer.state_dict().items()})
+    with open(os.path.join(GOLD, "module_state_dict_layout.json"), "w") as f:
+        json.dump(layout, f, indent=1, sort_keys=True)
+
+    torch.manual_seed(31)
+    layer = RefLayer(64, 128, 8, 2, num_shared_experts=1, aux_loss_coeff=0.01, z_loss_coeff=0.001)
+    with torch.no_grad():
+        for prm in layer.parameters():
+            prm.normal_(0.0, 0.05)
+    layer = layer.bfloat16()
+    x = torch.randn(2, 48, 64).bfloat16().requires_grad_()
+    go = torch.randn(2, 48, 64).bfloat16()
+    out, losses = layer(x)
+    loss = (out.float() * go.float()).sum() + losses["aux_loss"] + losses["z_loss"]
+    loss.backward()
+    gold = dict(ctor=dict(d_model=64, ffn_dim=128, num_experts=8, top_k=2, num_shared_experts=1, aux_loss_coeff=0.01,
+                          z_loss_coeff=0.001),
+                state_dict={n: t.detach().clone() for n, t in layer.state_dict().items()},
+                x=x.detach().clone(), go=go, out=out.detach().clone(), dx=x.grad.clone(),
+                losses={n: float(v.detach()) for n, v in losses.items() if n in ("aux_loss", "z_loss")},
+                grads={n: prm.grad.clone() for n, prm in layer.named_parameters()})
+    torch.save(gold, os.path.join(GOLD, "module_checkpoint_bf16.pt"))
+    print("module layout and checkpoint written:", sorted(layout["shared_latent_sigmoid"]["params"]))
+
+
 if __name__ == "__main__":
     pin_routing_rule()
+    pin_module()
     pin_variants()
     combos = [("swiglu", "softmax", 0.01, 0.001), ("geglu", "softmax", 0.0, 0.0), ("relu_squared", "sigmoid", 0.01, 0.001),
               ("swiglu", "sigmoid", 0.0, 0.0)]
