@@ -4,6 +4,10 @@
 //
 //   p2p_push_kernel     copies up to FFM_P2P_MAX_PEERS contiguous segments of the local send buffer to
 //                       (peer base + offset); blockIdx.y selects the segment.
+//   p2p_rows_kernel     the same copy at row granularity, driven by a table of segments in device memory
+//                       {first source row, first destination row, rows, destination buffer}: one warp per row finds
+//                       its segment by binary search on the running row count. The source row may be looked up
+//                       through an index (gather from the token matrix), or be absent (the rows are zeroed).
 //   p2p_signal_kernel   after the push (stream order), every rank stores the exchange's epoch into slot [my_rank]
 //                       of every peer's flag array (release, system scope) and then waits until its own slots
 //                       show that epoch from every peer (acquire, system scope). Epochs only grow, so flags are
@@ -36,6 +40,53 @@ __global__ void __launch_bounds__(256) p2p_push_kernel(PushArgs a) {
     d[i + 3 * stride] = v3;
   }
   for (; i < n16; i += stride) d[i] = s[i];
+}
+
+struct RowBases {
+  uint8_t* base[FFM_P2P_MAX_PEERS];
+};
+
+__global__ void __launch_bounds__(256) p2p_rows_kernel(const uint8_t* __restrict__ src, const int32_t* __restrict__ src_index,
+                                                       int index_div, long long row_bytes,
+                                                       const long long* __restrict__ segments,
+                                                       const long long* __restrict__ seg_end, int n_segments,
+                                                       long long total_rows, RowBases bases) {
+  const int warps = blockDim.x >> 5;
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int chunks = static_cast<int>(row_bytes >> 4);
+  for (long long row = static_cast<long long>(blockIdx.x) * warps + warp; row < total_rows;
+       row += static_cast<long long>(gridDim.x) * warps) {
+    int lo = 0, hi = n_segments - 1;  // smallest segment whose running end lies beyond this row
+    while (lo < hi) {
+      const int mid = (lo + hi) >> 1;
+      if (__ldg(seg_end + mid) > row) {
+        hi = mid;
+      } else {
+        lo = mid + 1;
+      }
+    }
+    const long long j = row - (lo > 0 ? __ldg(seg_end + lo - 1) : 0LL);
+    const long long* seg = segments + 4LL * lo;
+    long long src_row = __ldg(seg) + j;
+    if (src_index != nullptr) src_row = __ldg(src_index + src_row) / index_div;
+    uint4* __restrict__ d = reinterpret_cast<uint4*>(bases.base[__ldg(seg + 3)] + (__ldg(seg + 1) + j) * row_bytes);
+    if (src != nullptr) {
+      const uint4* __restrict__ s = reinterpret_cast<const uint4*>(src + src_row * row_bytes);
+      int c = lane;
+      for (; c + 96 < chunks; c += 128) {  // four independent 16-byte copies in flight per lane
+        const uint4 v0 = s[c], v1 = s[c + 32], v2 = s[c + 64], v3 = s[c + 96];
+        d[c] = v0;
+        d[c + 32] = v1;
+        d[c + 64] = v2;
+        d[c + 96] = v3;
+      }
+      for (; c < chunks; c += 32) d[c] = s[c];
+    } else {
+      const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+      for (int c = lane; c < chunks; c += 32) d[c] = z;
+    }
+  }
 }
 
 struct SignalArgs {
@@ -94,6 +145,29 @@ extern "C" int ffm_p2p_push(int n_segments, const void* const* src, void* const*
   if (blocks < 1) blocks = 1;
   dim3 grid(static_cast<unsigned>(blocks), static_cast<unsigned>(n), 1);
   p2p_push_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  return cudaGetLastError() == cudaSuccess ? FFM_OK : FFM_ERR_LAUNCH;
+}
+
+extern "C" int ffm_p2p_push_rows(const void* src, const int32_t* src_index, int index_div, int64_t row_bytes,
+                                 const int64_t* segments, const int64_t* seg_end, int n_segments, int64_t total_rows,
+                                 void* const* dst_bases, int n_bases, ffm_stream_t stream) {
+  if (n_segments < 0 || total_rows < 0) return FFM_ERR_BAD_ARG;
+  if (n_segments == 0 || total_rows == 0) return FFM_OK;
+  if (!segments || !seg_end || !dst_bases) return FFM_ERR_BAD_ARG;
+  if (n_bases < 1 || n_bases > FFM_P2P_MAX_PEERS) return FFM_ERR_UNSUPPORTED;
+  if (row_bytes <= 0 || (row_bytes & 15) != 0) return FFM_ERR_UNSUPPORTED;
+  if (src_index != nullptr && (src == nullptr || index_div < 1)) return FFM_ERR_BAD_ARG;
+  if (src != nullptr && (reinterpret_cast<uintptr_t>(src) & 15u) != 0) return FFM_ERR_UNSUPPORTED;
+  RowBases b = {};
+  for (int i = 0; i < n_bases; ++i) {
+    if (!dst_bases[i] || (reinterpret_cast<uintptr_t>(dst_bases[i]) & 15u) != 0) return FFM_ERR_BAD_ARG;
+    b.base[i] = static_cast<uint8_t*>(dst_bases[i]);
+  }
+  long long blocks = (total_rows + 7) / 8;
+  if (blocks > 148LL * 8) blocks = 148LL * 8;
+  p2p_rows_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint8_t*>(src), src_index, index_div, row_bytes, reinterpret_cast<const long long*>(segments),
+      reinterpret_cast<const long long*>(seg_end), n_segments, total_rows, b);
   return cudaGetLastError() == cudaSuccess ? FFM_OK : FFM_ERR_LAUNCH;
 }
 

@@ -47,6 +47,9 @@ _EP_TRANSPORT = os.environ.get("FFM_EP_TRANSPORT", "p2p")
 # Measurement aid: when set, the row exchanges move nothing (the receive buffers keep whatever they held) while
 # every other kernel of the step still runs; the difference against a normal step is the exposed exchange time.
 _EP_DRY_EXCHANGE = False
+# Peer-store transport only: move rows straight into the receivers' grouped layout (FFM_EP_DIRECT=0 keeps the
+# contiguous-range exchange with a permute on either side, the layout the NCCL transport also uses).
+_EP_DIRECT = os.environ.get("FFM_EP_DIRECT", "1") != "0"
 
 
 def set_ep_dry_exchange(enable):
@@ -348,8 +351,8 @@ class _EPPlan:
         all_counts = torch.empty(ep, counts.numel(), dtype=counts.dtype, device=counts.device)
         torch.distributed.all_gather_into_tensor(all_counts, counts.contiguous(), group=group)
         self.recv_counts = all_counts[:, self.rank * e_local:(self.rank + 1) * e_local].to(torch.int64)  # [ep, E_local]
-        host = all_counts.view(ep, ep, e_local).sum(-1).tolist()
-        self.cnt = [[int(v) for v in row] for row in host]
+        C = all_counts.cpu().numpy()                      # [ep, E] rows rank s routes to expert e (the host sync)
+        self.cnt = [[int(v) for v in row] for row in C.reshape(ep, ep, e_local).sum(-1)]
         self.cnt_t = [[self.cnt[d][s] for d in range(ep)] for s in range(ep)]
         self.send_splits = self.cnt[self.rank]
         self.recv_splits = [self.cnt[s][self.rank] for s in range(ep)]
@@ -359,8 +362,48 @@ class _EPPlan:
         if _EP_TRANSPORT == "p2p" and p2p.available() and ep <= 16:
             worst = max(max(sum(self.cnt[s][d] for s in range(ep)) for d in range(ep)),
                         max(sum(self.cnt[s]) for s in range(ep)))
-            need = 1 << max(20, (2 * worst * row_bytes - 1).bit_length())  # twice the worst case, power of two
+            need = 1 << max(20, (2 * (worst + 256 * e_local) * row_bytes - 1).bit_length())  # twice the worst case
             self.px = p2p.get_exchange(group, counts.device, need)
+        # Row-granular tables: rows travel straight between the senders' expert-sorted order and the receivers'
+        # grouped layout (p2p.SegmentPlan), so neither side runs a staging permute around the exchange.
+        self.seg = None
+        if self.px is not None and _EP_DIRECT:
+            sp = p2p.SegmentPlan(C, e_local, self.rank)
+            if self.px.fits(int(max(sp.rows_grouped.max(), sp.send_rows.max())), row_bytes):
+                self.seg = sp
+                r = self.rank
+                self.rows_l = int(sp.rows_grouped[r])
+                (self.d_seg, self.d_end, self.c_seg, self.c_end, self.p_seg, self.p_end, ts) = self.px.upload(
+                    sp.dispatch[0], sp.dispatch[1], sp.combine[0], sp.combine[1], sp.padding[0], sp.padding[1],
+                    sp.tile_start[r])
+                self.ts_l = ts.to(torch.int32)
+                self.remote_dispatch = int(sp.dispatch[0][sp.dispatch[0][:, 3] != r, 2].sum())
+                self.remote_combine = int(sp.combine[0][sp.combine[0][:, 3] != r, 2].sum())
+
+    def dispatch_grouped(self, src, src_index, index_div, region):
+        """Sender order (or, with src_index, a gather from the token matrix) -> every receiver's grouped layout in
+        `region`; returns this rank's grouped rows [rows_l, W] (a view of the region; padding rows are zero)."""
+        px, sp = self.px, self.seg
+        W = src.shape[1]
+        rb = W * src.element_size()
+        dry = _EP_DRY_EXCHANGE
+        px.push_rows(src, src_index, index_div, rb, self.d_seg, self.d_end, len(sp.dispatch[0]),
+                     int(sp.send_rows[self.rank]), region, remote_rows=self.remote_dispatch, dry=dry)
+        px.push_rows(None, None, 1, rb, self.p_seg, self.p_end, len(sp.padding[0]),
+                     int(sp.padding[0][:, 2].sum()), region, name="zero_padding")
+        px.barrier(dry=dry)
+        return px.region_view(region, self.rows_l, W, src.dtype)
+
+    def combine_grouped(self, grouped, region):
+        """Grouped layout of this rank -> every origin's sender order in `region`; returns this rank's [T, W] view."""
+        px, sp = self.px, self.seg
+        W = grouped.shape[1]
+        rb = W * grouped.element_size()
+        dry = _EP_DRY_EXCHANGE
+        px.push_rows(grouped, None, 1, rb, self.c_seg, self.c_end, len(sp.combine[0]),
+                     int(sp.recv_rows[self.rank]), region, remote_rows=self.remote_combine, dry=dry)
+        px.barrier(dry=dry)
+        return px.region_view(region, int(sp.send_rows[self.rank]), W, grouped.dtype)
 
     def exchange(self, rows, reverse, region):
         """Dispatch direction (reverse=False: rows ordered by destination rank) or its inverse. The result may be a
@@ -443,27 +486,42 @@ class _FusedMoEEPFunction(torch.autograd.Function):
         plan = _EPPlan(routing.counts, ep, El, group, max(W_bytes, D * 2))
         recv_counts, M = plan.recv_counts, plan.M
         cpos, src_c = _compact_send_map(routing, T)
-        send = ops.permute_rows(disp, src_c, T, k)
-        recv, is_view = plan.exchange(send, False, 0)                          # [M, W]
-        if is_view and has_latent and need_grad:
-            recv = recv.clone()  # saved for the latent weight gradients
-
-        if M > 0:
-            local_ids = local_ids_from_counts(recv_counts, M).to(torch.int32)
-            _, ts_l, pos_l, src_l, rows_l = ops.group_rows(local_ids, El)
-        else:
-            ts_l = pos_l = src_l = None
-            rows_l = 0
+        direct = plan.seg is not None
+        pos_l = src_l = None
         recv_lat = None
-        if has_latent:
-            recv_lat = recv
-            recv = ops.grouped_gemm(recv, lwu, _lib.B_KMAJOR, 1, None, L, D) if M > 0 else recv.new_empty(0, D)
+        if direct:
+            # rows are gathered from the token matrix and stored straight into the owners' grouped layouts
+            rows_l = plan.rows_l
+            ts_l = plan.ts_l
+            recv = plan.dispatch_grouped(disp, src_c, k, 0)                      # [rows_l, W] grouped, region view
+            if need_grad:
+                recv = recv.clone()  # saved for backward; the region is overwritten by the next call
+            if has_latent:
+                recv_lat = recv
+                recv = (ops.grouped_gemm(recv, lwu, _lib.B_KMAJOR, 1, None, L, D) if rows_l > 0
+                        else recv.new_empty(0, D))
+            Xg = recv
+        else:
+            send = ops.permute_rows(disp, src_c, T, k)
+            recv, is_view = plan.exchange(send, False, 0)                          # [M, W]
+            if is_view and has_latent and need_grad:
+                recv = recv.clone()  # saved for the latent weight gradients
+            if M > 0:
+                local_ids = local_ids_from_counts(recv_counts, M).to(torch.int32)
+                _, ts_l, pos_l, src_l, rows_l = ops.group_rows(local_ids, El)
+            else:
+                ts_l = None
+                rows_l = 0
+            if has_latent:
+                recv_lat = recv
+                recv = ops.grouped_gemm(recv, lwu, _lib.B_KMAJOR, 1, None, L, D) if M > 0 else recv.new_empty(0, D)
+            Xg = ops.permute_rows(recv, src_l, rows_l, 1) if M > 0 else None
         if M > 0:
-            Xg = ops.permute_rows(recv, src_l, rows_l, 1)
             act, pre = ops.grouped_gemm_glu(Xg, wu, wu.view(-1, D)[H:], 2 * H, El, ts_l, D, H, cfg.activation,
                                             want_preact=need_grad)
             Y = ops.grouped_gemm(act, wd, _lib.B_KMAJOR, El, ts_l, H, D)
-            local_out = ops.combine_forward(Y, pos_l, None, M, 1)            # back to arrival order [M, D]
+            # direct: the grouped rows go back as they lie; otherwise back to arrival order [M, D] first
+            local_out = Y if direct else ops.combine_forward(Y, pos_l, None, M, 1)
         else:
             Xg = act = pre = None
             local_out = h.new_empty(0, D)
@@ -472,7 +530,10 @@ class _FusedMoEEPFunction(torch.autograd.Function):
             local_out = ops.grouped_gemm(local_out, lwd, _lib.B_KMAJOR, 1, None, D, L)
         elif has_latent:
             local_out = h.new_empty(0, L)
-        returned, is_view = plan.exchange(local_out, True, 1)                  # [T, W], send order
+        if direct:
+            returned, is_view = plan.combine_grouped(local_out, 1), True           # [T, W], send order
+        else:
+            returned, is_view = plan.exchange(local_out, True, 1)                  # [T, W], send order
         if is_view and need_grad:
             returned = returned.clone()  # saved for backward; the region is overwritten by the next call
         returned_lat = None
@@ -487,7 +548,7 @@ class _FusedMoEEPFunction(torch.autograd.Function):
         ctx.set_materialize_grads(False)
         ctx.cfg = cfg
         ctx.dims = (N, D, E, El, H, k, M, ep, rows_l)
-        ctx.flags = (has_shared, has_latent)
+        ctx.flags = (has_shared, has_latent, direct)
         ctx.plan = plan
         ctx.in_dtypes = tuple(None if t is None else t.dtype for t in
                               (hidden_states, gate_weight, w_up, w_down, sw_gate, sw_up, sw_down, lw_down, lw_up))
@@ -511,7 +572,7 @@ class _FusedMoEEPFunction(torch.autograd.Function):
         cfg = ctx.cfg
         group = cfg.ep_group
         N, D, E, El, H, k, M, ep, rows_l = ctx.dims
-        has_shared, has_latent = ctx.flags
+        has_shared, has_latent, direct = ctx.flags
         plan = ctx.plan
         t = dict(zip(ctx.names, ctx.saved_tensors))
         h, g, wu, wd = t["h"], t["g"], t["wu"], t["wd"]
@@ -547,7 +608,10 @@ class _FusedMoEEPFunction(torch.autograd.Function):
         ready2.record()
         with torch.cuda.stream(a2a):
             a2a.wait_event(ready2)
-            recv_grad, grad_is_view = plan.exchange(send, False, 2)
+            if direct:
+                recv_grad, grad_is_view = plan.dispatch_grouped(send, None, 1, 2), True   # grouped [rows_l, W]
+            else:
+                recv_grad, grad_is_view = plan.exchange(send, False, 2)
         a2a_done = torch.cuda.Event()
         a2a_done.record(a2a)
         send.record_stream(a2a)
@@ -566,7 +630,7 @@ class _FusedMoEEPFunction(torch.autograd.Function):
             recv_grad = (ops.grouped_gemm(recv_grad_lat, t["lwu"], _lib.B_KMAJOR, 1, None, L, D)
                          if M > 0 else recv_grad.new_empty(0, D))
         if M > 0:
-            gYg = ops.permute_rows(recv_grad, t["src_l"], rows_l, 1)
+            gYg = recv_grad if direct else ops.permute_rows(recv_grad, t["src_l"], rows_l, 1)
             d_act = ops.grouped_gemm(gYg, wd, _lib.B_NMAJOR, El, t["ts_l"], D, H)
             gU = ops.glu_backward(d_act, t["pre"], t["ts_l"], El, cfg.activation)
             d_wd = ops.grouped_gemm_wgrad(gYg, t["act"], El, t["ts_l"], scale=inv_ep)
@@ -575,7 +639,7 @@ class _FusedMoEEPFunction(torch.autograd.Function):
                 # opt-in: the expert input gradient the reference leaves out (fused_moe.py:1001-1005) travels back
                 # through a reverse dispatch exchange and is summed over each token's k slots
                 dXg = ops.grouped_gemm(gU, wu, _lib.B_NMAJOR, El, t["ts_l"], 2 * H, D)
-                dx_recv = ops.combine_forward(dXg, t["pos_l"], None, M, 1)
+                dx_recv = dXg if direct else ops.combine_forward(dXg, t["pos_l"], None, M, 1)
                 if has_latent:
                     dx_recv = ops.grouped_gemm(dx_recv, t["lwu"], _lib.B_NMAJOR, 1, None, D, L)
         else:
@@ -585,7 +649,7 @@ class _FusedMoEEPFunction(torch.autograd.Function):
             # fused_moe.py:989-999: both un-projection sites feed proj_up, the combine projection feeds proj_down
             d_lwu = ops.grouped_gemm_wgrad(gYw, t["returned_lat"], 1, _dense_ts(T, h.device), scale=inv_ep)[0]
             if M > 0:
-                ts_m = _dense_ts(M, h.device)
+                ts_m = _dense_ts(recv_grad.shape[0], h.device)   # M rows, or the grouped rows with zero padding
                 d_lwu = d_lwu + ops.grouped_gemm_wgrad(recv_grad, t["recv_lat"], 1, ts_m, scale=inv_ep)[0]
                 d_lwd = ops.grouped_gemm_wgrad(recv_grad_lat, t["local_out_D"], 1, ts_m, scale=inv_ep)[0]
             else:
@@ -594,7 +658,10 @@ class _FusedMoEEPFunction(torch.autograd.Function):
         if cfg.ep_full_input_grad:
             W = L if has_latent else D
             back = dx_recv if M > 0 else h.new_empty(0, W)
-            d_send, _ = plan.exchange(back, True, 1)                               # [T, W], send order
+            if direct:
+                d_send = plan.combine_grouped(back, 1)                             # [T, W], send order
+            else:
+                d_send, _ = plan.exchange(back, True, 1)
             d_disp = ops.combine_forward(d_send, t["cpos"], None, N, k)            # sum over the k slots
             if has_latent:
                 d_disp = ops.grouped_gemm(d_disp, t["lwd"], _lib.B_NMAJOR, 1, None, L, D)

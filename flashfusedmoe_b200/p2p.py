@@ -14,6 +14,7 @@ consumes (or copies) a region before it takes part in the exchange that could ov
 import ctypes
 import os
 
+import numpy as np
 import torch
 
 from . import _lib, ops
@@ -22,6 +23,58 @@ FLAG_BYTES = 4096
 NUM_REGIONS = 3  # dispatch, combine (also the reverse-dispatch of the full input gradient), backward
 
 _exchanges = {}
+
+
+class SegmentPlan:
+    """Row runs of one expert-parallel call between every sender's expert-sorted order and every receiver's grouped
+    layout, from the [ep, E] matrix C[s][e] = rows rank s routes to expert e (host integers, same on every rank).
+
+    Sender order (rank s): its routed rows sorted by expert, no padding; expert e starts at row send0[s][e].
+    Receiver layout (rank d, experts d*El .. (d+1)*El-1): expert segments aligned to 256 rows (tile_start in 128-row
+    tiles, as the grouped GEMM expects); inside a segment the rows of source rank 0 come first, then rank 1, ...;
+    the run of (source s, expert e) starts at row recv0[s][e] of rank (e // El).
+    Tables (int64 [n, 4] = {first source row, first destination row, rows, destination rank}, plus running ends):
+      dispatch  this rank's runs, sender order -> receivers' grouped layouts
+      combine   the runs this rank holds as expert owner, grouped layout -> the origins' sender order
+      padding   the rows between a segment's last row and the next segment of this rank's own layout (to be zeroed)
+    """
+
+    def __init__(self, C, e_local, rank):
+        C = np.asarray(C, dtype=np.int64)
+        ep, E = C.shape
+        assert E == ep * e_local
+        self.ep, self.e_local, self.rank = ep, e_local, rank
+        self.send0 = np.cumsum(C, axis=1) - C                       # [ep, E]
+        self.send_rows = C.sum(axis=1)                              # rows every rank sends (= its T)
+        R = C.sum(axis=0)                                           # rows per expert over all sources
+        tiles = 2 * ((R + 255) // 256)                              # 128-row tiles per expert segment, even
+        tiles_l = tiles.reshape(ep, e_local)
+        ts = np.zeros((ep, e_local + 1), dtype=np.int64)
+        ts[:, 1:] = np.cumsum(tiles_l, axis=1)
+        self.tile_start = ts                                        # [ep, El + 1] per destination rank
+        self.rows_grouped = ts[:, -1] * 128                         # grouped rows (with padding) per rank
+        self.recv_rows = R.reshape(ep, e_local).sum(axis=1)         # valid rows per rank (M)
+        seg0 = (ts[:, :-1] * 128).reshape(E)                        # first row of expert e's segment at its owner
+        self.recv0 = seg0[None, :] + (np.cumsum(C, axis=0) - C)     # [ep, E]
+        owner = np.arange(E) // e_local
+        r = rank
+        mine = np.nonzero(C[r] > 0)[0]
+        self.dispatch = self._table(self.send0[r, mine], self.recv0[r, mine], C[r, mine], owner[mine])
+        lo, hi = r * e_local, (r + 1) * e_local
+        sub = C[:, lo:hi]                                           # [ep, El] rows this rank receives
+        e_idx, s_idx = np.nonzero(sub.T > 0)                        # expert-major, source within expert
+        self.combine = self._table(self.recv0[s_idx, lo + e_idx], self.send0[s_idx, lo + e_idx], sub[s_idx, e_idx], s_idx)
+        end_valid = seg0[lo:hi] + R[lo:hi]
+        end_seg = ts[r, 1:] * 128
+        pad = end_seg - end_valid
+        has = np.nonzero(pad > 0)[0]
+        self.padding = self._table(np.zeros(len(has), dtype=np.int64), end_valid[has], pad[has],
+                                   np.full(len(has), r, dtype=np.int64))
+
+    @staticmethod
+    def _table(src0, dst0, rows, dst_rank):
+        seg = np.stack([src0, dst0, rows, dst_rank], axis=1).astype(np.int64).reshape(-1, 4)
+        return seg, np.cumsum(seg[:, 2]).astype(np.int64)
 
 
 def available():
@@ -95,6 +148,55 @@ class PeerExchange:
                        "ffm_p2p_signal_wait")
         lo = FLAG_BYTES + region * self.region_bytes
         return self.buf[lo:lo + M * row_bytes].view(rows.dtype).view(M, W)
+
+    def upload(self, *arrays):
+        """One host -> device copy for several int64 tables; returns device views in the same order."""
+        flat = np.concatenate([np.ascontiguousarray(a, dtype=np.int64).reshape(-1) for a in arrays])
+        if flat.size == 0:
+            flat = np.zeros(1, dtype=np.int64)
+        dev = torch.from_numpy(flat).pin_memory().to(self.buf.device, non_blocking=True)
+        out, o = [], 0
+        for a in arrays:
+            n = int(np.asarray(a).size)
+            out.append(dev[o:o + n])
+            o += n
+        return out
+
+
+    def push_rows(self, src, src_index, index_div, row_bytes, seg_dev, end_dev, n_segments, total_rows, region,
+                          remote_rows=0, dry=False, name="all_to_all"):
+        """Row runs listed in a device table (ffm_p2p_push_rows) into region `region` of the ranks named by the table.
+        src None zeroes the rows. remote_rows only feeds the byte counter."""
+        if n_segments == 0 or total_rows == 0 or dry:
+            return
+        lib = _lib.load()
+        n = self.world
+        bases = (ctypes.c_void_p * n)(*[self.region_ptr(d, region) for d in range(n)])
+        ops.a2a_bytes_sent += remote_rows * row_bytes
+        with ops._Launch(name, 1):
+            _lib.check(lib.ffm_p2p_push_rows(0 if src is None else src.data_ptr(),
+                                             0 if src_index is None else src_index.data_ptr(), int(index_div),
+                                             int(row_bytes), seg_dev.data_ptr(), end_dev.data_ptr(), int(n_segments),
+                                             int(total_rows), bases, n, ops._stream()), "ffm_p2p_push_rows")
+
+
+    def barrier(self, dry=False):
+        """Flag barrier of the group on the current stream: what the peers pushed before it is readable after it."""
+        if dry:
+            return
+        lib = _lib.load()
+        self.epoch += 1
+        with ops._Launch("all_to_all", 1):
+            _lib.check(lib.ffm_p2p_signal_wait(self._flag_ptrs, self.rank, self.world, self.epoch,
+                                               ops.status_tensor(self.buf.device).data_ptr(), 0, ops._stream()),
+                       "ffm_p2p_signal_wait")
+
+
+    def region_view(self, region, rows, width, dtype):
+        lo = FLAG_BYTES + region * self.region_bytes
+        nbytes = rows * width * torch.empty(0, dtype=dtype).element_size()
+        return self.buf[lo:lo + nbytes].view(dtype).view(rows, width)
+
 
 
 def get_exchange(group, device, region_bytes):

@@ -238,6 +238,14 @@ int ffm_route_backward(const float* gw, const float* topk_w, const int32_t* topk
  *
  * ffm_p2p_push: copy n_segments (<= FFM_P2P_MAX_PEERS) contiguous byte ranges src[i] -> dst[i], dst[i] usually in a
  *   peer's memory. Ranges and sizes must be multiples of 16 bytes; empty segments are skipped.
+ * ffm_p2p_push_rows: the same at row granularity, for layouts that are not one contiguous range per peer. A table in
+ *   device memory lists n_segments runs of rows: segments[i] = {first source row, first destination row, rows,
+ *   index into dst_bases} (int64 x 4), seg_end[i] = rows of segments 0..i (int64, growing); total_rows = seg_end[last].
+ *   Row r of run i goes from src + (first source row + r) * row_bytes to dst_bases[..] + (first destination row + r)
+ *   * row_bytes. With src_index the source row is src_index[first source row + r] / index_div instead (a gather
+ *   from the token matrix by flat slot); with src == NULL the destination rows are zeroed. row_bytes % 16 == 0.
+ *   This is how rows travel straight between the sender's expert-sorted order and the receiver's 256-row-aligned
+ *   grouped layout (and back), without a staging permute on either side.
  * ffm_p2p_signal_wait: all ranks call it with the same, growing epoch after their pushes: stores epoch into
  *   slot [my_rank] of every rank's flag array (release), then waits (bounded by wait_cycles, 0 = default) until its
  *   own array holds epoch in every slot (acquire). Kernels enqueued after it may read what the peers pushed.
@@ -246,6 +254,9 @@ int ffm_route_backward(const float* gw, const float* topk_w, const int32_t* topk
 #define FFM_P2P_MAX_PEERS 16
 int ffm_p2p_push(int n_segments, const void* const* src, void* const* dst, const int64_t* bytes,
                  ffm_stream_t stream);
+int ffm_p2p_push_rows(const void* src, const int32_t* src_index, int index_div, int64_t row_bytes,
+                      const int64_t* segments, const int64_t* seg_end, int n_segments, int64_t total_rows,
+                      void* const* dst_bases, int n_bases, ffm_stream_t stream);
 int ffm_p2p_signal_wait(void* const* flag_arrays, int my_rank, int world, uint32_t epoch, int32_t* status,
                         long long wait_cycles, ffm_stream_t stream);
 

@@ -170,3 +170,49 @@ def test_dispatcher_roundtrip_gloo():
 
 def test_shard_and_gradsync_gloo():
     _run_two_ranks("_case_shard_and_gradsync")
+
+
+def test_segment_plan_moves_every_row_to_the_grouped_layout_and_back():
+    """Host tables of the row-granular exchange: simulate all ranks with numpy and check layout, order and padding."""
+    import numpy as np
+    from flashfusedmoe_b200.p2p import SegmentPlan
+    rng = np.random.default_rng(3)
+    for ep, e_local in [(2, 4), (4, 2), (8, 1), (4, 16)]:
+        E = ep * e_local
+        C = rng.integers(0, 700, size=(ep, E))
+        C[rng.random((ep, E)) < 0.2] = 0            # some (rank, expert) pairs send nothing
+        C[:, 1 % E] = 0                             # one expert receives nothing at all
+        plans = [SegmentPlan(C, e_local, r) for r in range(ep)]
+        # sender buffers: row id = (source rank, expert, ordinal inside that run)
+        send = [[(s, e, j) for e in range(E) for j in range(int(C[s, e]))] for s in range(ep)]
+        grouped = [[None] * int(plans[0].rows_grouped[d]) for d in range(ep)]
+        for s in range(ep):
+            seg, end = plans[s].dispatch
+            assert (end[-1] if len(end) else 0) == len(send[s])
+            for src0, dst0, rows, d in seg:
+                for j in range(rows):
+                    assert grouped[d][dst0 + j] is None
+                    grouped[d][dst0 + j] = send[s][src0 + j]
+        for d in range(ep):
+            ts = plans[0].tile_start[d]
+            assert (ts % 2 == 0).all() and ts[0] == 0
+            for el in range(e_local):
+                e = d * e_local + el
+                rows = grouped[d][ts[el] * 128:ts[el + 1] * 128]
+                valid = [x for x in rows if x is not None]
+                assert len(valid) == C[:, e].sum()
+                assert rows[:len(valid)] == valid                                  # valid rows first, padding after
+                assert valid == sorted(valid) and all(x[1] == e for x in valid)    # source-major, stable inside a source
+            seg, _ = plans[d].padding
+            padded = sorted(int(dst0 + j) for _, dst0, rows, dd in seg for j in range(rows))
+            assert all(dd == d for _, _, _, dd in seg)
+            assert padded == [i for i, x in enumerate(grouped[d]) if x is None]
+            assert plans[d].recv_rows[d] == sum(x is not None for x in grouped[d])
+        # combine direction: every row returns to the position it was sent from
+        back = [[None] * len(send[s]) for s in range(ep)]
+        for d in range(ep):
+            seg, _ = plans[d].combine
+            for src0, dst0, rows, s in seg:
+                for j in range(rows):
+                    back[s][dst0 + j] = grouped[d][src0 + j]
+        assert back == send
