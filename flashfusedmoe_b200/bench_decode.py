@@ -25,6 +25,9 @@ def main():
     ap.add_argument("--iters", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--tokens", type=int, default=128)
+    ap.add_argument("--graph", action="store_true",
+                    help="capture the forward pass in a CUDA graph and time replays (expert parallel: uses the "
+                         "host-sync-free forward, set_ep_static_forward)")
     a = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -58,16 +61,36 @@ def main():
     x = torch.randn(a.tokens, D, device=dev).bfloat16()
     times = []
     timer = ops.KernelTimer()
+    graph = None
     with torch.no_grad():
+        if a.graph:
+            if world > 1:
+                from .fused_moe import set_ep_static_forward
+                set_ep_static_forward(a.tokens)
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                for _ in range(3):
+                    layer(x)
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                layer(x)
         for i in range(a.warmup + a.iters):
-            if i == a.warmup:
+            if i == a.warmup and graph is None:
                 ops.set_timer(timer)
             if world > 1:
                 dist.barrier()
             s = torch.cuda.Event(enable_timing=True)
             e = torch.cuda.Event(enable_timing=True)
             s.record()
-            layer(x)
+            if graph is not None:
+                graph.replay()
+            else:
+                layer(x)
             e.record()
             e.synchronize()
             if i >= a.warmup:
@@ -88,6 +111,7 @@ def main():
                 "min": float(ts[0]), "iters": a.iters, "tokens_per_gpu": a.tokens, "dtype": "bf16",
                 "config": {"workload": "BASELINE configs[4]: d_model=7168 E=256 top_k=8 ffn_dim=4096 + shared expert, forward only",
                            "experts_per_gpu": e_local if world > 1 else E},
+                "mode": "cuda graph replay" if a.graph else "eager",
                 "weight_stream_bound_ms": weight_bytes / (hbm * 1e9) * 1e3,
                 "kernel_ms_per_iter": {n: v[1] / a.iters for n, v in kt.items()}}
         if "all_to_all" in kt:

@@ -8,6 +8,8 @@
 //                       {first source row, first destination row, rows, destination buffer}: one warp per row finds
 //                       its segment by binary search on the running row count. The source row may be looked up
 //                       through an index (gather from the token matrix), or be absent (the rows are zeroed).
+//   p2p_plan_kernel     builds those tables on the device from the [ep, E] matrix of row counts, so that a forward
+//                       pass needs no host read of the counts (and can be captured in a CUDA graph).
 //   p2p_signal_kernel   after the push (stream order), every rank stores the exchange's epoch into slot [my_rank]
 //                       of every peer's flag array (release, system scope) and then waits until its own slots
 //                       show that epoch from every peer (acquire, system scope). Epochs only grow, so flags are
@@ -50,7 +52,9 @@ __global__ void __launch_bounds__(256) p2p_rows_kernel(const uint8_t* __restrict
                                                        int index_div, long long row_bytes,
                                                        const long long* __restrict__ segments,
                                                        const long long* __restrict__ seg_end, int n_segments,
-                                                       long long total_rows, RowBases bases) {
+                                                       long long total_rows,
+                                                       const long long* __restrict__ total_rows_dev, RowBases bases) {
+  if (total_rows_dev != nullptr) total_rows = *total_rows_dev;
   const int warps = blockDim.x >> 5;
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -89,12 +93,118 @@ __global__ void __launch_bounds__(256) p2p_rows_kernel(const uint8_t* __restrict
   }
 }
 
+// Device-side twin of the host planner (p2p.SegmentPlan). One block. C[s * E + e] = rows rank s routes to expert e.
+// Outputs (int64 unless noted): dispatch [E][4] + ends [E]; combine [El * ep][4] + ends; padding [El][4] + ends;
+// tile_start int32 [El + 1]; totals [4] = {rows this rank sends, rows it receives, padding rows, grouped rows}.
+// Runs with zero rows stay in the tables (their running end repeats), which the row kernel's search skips.
+constexpr int PLAN_MAX_E = 256;
+
+__global__ void __launch_bounds__(256) p2p_plan_kernel(const int32_t* __restrict__ C, int ep, int e_local, int rank,
+                                                       long long* __restrict__ dispatch, long long* __restrict__ dispatch_end,
+                                                       long long* __restrict__ combine, long long* __restrict__ combine_end,
+                                                       long long* __restrict__ padding, long long* __restrict__ padding_end,
+                                                       int32_t* __restrict__ tile_start, long long* __restrict__ totals) {
+  __shared__ long long s_R[PLAN_MAX_E];      // rows per expert over all sources
+  __shared__ long long s_seg0[PLAN_MAX_E];   // first grouped row of expert e at its owner
+  __shared__ long long s_send0[FFM_P2P_MAX_PEERS][PLAN_MAX_E];  // first sender-order row of expert e at rank s
+  __shared__ long long s_rows_grouped;
+  const int E = ep * e_local;
+  const int t = threadIdx.x;
+  for (int e = t; e < E; e += blockDim.x) {
+    long long r = 0;
+    for (int s = 0; s < ep; ++s) r += C[s * E + e];
+    s_R[e] = r;
+  }
+  if (t < ep) {  // sender-order prefix of rank t
+    long long acc = 0;
+    for (int e = 0; e < E; ++e) {
+      s_send0[t][e] = acc;
+      acc += C[t * E + e];
+    }
+  }
+  __syncthreads();
+  if (t < ep) {  // grouped layout of owner t: segments aligned to 256 rows
+    long long tiles = 0;
+    for (int el = 0; el < e_local; ++el) {
+      const int e = t * e_local + el;
+      s_seg0[e] = tiles * 128;
+      if (t == rank) tile_start[el] = static_cast<int32_t>(tiles);
+      tiles += 2 * ((s_R[e] + 255) / 256);
+    }
+    if (t == rank) {
+      tile_start[e_local] = static_cast<int32_t>(tiles);
+      s_rows_grouped = tiles * 128;
+    }
+  }
+  __syncthreads();
+  const int lo = rank * e_local;
+  // dispatch: one run per expert, sender order -> owner's grouped layout
+  for (int e = t; e < E; e += blockDim.x) {
+    long long before = 0;
+    for (int s = 0; s < rank; ++s) before += C[s * E + e];
+    const long long rows = C[rank * E + e];
+    dispatch[4 * e + 0] = s_send0[rank][e];
+    dispatch[4 * e + 1] = s_seg0[e] + before;
+    dispatch[4 * e + 2] = rows;
+    dispatch[4 * e + 3] = e / e_local;
+    dispatch_end[e] = s_send0[rank][e] + rows;
+  }
+  // combine: runs (expert, source) this rank holds, grouped layout -> the origin's sender order
+  for (int i = t; i < e_local * ep; i += blockDim.x) {
+    const int el = i / ep, s = i % ep, e = lo + el;
+    long long before = 0;
+    for (int s2 = 0; s2 < s; ++s2) before += C[s2 * E + e];
+    long long prior = 0;  // valid rows of this rank's earlier experts
+    for (int el2 = 0; el2 < el; ++el2) prior += s_R[lo + el2];
+    const long long rows = C[s * E + e];
+    combine[4 * i + 0] = s_seg0[e] + before;
+    combine[4 * i + 1] = s_send0[s][e];
+    combine[4 * i + 2] = rows;
+    combine[4 * i + 3] = s;
+    combine_end[i] = prior + before + rows;
+  }
+  // padding of this rank's own layout
+  for (int el = t; el < e_local; el += blockDim.x) {
+    const int e = lo + el;
+    long long acc = 0;
+    for (int el2 = 0; el2 <= el; ++el2) {
+      const int e2 = lo + el2;
+      acc += 256 * ((s_R[e2] + 255) / 256) - s_R[e2];
+    }
+    padding[4 * el + 0] = 0;
+    padding[4 * el + 1] = s_seg0[e] + s_R[e];
+    padding[4 * el + 2] = 256 * ((s_R[e] + 255) / 256) - s_R[e];
+    padding[4 * el + 3] = rank;
+    padding_end[el] = acc;
+  }
+  if (t == 0) {
+    long long recv = 0, pad = 0;
+    for (int el = 0; el < e_local; ++el) {
+      recv += s_R[lo + el];
+      pad += 256 * ((s_R[lo + el] + 255) / 256) - s_R[lo + el];
+    }
+    long long sent = 0;
+    for (int e = 0; e < E; ++e) sent += C[rank * E + e];
+    totals[0] = sent;
+    totals[1] = recv;
+    totals[2] = pad;
+    totals[3] = s_rows_grouped;
+  }
+}
+
 struct SignalArgs {
   uint32_t* flags[FFM_P2P_MAX_PEERS];  // flag array of every rank (index = rank); [my_rank] is local memory
 };
 
-__global__ void p2p_signal_kernel(SignalArgs a, int my_rank, int world, uint32_t epoch, int32_t* status,
-                                  long long wait_cycles) {
+__global__ void p2p_signal_kernel(SignalArgs a, int my_rank, int world, uint32_t epoch, uint32_t* epoch_counter,
+                                  int32_t* status, long long wait_cycles) {
+  __shared__ uint32_t s_epoch;
+  if (epoch_counter != nullptr) {
+    // the epoch lives in device memory and grows by one per call, so that a captured graph can be replayed
+    if (threadIdx.x == 0) s_epoch = atomicAdd(epoch_counter, 1u) + 1u;
+    __syncthreads();
+    epoch = s_epoch;
+  }
   const int p = threadIdx.x;
   if (p >= world) return;
   __threadfence_system();  // the rows pushed by the preceding kernel are visible before the flag is
@@ -167,7 +277,48 @@ extern "C" int ffm_p2p_push_rows(const void* src, const int32_t* src_index, int 
   if (blocks > 148LL * 8) blocks = 148LL * 8;
   p2p_rows_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint8_t*>(src), src_index, index_div, row_bytes, reinterpret_cast<const long long*>(segments),
-      reinterpret_cast<const long long*>(seg_end), n_segments, total_rows, b);
+      reinterpret_cast<const long long*>(seg_end), n_segments, total_rows, nullptr, b);
+  return cudaGetLastError() == cudaSuccess ? FFM_OK : FFM_ERR_LAUNCH;
+}
+
+extern "C" int ffm_p2p_push_rows_dev(const void* src, const int32_t* src_index, int index_div, int64_t row_bytes,
+                                     const int64_t* segments, const int64_t* seg_end, int n_segments,
+                                     const int64_t* total_rows_dev, int64_t max_rows, void* const* dst_bases, int n_bases,
+                                     ffm_stream_t stream) {
+  if (n_segments < 0 || max_rows < 0) return FFM_ERR_BAD_ARG;
+  if (n_segments == 0 || max_rows == 0) return FFM_OK;
+  if (!segments || !seg_end || !dst_bases || !total_rows_dev) return FFM_ERR_BAD_ARG;
+  if (n_bases < 1 || n_bases > FFM_P2P_MAX_PEERS) return FFM_ERR_UNSUPPORTED;
+  if (row_bytes <= 0 || (row_bytes & 15) != 0) return FFM_ERR_UNSUPPORTED;
+  if (src_index != nullptr && (src == nullptr || index_div < 1)) return FFM_ERR_BAD_ARG;
+  if (src != nullptr && (reinterpret_cast<uintptr_t>(src) & 15u) != 0) return FFM_ERR_UNSUPPORTED;
+  RowBases b = {};
+  for (int i = 0; i < n_bases; ++i) {
+    if (!dst_bases[i] || (reinterpret_cast<uintptr_t>(dst_bases[i]) & 15u) != 0) return FFM_ERR_BAD_ARG;
+    b.base[i] = static_cast<uint8_t*>(dst_bases[i]);
+  }
+  long long blocks = (max_rows + 7) / 8;
+  if (blocks > 148LL * 8) blocks = 148LL * 8;
+  p2p_rows_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint8_t*>(src), src_index, index_div, row_bytes, reinterpret_cast<const long long*>(segments),
+      reinterpret_cast<const long long*>(seg_end), n_segments, 0, reinterpret_cast<const long long*>(total_rows_dev), b);
+  return cudaGetLastError() == cudaSuccess ? FFM_OK : FFM_ERR_LAUNCH;
+}
+
+extern "C" int ffm_p2p_plan(const int32_t* counts, int ep, int e_local, int rank, int64_t* dispatch,
+                            int64_t* dispatch_end, int64_t* combine, int64_t* combine_end, int64_t* padding,
+                            int64_t* padding_end, int32_t* tile_start, int64_t* totals, ffm_stream_t stream) {
+  if (!counts || !dispatch || !dispatch_end || !combine || !combine_end || !padding || !padding_end || !tile_start ||
+      !totals) {
+    return FFM_ERR_BAD_ARG;
+  }
+  if (ep < 1 || ep > FFM_P2P_MAX_PEERS || e_local < 1 || rank < 0 || rank >= ep) return FFM_ERR_BAD_ARG;
+  if (ep * e_local > PLAN_MAX_E) return FFM_ERR_UNSUPPORTED;
+  p2p_plan_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      counts, ep, e_local, rank, reinterpret_cast<long long*>(dispatch), reinterpret_cast<long long*>(dispatch_end),
+      reinterpret_cast<long long*>(combine), reinterpret_cast<long long*>(combine_end),
+      reinterpret_cast<long long*>(padding), reinterpret_cast<long long*>(padding_end), tile_start,
+      reinterpret_cast<long long*>(totals));
   return cudaGetLastError() == cudaSuccess ? FFM_OK : FFM_ERR_LAUNCH;
 }
 
@@ -181,6 +332,22 @@ extern "C" int ffm_p2p_signal_wait(void* const* flag_arrays, int my_rank, int wo
     a.flags[i] = static_cast<uint32_t*>(flag_arrays[i]);
   }
   if (wait_cycles <= 0) wait_cycles = 2000000000LL;
-  p2p_signal_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(a, my_rank, world, epoch, status, wait_cycles);
+  p2p_signal_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(a, my_rank, world, epoch, nullptr, status,
+                                                                     wait_cycles);
+  return cudaGetLastError() == cudaSuccess ? FFM_OK : FFM_ERR_LAUNCH;
+}
+
+extern "C" int ffm_p2p_signal_wait_dev(void* const* flag_arrays, int my_rank, int world, uint32_t* epoch_counter,
+                                       int32_t* status, long long wait_cycles, ffm_stream_t stream) {
+  if (!flag_arrays || !status || !epoch_counter) return FFM_ERR_BAD_ARG;
+  if (world < 1 || world > FFM_P2P_MAX_PEERS || my_rank < 0 || my_rank >= world) return FFM_ERR_UNSUPPORTED;
+  SignalArgs a = {};
+  for (int i = 0; i < world; ++i) {
+    if (!flag_arrays[i]) return FFM_ERR_BAD_ARG;
+    a.flags[i] = static_cast<uint32_t*>(flag_arrays[i]);
+  }
+  if (wait_cycles <= 0) wait_cycles = 2000000000LL;
+  p2p_signal_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(a, my_rank, world, 0u, epoch_counter, status,
+                                                                     wait_cycles);
   return cudaGetLastError() == cudaSuccess ? FFM_OK : FFM_ERR_LAUNCH;
 }

@@ -380,17 +380,19 @@ class _EPPlan:
                 self.remote_dispatch = int(sp.dispatch[0][sp.dispatch[0][:, 3] != r, 2].sum())
                 self.remote_combine = int(sp.combine[0][sp.combine[0][:, 3] != r, 2].sum())
 
-    def dispatch_grouped(self, src, src_index, index_div, region):
+    def dispatch_grouped(self, src, src_index, index_div, region, zero_padding=True):
         """Sender order (or, with src_index, a gather from the token matrix) -> every receiver's grouped layout in
-        `region`; returns this rank's grouped rows [rows_l, W] (a view of the region; padding rows are zero)."""
+        `region`; returns this rank's grouped rows [rows_l, W] (a view of the region). The padding rows are zeroed
+        unless the caller says nothing will sum over them (forward without gradients)."""
         px, sp = self.px, self.seg
         W = src.shape[1]
         rb = W * src.element_size()
         dry = _EP_DRY_EXCHANGE
         px.push_rows(src, src_index, index_div, rb, self.d_seg, self.d_end, len(sp.dispatch[0]),
                      int(sp.send_rows[self.rank]), region, remote_rows=self.remote_dispatch, dry=dry)
-        px.push_rows(None, None, 1, rb, self.p_seg, self.p_end, len(sp.padding[0]),
-                     int(sp.padding[0][:, 2].sum()), region, name="zero_padding")
+        if zero_padding:
+            px.push_rows(None, None, 1, rb, self.p_seg, self.p_end, len(sp.padding[0]),
+                         int(sp.padding[0][:, 2].sum()), region, name="zero_padding")
         px.barrier(dry=dry)
         return px.region_view(region, self.rows_l, W, src.dtype)
 
@@ -419,6 +421,73 @@ class _EPPlan:
         ops.a2a_bytes_sent += (sum(in_splits) - in_splits[self.rank]) * rows.shape[1] * rows.element_size()
         with ops._Launch("all_to_all", 0):
             return all_to_all_rows(rows, out_splits, in_splits, self.group), False
+
+
+# Host-sync-free forward (inference): set_ep_static_forward(max_tokens_per_rank) declares, with the same value on
+# every rank, the most tokens a rank passes per call. Without gradients the expert-parallel forward then sizes its
+# buffers for the worst case (every routed row of every rank arriving at one rank), shares the counts and builds the
+# exchange tables on the device, and never reads anything back: the call is a fixed launch sequence that a CUDA graph
+# can capture and replay.
+_EP_STATIC_TOKENS = None
+
+
+def set_ep_static_forward(max_tokens_per_rank):
+    """Enable (int, identical on every rank) or disable (None) the host-sync-free expert-parallel forward."""
+    global _EP_STATIC_TOKENS
+    _EP_STATIC_TOKENS = None if max_tokens_per_rank is None else int(max_tokens_per_rank)
+
+
+def _ep_forward_static(hidden_states, gate_weight, w_up, w_down, sw, cfg, dtype):
+    """Expert-parallel forward without a host read: routing -> counts to every rank (peer stores) -> tables built on
+    the device (ffm_p2p_plan) -> rows into the owners' grouped layouts -> grouped GEMMs over the worst-case buffer
+    (the persistent kernel stops at the last real tile) -> rows back -> weighted combine."""
+    group = cfg.ep_group
+    ep = torch.distributed.get_world_size(group)
+    N, D = hidden_states.shape
+    El = w_up.shape[0]
+    E = ep * El
+    H = w_up.shape[1] // 2
+    k = cfg.top_k
+    T = N * k
+    if N > _EP_STATIC_TOKENS:
+        raise RuntimeError(f"static expert-parallel forward was declared for at most {_EP_STATIC_TOKENS} tokens per "
+                           f"rank, got {N}")
+    h, g, wu, wd = _to(hidden_states, dtype), _to(gate_weight, dtype), _to(w_up, dtype), _to(w_down, dtype)
+    routing = _route(h, g, cfg, False)
+    shared_out = None
+    if sw[0] is not None:
+        swg, swu, swd = _to(sw[0], dtype), _to(sw[1], dtype), _to(sw[2], dtype)
+        side = _get_side_stream("shared", priority=-1)
+        ready = torch.cuda.Event()
+        ready.record()
+        with torch.cuda.stream(side):
+            side.wait_event(ready)
+            shared_out, _, _ = _glu_ffn_forward(h, swg, swu, swd, cfg.shared_activation, want_preact=False)
+        shared_done = torch.cuda.Event()
+        shared_done.record(side)
+    rb = D * h.element_size()
+    cap_rows = (ep * _EP_STATIC_TOKENS * k + 256 * El + 255) // 256 * 256   # every row of every rank lands here
+    px = p2p.get_exchange(group, h.device, cap_rows * rb)
+    C = px.share_counts(routing.counts)
+    t = px.plan_dev(C, El)
+    cpos, src_c = _compact_send_map(routing, T)
+    tot = t["totals"]
+    px.push_rows_dev(h, src_c, k, rb, t["dispatch"], t["dispatch_end"], tot[0:1], T, 0)
+    px.barrier_dev()
+    # (the padding rows of the grouped layout stay as they are: without a backward pass nothing sums over them, and
+    # a GEMM row only depends on its own input row)
+    Xg = px.region_view(0, cap_rows, D, h.dtype)
+    act, _ = ops.grouped_gemm_glu(Xg, wu, wu.view(-1, D)[H:], 2 * H, El, t["tile_start"], D, H, cfg.activation,
+                                  want_preact=False)
+    Y = ops.grouped_gemm(act, wd, _lib.B_KMAJOR, El, t["tile_start"], H, D)
+    px.push_rows_dev(Y, None, 1, rb, t["combine"], t["combine_end"], tot[1:2], cap_rows, 1)
+    px.barrier_dev()
+    returned = px.region_view(1, T, D, h.dtype)
+    if shared_out is not None:
+        torch.cuda.current_stream().wait_event(shared_done)
+    out = ops.combine_forward(returned, cpos, routing.topk_w, N, k, addend=shared_out)
+    aux, z = _loss_tensors(routing, N, E, cfg)
+    return out, aux, z, routing.counts, torch.zeros(1, dtype=torch.int32, device=h.device)
 
 
 def _compact_send_map(routing, T):
@@ -493,7 +562,7 @@ class _FusedMoEEPFunction(torch.autograd.Function):
             # rows are gathered from the token matrix and stored straight into the owners' grouped layouts
             rows_l = plan.rows_l
             ts_l = plan.ts_l
-            recv = plan.dispatch_grouped(disp, src_c, k, 0)                      # [rows_l, W] grouped, region view
+            recv = plan.dispatch_grouped(disp, src_c, k, 0, zero_padding=need_grad)   # [rows_l, W] grouped, region view
             if need_grad:
                 recv = recv.clone()  # saved for backward; the region is overwritten by the next call
             if has_latent:
@@ -767,8 +836,14 @@ def fused_moe(
     if group is not None:
         sw = shared_expert_weights if shared_expert_weights is not None else (None, None, None)
         lw = latent_weights if latent_weights is not None else (None, None)
-        out, aux, z, counts, dropped = _FusedMoEEPFunction.apply(hidden_states, gate_weight, w_up, w_down, sw[0],
-                                                                 sw[1], sw[2], lw[0], lw[1], cfg, dtype)
+        wants_grad = torch.is_grad_enabled() and any(
+            t is not None and t.requires_grad for t in (hidden_states, gate_weight, w_up, w_down, *sw, *lw))
+        if (_EP_STATIC_TOKENS is not None and not wants_grad and lw[0] is None and _EP_TRANSPORT == "p2p"
+                and p2p.available() and E % 4 == 0 and E <= 256 and cfg.input_jitter == 0.0):
+            out, aux, z, counts, dropped = _ep_forward_static(hidden_states, gate_weight, w_up, w_down, sw, cfg, dtype)
+        else:
+            out, aux, z, counts, dropped = _FusedMoEEPFunction.apply(hidden_states, gate_weight, w_up, w_down, sw[0],
+                                                                     sw[1], sw[2], lw[0], lw[1], cfg, dtype)
     else:
         out, aux, z, counts, dropped = _FusedMoEFunction.apply(hidden_states, gate_weight, w_up, w_down, _addend, cfg,
                                                                dtype)

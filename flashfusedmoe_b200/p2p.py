@@ -19,7 +19,14 @@ import torch
 
 from . import _lib, ops
 
-FLAG_BYTES = 4096
+# Head of the symmetric buffer: [0, 2048) flags of the host-epoch barrier, [2048, 3072) flags of the device-epoch
+# barrier, [3072, 3076) its epoch counter, [4096, 4096 + 16 KiB) the [ep, E] int32 count matrix of the host-sync-free
+# forward (every rank writes its row into every rank's copy).
+FLAG_BYTES = 65536
+DEV_FLAGS_OFFSET = 2048
+DEV_COUNTER_OFFSET = 3072
+COUNTS_OFFSET = 4096
+COUNTS_BYTES = 16 * 256 * 4
 NUM_REGIONS = 3  # dispatch, combine (also the reverse-dispatch of the full input gradient), backward
 
 _exchanges = {}
@@ -105,6 +112,7 @@ class PeerExchange:
         dist.barrier(group)  # every rank's flags are zero before anyone signals
         self.epoch = 0
         self._flag_ptrs = (ctypes.c_void_p * self.world)(*self.ptrs)
+        self._dev_flag_ptrs = (ctypes.c_void_p * self.world)(*[p + DEV_FLAGS_OFFSET for p in self.ptrs])
 
     def region_ptr(self, rank, region):
         return self.ptrs[rank] + FLAG_BYTES + region * self.region_bytes
@@ -191,6 +199,63 @@ class PeerExchange:
                                                ops.status_tensor(self.buf.device).data_ptr(), 0, ops._stream()),
                        "ffm_p2p_signal_wait")
 
+
+    def barrier_dev(self):
+        """Flag barrier whose epoch lives in device memory (replayable inside a CUDA graph)."""
+        lib = _lib.load()
+        with ops._Launch("all_to_all", 1):
+            _lib.check(lib.ffm_p2p_signal_wait_dev(self._dev_flag_ptrs, self.rank, self.world,
+                                                   self.ptrs[self.rank] + DEV_COUNTER_OFFSET,
+                                                   ops.status_tensor(self.buf.device).data_ptr(), 0, ops._stream()),
+                       "ffm_p2p_signal_wait_dev")
+
+    def share_counts(self, counts):
+        """counts int32 [E] of this rank -> row `rank` of every rank's [ep, E] count matrix; returns this rank's copy
+        (valid after the barrier this call ends with; no host involvement)."""
+        lib = _lib.load()
+        E = counts.numel()
+        n = self.world
+        if E * 4 % 16 != 0 or n * E * 4 > COUNTS_BYTES:
+            raise RuntimeError("share_counts needs E % 4 == 0 and ep * E <= 4096")
+        src = (ctypes.c_void_p * n)(*[counts.data_ptr()] * n)
+        dst = (ctypes.c_void_p * n)(*[p + COUNTS_OFFSET + self.rank * E * 4 for p in self.ptrs])
+        nbytes = (ctypes.c_int64 * n)(*[E * 4] * n)
+        with ops._Launch("all_to_all", 1):
+            _lib.check(lib.ffm_p2p_push(n, src, dst, nbytes, ops._stream()), "ffm_p2p_push")
+        self.barrier_dev()
+        return self.buf[COUNTS_OFFSET:COUNTS_OFFSET + n * E * 4].view(torch.int32).view(n, E)
+
+    def plan_dev(self, count_matrix, e_local):
+        """Device-built tables of one call (ffm_p2p_plan) from the shared count matrix."""
+        lib = _lib.load()
+        ep = self.world
+        E = ep * e_local
+        dev = self.buf.device
+        i64 = dict(dtype=torch.int64, device=dev)
+        t = dict(dispatch=torch.empty(E, 4, **i64), dispatch_end=torch.empty(E, **i64),
+                 combine=torch.empty(e_local * ep, 4, **i64), combine_end=torch.empty(e_local * ep, **i64),
+                 padding=torch.empty(e_local, 4, **i64), padding_end=torch.empty(e_local, **i64),
+                 tile_start=torch.empty(e_local + 1, dtype=torch.int32, device=dev), totals=torch.empty(4, **i64))
+        with ops._Launch("ep_plan", 1):
+            _lib.check(lib.ffm_p2p_plan(count_matrix.data_ptr(), ep, e_local, self.rank, t["dispatch"].data_ptr(),
+                                        t["dispatch_end"].data_ptr(), t["combine"].data_ptr(),
+                                        t["combine_end"].data_ptr(), t["padding"].data_ptr(),
+                                        t["padding_end"].data_ptr(), t["tile_start"].data_ptr(),
+                                        t["totals"].data_ptr(), ops._stream()), "ffm_p2p_plan")
+        return t
+
+    def push_rows_dev(self, src, src_index, index_div, row_bytes, seg, seg_end, total_dev, max_rows, region,
+                      name="all_to_all"):
+        """push_rows with the row total read on the device (tables from plan_dev)."""
+        lib = _lib.load()
+        n = self.world
+        bases = (ctypes.c_void_p * n)(*[self.region_ptr(d, region) for d in range(n)])
+        with ops._Launch(name, 1):
+            _lib.check(lib.ffm_p2p_push_rows_dev(0 if src is None else src.data_ptr(),
+                                                 0 if src_index is None else src_index.data_ptr(), int(index_div),
+                                                 int(row_bytes), seg.data_ptr(), seg_end.data_ptr(), int(seg.shape[0]),
+                                                 total_dev.data_ptr(), int(max_rows), bases, n, ops._stream()),
+                       "ffm_p2p_push_rows_dev")
 
     def region_view(self, region, rows, width, dtype):
         lo = FLAG_BYTES + region * self.region_bytes

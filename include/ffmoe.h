@@ -246,10 +246,22 @@ int ffm_route_backward(const float* gw, const float* topk_w, const int32_t* topk
  *   from the token matrix by flat slot); with src == NULL the destination rows are zeroed. row_bytes % 16 == 0.
  *   This is how rows travel straight between the sender's expert-sorted order and the receiver's 256-row-aligned
  *   grouped layout (and back), without a staging permute on either side.
+ * ffm_p2p_push_rows_dev: ffm_p2p_push_rows with the row total read from device memory at run time (max_rows only
+ *   sizes the grid) and tables that may contain empty runs, as ffm_p2p_plan writes them.
+ * ffm_p2p_plan: builds on the device, from counts[s * E + e] = rows rank s routes to expert e (int32 [ep][E],
+ *   E = ep * e_local <= 256, the same on every rank), the tables of one expert-parallel call for `rank`:
+ *   dispatch int64 [E][4] + dispatch_end [E] (sender order -> the owners' grouped layouts), combine
+ *   int64 [e_local * ep][4] + combine_end (this rank's grouped layout -> the origins' sender order), padding
+ *   int64 [e_local][4] + padding_end (rows of its own layout to zero), tile_start int32 [e_local + 1] for the grouped
+ *   GEMM, totals int64 [4] = {rows sent, rows received, padding rows, grouped rows}. With it a forward pass needs no
+ *   host read of the counts and can be captured in a CUDA graph.
  * ffm_p2p_signal_wait: all ranks call it with the same, growing epoch after their pushes: stores epoch into
  *   slot [my_rank] of every rank's flag array (release), then waits (bounded by wait_cycles, 0 = default) until its
  *   own array holds epoch in every slot (acquire). Kernels enqueued after it may read what the peers pushed.
  *   flag_arrays[r] points at rank r's array of `world` uint32 flags, zero-initialised once.
+ * ffm_p2p_signal_wait_dev: the same with the epoch kept in device memory (*epoch_counter grows by one per call, and
+ *   by the same amount on every rank), so that the call can sit in a CUDA graph that is replayed. Give it flag
+ *   arrays of its own: the two kinds of barrier must not share flags.
  * ------------------------------------------------------------------------------------------------- */
 #define FFM_P2P_MAX_PEERS 16
 int ffm_p2p_push(int n_segments, const void* const* src, void* const* dst, const int64_t* bytes,
@@ -257,6 +269,15 @@ int ffm_p2p_push(int n_segments, const void* const* src, void* const* dst, const
 int ffm_p2p_push_rows(const void* src, const int32_t* src_index, int index_div, int64_t row_bytes,
                       const int64_t* segments, const int64_t* seg_end, int n_segments, int64_t total_rows,
                       void* const* dst_bases, int n_bases, ffm_stream_t stream);
+int ffm_p2p_push_rows_dev(const void* src, const int32_t* src_index, int index_div, int64_t row_bytes,
+                          const int64_t* segments, const int64_t* seg_end, int n_segments,
+                          const int64_t* total_rows_dev, int64_t max_rows, void* const* dst_bases, int n_bases,
+                          ffm_stream_t stream);
+int ffm_p2p_plan(const int32_t* counts, int ep, int e_local, int rank, int64_t* dispatch, int64_t* dispatch_end,
+                 int64_t* combine, int64_t* combine_end, int64_t* padding, int64_t* padding_end, int32_t* tile_start,
+                 int64_t* totals, ffm_stream_t stream);
+int ffm_p2p_signal_wait_dev(void* const* flag_arrays, int my_rank, int world, uint32_t* epoch_counter,
+                            int32_t* status, long long wait_cycles, ffm_stream_t stream);
 int ffm_p2p_signal_wait(void* const* flag_arrays, int my_rank, int world, uint32_t epoch, int32_t* status,
                         long long wait_cycles, ffm_stream_t stream);
 

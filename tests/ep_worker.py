@@ -139,6 +139,44 @@ def main():
     assert torch.equal(out_lf, out_l.detach()) and torch.isfinite(hl.grad).all()
     assert (hl.grad.float() - route_only.to(dev).float()).abs().max() > 0, "latent path adds the expert input gradient"
 
+    # ---- host-sync-free forward (inference), eager and replayed from a CUDA graph ---------------------------------
+    if fm._EP_TRANSPORT == "p2p":
+        with torch.no_grad():
+            ref_out, ref_losses = ffm.fused_moe(h, g, wu_l, wd_l, top_k=k, ep_group=group,
+                                                shared_expert_weights=(sg, su, sd), return_metrics=True)
+            ffm.set_ep_static_forward(384 + 64 * world)    # the same bound on every rank (ranks hold different N)
+            st_out, st_losses = ffm.fused_moe(h, g, wu_l, wd_l, top_k=k, ep_group=group,
+                                              shared_expert_weights=(sg, su, sd), return_metrics=True)
+            ops.check_status()
+            assert torch.equal(st_out, ref_out), f"static forward differs: {rel(st_out, ref_out)}"
+            assert torch.equal(st_losses["tokens_per_expert"], ref_losses["tokens_per_expert"])
+            # graph: capture once, replay on new tokens
+            h_static = h.clone()
+            stream = torch.cuda.Stream()
+            stream.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(stream):
+                for _ in range(2):
+                    ffm.fused_moe(h_static, g, wu_l, wd_l, top_k=k, ep_group=group, shared_expert_weights=(sg, su, sd))
+            torch.cuda.current_stream().wait_stream(stream)
+            torch.cuda.synchronize()
+            dist.barrier()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                g_out, _ = ffm.fused_moe(h_static, g, wu_l, wd_l, top_k=k, ep_group=group,
+                                         shared_expert_weights=(sg, su, sd))
+            torch.manual_seed(500 + rank)
+            h_new = torch.randn(N, D).bfloat16().to(dev)
+            for src in (h, h_new, h):
+                h_static.copy_(src)
+                graph.replay()
+                torch.cuda.synchronize()
+                ffm.set_ep_static_forward(None)
+                want, _ = ffm.fused_moe(src, g, wu_l, wd_l, top_k=k, ep_group=group, shared_expert_weights=(sg, su, sd))
+                ffm.set_ep_static_forward(384 + 64 * world)
+                assert torch.equal(g_out, want), f"graph replay differs: {rel(g_out, want)}"
+            ops.check_status()
+            ffm.set_ep_static_forward(None)
+
     # ---- MoELayer.shard_experts ----------------------------------------------------------------
     torch.manual_seed(3)
     layer = ffm.MoELayer(D, F, E, k, num_shared_experts=1).to(dev).bfloat16()
