@@ -87,6 +87,8 @@ struct Shape {
 
 struct GemmParams {
   const int32_t* tile_start;  // [groups + 1] cumulative 128-row tiles, or null (dense)
+  const int32_t* group_rows;  // [groups] valid rows per group, or null: when given (grouped-M only) the tiles of a
+                              // group that hold no valid row are not computed
   int groups;
   int dense_m_tiles;
   int n_cols;              // output columns per group (GLU: H)
@@ -128,7 +130,8 @@ struct TileCoord {
 // weight tile through L2.
 template <int GROUPK, int CTA2>
 struct TileWalker {
-  const int* ts;
+  const int* ts;             // cumulative tiles to walk (shared memory)
+  const int32_t* layout_ts;  // cumulative tiles of the memory layout when it differs from `ts` (global), else null
   int groups, n_tiles, m_units_per_group, k_blocks, rank;
   long long total, cur, step;
   int g;
@@ -137,6 +140,7 @@ struct TileWalker {
 
   __device__ TileWalker(const GemmParams& p, const int* ts_smem, int cta_rank) {
     ts = ts_smem;
+    layout_ts = (!GROUPK && p.group_rows != nullptr) ? p.tile_start : nullptr;
     groups = p.groups;
     n_tiles = p.n_tiles;
     k_blocks = p.k_blocks;
@@ -170,7 +174,7 @@ struct TileWalker {
       const int r = static_cast<int>(cur - static_cast<long long>(u0) * n_tiles);
       t.group = g;
       t.n_block = r / cnt;
-      unit = u0 + r % cnt;
+      unit = (layout_ts != nullptr ? units(__ldg(layout_ts + g)) : u0) + r % cnt;
       t.k_row0 = 0;
       t.k_blocks = k_blocks;
     }
@@ -302,7 +306,22 @@ ffm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     tma_prefetch_desc(&tmC);
     tma_prefetch_desc(&tmC2);
   }
-  if (p.tile_start != nullptr) {
+  if (!GROUPK && p.group_rows != nullptr) {
+    // walk only the tiles that hold valid rows: per group ceil(rows / 128), rounded up to a pair with CTA2
+    for (int i = threadIdx.x; i < p.groups; i += GEMM_THREADS) {
+      const int tiles = (p.group_rows[i] + BM - 1) / BM;
+      ctrl->tile_start[i + 1] = CTA2 ? ((tiles + 1) & ~1) : tiles;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int acc = 0;
+      ctrl->tile_start[0] = 0;
+      for (int i = 1; i <= p.groups; ++i) {
+        acc += ctrl->tile_start[i];
+        ctrl->tile_start[i] = acc;
+      }
+    }
+  } else if (p.tile_start != nullptr) {
     for (int i = threadIdx.x; i <= p.groups; i += GEMM_THREADS) ctrl->tile_start[i] = p.tile_start[i];
   } else if (threadIdx.x == 0) {
     ctrl->tile_start[0] = 0;
@@ -755,8 +774,9 @@ int launch_gemm_shape(const CUtensorMap& tmA, const CUtensorMap& tmB0, const CUt
 template <int A_MN, int B_MN, int EPI, int GROUPK>
 int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB0, const CUtensorMap& tmB1, const CUtensorMap& tmC,
                 const CUtensorMap& tmC2, const GemmParams& p, long long max_m_tiles, long long multiplier,
-                cudaStream_t stream) {
-  if (use_cta_pair()) {
+                cudaStream_t stream, int tile_rows = 0) {
+  const bool pair = tile_rows == 256 ? true : (tile_rows == 128 ? false : use_cta_pair());
+  if (pair) {
     return launch_gemm_shape<A_MN, B_MN, EPI, GROUPK, 1>(tmA, tmB0, tmB1, tmC, tmC2, p,
                                                          ((max_m_tiles + 1) / 2) * multiplier, stream);
   }
@@ -783,12 +803,14 @@ extern "C" int ffm_set_gemm_cta_pair(int enable) {
 
 extern "C" int ffm_grouped_gemm_glu(const void* A, const void* w_gate, const void* w_up, int64_t group_rows,
                                     int groups, const int32_t* tile_start, int64_t rows, int K, int H,
-                                    int activation, void* act, void* preact, int32_t* status,
-                                    ffm_stream_t stream) {
+                                    int activation, void* act, void* preact, const int32_t* valid_rows, int tile_rows,
+                                    int32_t* status, ffm_stream_t stream) {
   if (!A || !w_gate || !w_up || !act || !status) return FFM_ERR_BAD_ARG;
   if (groups < 1 || groups > MAX_GROUPS || rows < 0 || K <= 0 || H <= 0 || group_rows < H) return FFM_ERR_BAD_ARG;
   if (activation < 0 || activation > 3) return FFM_ERR_BAD_ARG;
   if (tile_start == nullptr && groups != 1) return FFM_ERR_BAD_ARG;
+  if (tile_rows != 0 && tile_rows != 128 && tile_rows != 256) return FFM_ERR_BAD_ARG;
+  if (valid_rows != nullptr && tile_start == nullptr) return FFM_ERR_BAD_ARG;
   if (K % 64 != 0 || H % 64 != 0) return FFM_ERR_UNSUPPORTED;  // a 64-column box of gate must not reach into up
   if (rows == 0) return FFM_OK;
   CUtensorMap tmA, tmB0, tmB1, tmC, tmC2;
@@ -818,17 +840,20 @@ extern "C" int ffm_grouped_gemm_glu(const void* A, const void* w_gate, const voi
   p.n_tiles = (H + 127) / 128;
   p.status = status;
   p.wait_cycles = g_wait_cycles;
+  p.group_rows = valid_rows;
   return launch_gemm<0, 0, EPI_GLU, 0>(tmA, tmB0, tmB1, tmC, tmC2, p, (rows + BM - 1) / BM, p.n_tiles,
-                                       static_cast<cudaStream_t>(stream));
+                                       static_cast<cudaStream_t>(stream), tile_rows);
 }
 
 extern "C" int ffm_grouped_gemm(const void* A, const void* B, int b_major, int groups, const int32_t* tile_start,
-                                int64_t rows, int K, int Nout, float scale, void* out, int32_t* status,
-                                ffm_stream_t stream) {
+                                int64_t rows, int K, int Nout, float scale, void* out, const int32_t* valid_rows,
+                                int tile_rows, int32_t* status, ffm_stream_t stream) {
   if (!A || !B || !out || !status) return FFM_ERR_BAD_ARG;
   if (groups < 1 || groups > MAX_GROUPS || rows < 0 || K <= 0 || Nout <= 0) return FFM_ERR_BAD_ARG;
   if (b_major != FFM_B_KMAJOR && b_major != FFM_B_NMAJOR) return FFM_ERR_BAD_ARG;
   if (tile_start == nullptr && groups != 1) return FFM_ERR_BAD_ARG;
+  if (tile_rows != 0 && tile_rows != 128 && tile_rows != 256) return FFM_ERR_BAD_ARG;
+  if (valid_rows != nullptr && tile_start == nullptr) return FFM_ERR_BAD_ARG;
   if (K % 64 != 0 || Nout % 32 != 0) return FFM_ERR_UNSUPPORTED;
   if (b_major == FFM_B_NMAJOR && Nout % 64 != 0) return FFM_ERR_UNSUPPORTED;
   if (rows == 0) return FFM_OK;
@@ -846,17 +871,18 @@ extern "C" int ffm_grouped_gemm(const void* A, const void* B, int b_major, int g
   p.n_tiles = (Nout + BN - 1) / BN;
   p.status = status;
   p.wait_cycles = g_wait_cycles;
+  p.group_rows = valid_rows;
   const long long m_tiles = (rows + BM - 1) / BM;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (b_major == FFM_B_KMAJOR) {
     if ((rc = make_map_2d(&tmB, B, static_cast<long long>(groups) * Nout, K, 64, 128)) != FFM_OK) return rc;
     p.b_group_rows = Nout;
     p.b1_row_offset = 128;
-    return launch_gemm<0, 0, EPI_PLAIN, 0>(tmA, tmB, tmB, tmC, tmC, p, m_tiles, p.n_tiles, s);
+    return launch_gemm<0, 0, EPI_PLAIN, 0>(tmA, tmB, tmB, tmC, tmC, p, m_tiles, p.n_tiles, s, tile_rows);
   }
   if ((rc = make_map_2d(&tmB, B, static_cast<long long>(groups) * K, Nout, 64, 64)) != FFM_OK) return rc;
   p.b_group_rows = K;
-  return launch_gemm<0, 1, EPI_PLAIN, 0>(tmA, tmB, tmB, tmC, tmC, p, m_tiles, p.n_tiles, s);
+  return launch_gemm<0, 1, EPI_PLAIN, 0>(tmA, tmB, tmB, tmC, tmC, p, m_tiles, p.n_tiles, s, tile_rows);
 }
 
 extern "C" int ffm_grouped_gemm_wgrad(const void* A, const void* B, int groups, const int32_t* tile_start,

@@ -782,7 +782,8 @@ extern "C" int ffm_route_forward(const void* hidden, const void* gate_w, const f
   // scoring kernel. Few experts: everything in one warp-level kernel.
   const bool tensor_gate = E > 32 && D % 64 == 0 && E % 32 == 0 && logits != nullptr;
   if (tensor_gate) {
-    const int rc = ffm_grouped_gemm(hidden, gate_w, FFM_B_KMAJOR, 1, nullptr, N, D, E, 1.0f, logits, status, stream);
+    const int rc = ffm_grouped_gemm(hidden, gate_w, FFM_B_KMAJOR, 1, nullptr, N, D, E, 1.0f, logits, nullptr, 0, status,
+                                    stream);
     if (rc != FFM_OK) return rc;
 #define FFM_LOGIT_CASE(NG)                                                                                      \
   route_from_logits<NG><<<g.blocks, ROUTE_THREADS, 0, s>>>(lg, expert_bias, N, E, top_k, opts, g.tokens_per_block, \

@@ -279,9 +279,11 @@ class _FusedMoEFunction(torch.autograd.Function):
         Xg = ops.permute_rows(h, routing.src, routing.rows_cap, k)
         need_grad = any(ctx.needs_input_grad[:5])
         keep = need_grad and not cfg.recompute
+        # inference with few rows per expert (decode): one CTA per 128-row tile and no work on tiles without rows
+        small = _small_m_kwargs(not need_grad and cfg.capacity is None and N * k < 128 * E, routing.counts)
         act, pre = ops.grouped_gemm_glu(Xg, wu, wu.view(-1, D)[H:], 2 * H, E, routing.tile_start, D, H,
-                                        cfg.activation, want_preact=keep)
-        Y = ops.grouped_gemm(act, wd, _lib.B_KMAJOR, E, routing.tile_start, H, D)
+                                        cfg.activation, want_preact=keep, **small)
+        Y = ops.grouped_gemm(act, wd, _lib.B_KMAJOR, E, routing.tile_start, H, D, **small)
         out = ops.combine_forward(Y, routing.pos, routing.topk_w, N, k, addend=add)
 
         ctx.set_materialize_grads(False)
@@ -477,9 +479,12 @@ def _ep_forward_static(hidden_states, gate_weight, w_up, w_down, sw, cfg, dtype)
     # (the padding rows of the grouped layout stay as they are: without a backward pass nothing sums over them, and
     # a GEMM row only depends on its own input row)
     Xg = px.region_view(0, cap_rows, D, h.dtype)
+    small = _small_m_kwargs(ep * _EP_STATIC_TOKENS * k < 128 * E, None)
+    if small:
+        small["valid_rows"] = C[:, px.rank * El:(px.rank + 1) * El].sum(0, dtype=torch.int32)
     act, _ = ops.grouped_gemm_glu(Xg, wu, wu.view(-1, D)[H:], 2 * H, El, t["tile_start"], D, H, cfg.activation,
-                                  want_preact=False)
-    Y = ops.grouped_gemm(act, wd, _lib.B_KMAJOR, El, t["tile_start"], H, D)
+                                  want_preact=False, **small)
+    Y = ops.grouped_gemm(act, wd, _lib.B_KMAJOR, El, t["tile_start"], H, D, **small)
     px.push_rows_dev(Y, None, 1, rb, t["combine"], t["combine_end"], tot[1:2], cap_rows, 1)
     px.barrier_dev()
     returned = px.region_view(1, T, D, h.dtype)
@@ -488,6 +493,13 @@ def _ep_forward_static(hidden_states, gate_weight, w_up, w_down, sw, cfg, dtype)
     out = ops.combine_forward(returned, cpos, routing.topk_w, N, k, addend=shared_out)
     aux, z = _loss_tensors(routing, N, E, cfg)
     return out, aux, z, routing.counts, torch.zeros(1, dtype=torch.int32, device=h.device)
+
+
+def _small_m_kwargs(enabled, counts):
+    """Arguments that make the grouped GEMMs use 128-row single-CTA tiles and skip tiles without valid rows."""
+    if not enabled:
+        return {}
+    return dict(valid_rows=None if counts is None else counts.to(torch.int32), tile_rows=128)
 
 
 def _compact_send_map(routing, T):
@@ -586,9 +598,12 @@ class _FusedMoEEPFunction(torch.autograd.Function):
                 recv = ops.grouped_gemm(recv, lwu, _lib.B_KMAJOR, 1, None, L, D) if M > 0 else recv.new_empty(0, D)
             Xg = ops.permute_rows(recv, src_l, rows_l, 1) if M > 0 else None
         if M > 0:
+            small = _small_m_kwargs(not need_grad and M < 128 * El, None)
+            if small:
+                small["valid_rows"] = recv_counts.sum(0, dtype=torch.int32)
             act, pre = ops.grouped_gemm_glu(Xg, wu, wu.view(-1, D)[H:], 2 * H, El, ts_l, D, H, cfg.activation,
-                                            want_preact=need_grad)
-            Y = ops.grouped_gemm(act, wd, _lib.B_KMAJOR, El, ts_l, H, D)
+                                            want_preact=need_grad, **small)
+            Y = ops.grouped_gemm(act, wd, _lib.B_KMAJOR, El, ts_l, H, D, **small)
             # direct: the grouped rows go back as they lie; otherwise back to arrival order [M, D] first
             local_out = Y if direct else ops.combine_forward(Y, pos_l, None, M, 1)
         else:

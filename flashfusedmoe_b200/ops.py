@@ -218,8 +218,11 @@ def permute_rows(x, src, rows_cap, top_k):
     return out
 
 
-def grouped_gemm_glu(A, w_gate, w_up, group_rows_, groups, tile_start, K, H, activation, want_preact=True):
-    """act = glu(A Wg^T, A Wu^T). w_gate / w_up are tensors whose data pointers address the first gate / up row."""
+def grouped_gemm_glu(A, w_gate, w_up, group_rows_, groups, tile_start, K, H, activation, want_preact=True,
+                     valid_rows=None, tile_rows=0):
+    """act = glu(A Wg^T, A Wu^T). w_gate / w_up are tensors whose data pointers address the first gate / up row.
+    valid_rows (int32 [groups], device): tiles beyond a group's valid rows are skipped; tile_rows 128 / 256 picks the
+    tile shape for this call (0 = library default)."""
     lib = _lib.load()
     _req(A, torch.bfloat16, "A")
     rows = A.shape[0]
@@ -227,13 +230,13 @@ def grouped_gemm_glu(A, w_gate, w_up, group_rows_, groups, tile_start, K, H, act
     pre = torch.empty(rows, 2 * H, dtype=torch.bfloat16, device=A.device) if want_preact else None
     with _Launch("gemm_up_glu", 1):
         rc = lib.ffm_grouped_gemm_glu(_ptr(A), _ptr(w_gate), _ptr(w_up), group_rows_, groups, _ptr(tile_start), rows, K,
-                                      H, _lib.ACTIVATION[activation], _ptr(act), _ptr(pre),
-                                      _ptr(status_tensor(A.device)), _stream())
+                                      H, _lib.ACTIVATION[activation], _ptr(act), _ptr(pre), _ptr(valid_rows),
+                                      int(tile_rows), _ptr(status_tensor(A.device)), _stream())
     _lib.check(rc, "ffm_grouped_gemm_glu")
     return act, pre
 
 
-def grouped_gemm(A, B, b_major, groups, tile_start, K, n_out, scale=1.0):
+def grouped_gemm(A, B, b_major, groups, tile_start, K, n_out, scale=1.0, valid_rows=None, tile_rows=0):
     lib = _lib.load()
     _req(A, torch.bfloat16, "A")
     _req(B, torch.bfloat16, "B")
@@ -241,7 +244,8 @@ def grouped_gemm(A, B, b_major, groups, tile_start, K, n_out, scale=1.0):
     out = torch.empty(rows, n_out, dtype=torch.bfloat16, device=A.device)
     with _Launch("gemm", 1):
         rc = lib.ffm_grouped_gemm(_ptr(A), _ptr(B), b_major, groups, _ptr(tile_start), rows, K, n_out, float(scale),
-                                  _ptr(out), _ptr(status_tensor(A.device)), _stream())
+                                  _ptr(out), _ptr(valid_rows), int(tile_rows), _ptr(status_tensor(A.device)),
+                                  _stream())
     _lib.check(rc, "ffm_grouped_gemm")
     return out
 

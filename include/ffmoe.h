@@ -178,12 +178,19 @@ int ffm_permute_rows(const void* x, const int32_t* src, int64_t rows_cap, int to
  *   Replaces the weight-gradient bmms (fused_moe.py:564-565, :961-966). A is [rows_cap, M], B is
  *   [rows_cap, Nout], dW is [groups, M, Nout]. Padding rows must be finite in A and zero in A or B.
  *   Limits: M % 64 == 0, Nout % 64 == 0.
+ * valid_rows / tile_rows (the two grouped-M entry points): valid_rows, when not NULL, is an int32 [groups] device array
+ *   of the valid rows of every group; 128-row tiles beyond them are then not computed (their output rows stay
+ *   unwritten). tile_rows picks the tile shape for this call: 256 = CTA pair, 128 = one CTA per tile, 0 = the
+ *   library default (ffm_set_gemm_cta_pair). With few rows per group (decode) 128 with valid_rows halves the
+ *   tensor-core work, which is then hidden behind the weight stream.
  * ------------------------------------------------------------------------------------------------- */
 int ffm_grouped_gemm_glu(const void* A, const void* w_gate, const void* w_up, int64_t group_rows, int groups,
                          const int32_t* tile_start, int64_t rows, int K, int H, int activation, void* act,
-                         void* preact, int32_t* status, ffm_stream_t stream);
+                         void* preact, const int32_t* valid_rows, int tile_rows, int32_t* status,
+                         ffm_stream_t stream);
 int ffm_grouped_gemm(const void* A, const void* B, int b_major, int groups, const int32_t* tile_start,
-                     int64_t rows, int K, int Nout, float scale, void* out, int32_t* status, ffm_stream_t stream);
+                     int64_t rows, int K, int Nout, float scale, void* out, const int32_t* valid_rows,
+                     int tile_rows, int32_t* status, ffm_stream_t stream);
 int ffm_grouped_gemm_wgrad(const void* A, const void* B, int groups, const int32_t* tile_start, int64_t rows_cap,
                            int M, int Nout, float scale, void* dW, int32_t* status, ffm_stream_t stream);
 

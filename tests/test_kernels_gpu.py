@@ -331,3 +331,38 @@ def test_route_backward(N, D, E, k, gating):
     dG_ref = gl.T @ hidden.float()
     assert rel_err(dH, dH_ref) < 2e-2
     assert rel_err(dGate, dG_ref) < 2e-2
+
+
+@pytest.mark.parametrize("tile_rows", [128, 256])
+def test_grouped_gemm_skips_tiles_without_valid_rows(tile_rows):
+    """valid_rows / tile_rows: rows of tiles that hold valid rows are bit-identical to the full computation; tiles
+    beyond a group's valid rows are left unwritten."""
+    torch.manual_seed(17)
+    counts = [5, 0, 200, 128, 300, 1, 129]
+    K, H = 128, 192
+    A, ts, row_expert, rows_cap = _grouped_case(counts, K)
+    E = len(counts)
+    cnt = torch.tensor(counts, dtype=torch.int32, device=DEV)
+    W = (torch.randn(E, 2 * H, K, device=DEV) * 0.05).bfloat16()
+    Wd = (torch.randn(E, K, H, device=DEV) * 0.05).bfloat16()
+    act_full, _ = ops.grouped_gemm_glu(A, W, W.view(-1, K)[H:], 2 * H, E, ts, K, H, "swiglu", want_preact=False)
+    y_full = ops.grouped_gemm(act_full, Wd, _lib.B_KMAJOR, E, ts, H, K)
+    act, _ = ops.grouped_gemm_glu(A, W, W.view(-1, K)[H:], 2 * H, E, ts, K, H, "swiglu", want_preact=False,
+                                  valid_rows=cnt, tile_rows=tile_rows)
+    sentinel = torch.full_like(y_full, 7.0)
+    lib = _lib.load()
+    rc = lib.ffm_grouped_gemm(act.data_ptr(), Wd.data_ptr(), _lib.B_KMAJOR, E, ts.data_ptr(), rows_cap, H, K, 1.0,
+                              sentinel.data_ptr(), cnt.data_ptr(), tile_rows, ops.status_tensor(A.device).data_ptr(),
+                              torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    ops.check_status()
+    valid = row_expert >= 0
+    assert torch.equal(act[valid], act_full[valid])
+    assert torch.equal(sentinel[valid], y_full[valid])
+    # rows of tiles (128 rows, or 256 for the pair shape) that start beyond a group's valid rows were not touched
+    tsl = ts.tolist()
+    for e, c in enumerate(counts):
+        first_untouched = tsl[e] * 128 + (c + tile_rows - 1) // tile_rows * tile_rows
+        end = tsl[e + 1] * 128
+        if first_untouched < end:
+            assert (sentinel[first_untouched:end] == 7.0).all(), e
