@@ -98,6 +98,16 @@ class ClockSampler:
             self.proc = subprocess.Popen([sys.executable, "-c", _SAMPLER_SCRIPT, uuid, self.path],
                                          stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL)
             self.mode = "nvml"
+            # wait until the child has initialised NVML and written its first sample: the first NVML initialisation on
+            # a box takes a while and stalls kernel launches of other processes while it runs
+            deadline = time.time() + 15.0
+            while time.time() < deadline and self.proc.poll() is None:
+                try:
+                    if sum(1 for _ in open(self.path)) >= 2:
+                        break
+                except OSError:
+                    pass
+                time.sleep(0.05)
             return
         except Exception:
             self.proc = None
@@ -310,13 +320,18 @@ def main():
     launches0 = ops.launch_count
     t0 = torch.cuda.Event(enable_timing=True)
     t1 = torch.cuda.Event(enable_timing=True)
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(K - 1)]  # per-step marks: a view into the region
     t0.record()
-    for _ in range(K):
+    for i in range(K):
         step()
+        if i < K - 1:
+            marks[i].record()
     t1.record()
     fence()
     launches = ops.launch_count - launches0
     ms = t0.elapsed_time(t1)
+    edges = [t0] + marks + [t1]
+    step_ms = sorted(edges[i].elapsed_time(edges[i + 1]) for i in range(K))
     ops.check_status()
 
     # ---- per-kernel pass: the same K steps again with a CUDA-event pair around every launch of this library ----
@@ -423,7 +438,8 @@ def main():
         value = tokens * world * K / (ms * 1e-3)
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
-            "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "ms_per_step": ms / K, "step_ms_median": step_ms[K // 2], "step_ms_max": step_ms[-1],
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
             "config": {"workload": "BASELINE configs[1]: MoELayer d_model=1024 ffn_dim=4096 E=8 top_k=2 swiglu + 1 shared "
                                    "expert (ffn_dim 4096), x [8,2048,1024] bf16 seed 1, weights N(0,0.02), forward+backward",

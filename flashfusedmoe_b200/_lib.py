@@ -51,6 +51,8 @@ SIGNATURES = {
     "ffm_combine_backward": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p,
                                      c_void_p, c_void_p]),
     "ffm_glu_backward": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_void_p, c_void_p]),
+    "ffm_compact_positions": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p, c_void_p,
+                                      c_void_p]),
     "ffm_p2p_push": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     "ffm_p2p_push_rows": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_void_p, c_void_p, c_int, c_int64, c_void_p, c_int,
                                   c_void_p]),

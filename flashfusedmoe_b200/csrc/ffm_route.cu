@@ -869,6 +869,48 @@ extern "C" int ffm_group_rows_static(const int32_t* expert_ids, int64_t T, int E
   return cudaGetLastError() == cudaSuccess ? FFM_OK : FFM_ERR_LAUNCH;
 }
 
+namespace ffm {
+namespace {
+
+// Positions of the routed rows in the grouped order with the 256-row padding squeezed out (the order in which an
+// expert-parallel rank sends them), and the inverse map. Every block rebuilds the per-expert shift in shared memory.
+__global__ void __launch_bounds__(ROUTE_THREADS)
+compact_positions_kernel(const int32_t* __restrict__ pos, const int32_t* __restrict__ topk_idx,
+                         const int32_t* __restrict__ counts, const int32_t* __restrict__ tile_start, long long T, int E,
+                         int32_t* __restrict__ cpos, int32_t* __restrict__ src_c) {
+  __shared__ int s_shift[MAX_E];  // padded position minus compact position for rows of expert e
+  if (threadIdx.x == 0) {
+    int before = 0;
+    for (int e = 0; e < E; ++e) {
+      s_shift[e] = tile_start[e] * 128 - before;
+      before += counts[e];
+    }
+  }
+  __syncthreads();
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i < T) {
+    const int c = pos[i] - s_shift[topk_idx[i]];
+    cpos[i] = c;
+    src_c[c] = static_cast<int32_t>(i);
+  }
+}
+
+}  // namespace
+}  // namespace ffm
+
+extern "C" int ffm_compact_positions(const int32_t* pos, const int32_t* topk_idx, const int32_t* counts,
+                                     const int32_t* tile_start, int64_t T, int E, int32_t* cpos, int32_t* src_c,
+                                     ffm_stream_t stream) {
+  if (!pos || !topk_idx || !counts || !tile_start || !cpos || !src_c) return FFM_ERR_BAD_ARG;
+  if (T < 0 || E < 1) return FFM_ERR_BAD_ARG;
+  if (E > ffm::MAX_E) return FFM_ERR_UNSUPPORTED;
+  if (T == 0) return FFM_OK;
+  const int blocks = static_cast<int>((T + ffm::ROUTE_THREADS - 1) / ffm::ROUTE_THREADS);
+  ffm::compact_positions_kernel<<<blocks, ffm::ROUTE_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
+      pos, topk_idx, counts, tile_start, T, E, cpos, src_c);
+  return cudaGetLastError() == cudaSuccess ? FFM_OK : FFM_ERR_LAUNCH;
+}
+
 extern "C" int ffm_route_apply_capacity(float* topk_w, const int32_t* topk_idx, const int32_t* pos, int32_t* src,
                                         const int32_t* tile_start, int64_t N, int top_k, int E, int capacity,
                                         int32_t* dropped_count, ffm_stream_t stream) {

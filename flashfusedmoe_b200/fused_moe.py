@@ -47,6 +47,10 @@ _EP_TRANSPORT = os.environ.get("FFM_EP_TRANSPORT", "p2p")
 # Measurement aid: when set, the row exchanges move nothing (the receive buffers keep whatever they held) while
 # every other kernel of the step still runs; the difference against a normal step is the exposed exchange time.
 _EP_DRY_EXCHANGE = False
+# Single GPU: run the HBM-bound kernels of the backward (routing backward, GLU backward, un-permute) beside the
+# tensor-core GEMMs that do not depend on them, on a second stream (the persistent GEMM leaves registers, threads
+# and a few KiB of shared memory free on every SM, so their blocks co-reside). FFM_OVERLAP=0 keeps one stream.
+_OVERLAP = os.environ.get("FFM_OVERLAP", "1") != "0"
 # Peer-store transport only: move rows straight into the receivers' grouped layout (FFM_EP_DIRECT=0 keeps the
 # contiguous-range exchange with a permute on either side, the layout the NCCL transport also uses).
 _EP_DIRECT = os.environ.get("FFM_EP_DIRECT", "1") != "0"
@@ -137,6 +141,7 @@ class _Cfg:
     topk_group: int = 0
     capacity: Optional[int] = None
     input_jitter: float = 0.0
+    addend_ready: object = None   # CUDA event: the addend (shared expert output) was produced on another stream
 
 
 def _to(t, dtype):
@@ -237,6 +242,24 @@ class _GLUFFNFunction(torch.autograd.Function):
 
 
 @torch.compiler.disable
+def run_beside(fn, *args):
+    """fn(*args) on the shared-expert side stream, ordered after the work already queued on the current stream.
+    Returns (result, event recorded when it is done), or (fn(*args), None) when overlap is switched off. Autograd
+    runs the backward of what fn recorded on that same stream, beside the routed experts' backward."""
+    if not _OVERLAP or not args[0].is_cuda:
+        return fn(*args), None
+    side = _get_side_stream("shared", priority=-1)
+    fork = torch.cuda.Event()
+    fork.record()
+    with torch.cuda.stream(side):
+        side.wait_event(fork)
+        out = fn(*args)
+        done = torch.cuda.Event()
+        done.record(side)
+    return out, done
+
+
+@torch.compiler.disable
 def glu_ffn(x, w_gate, w_up, w_down, activation="swiglu"):
     """Dense GLU feed-forward on the library's GEMM kernels. x [N, D] -> [N, D]."""
     dtype = _require_bf16(_get_compute_dtype(x.dtype))
@@ -284,6 +307,9 @@ class _FusedMoEFunction(torch.autograd.Function):
         act, pre = ops.grouped_gemm_glu(Xg, wu, wu.view(-1, D)[H:], 2 * H, E, routing.tile_start, D, H,
                                         cfg.activation, want_preact=keep, **small)
         Y = ops.grouped_gemm(act, wd, _lib.B_KMAJOR, E, routing.tile_start, H, D, **small)
+        if add is not None and cfg.addend_ready is not None:
+            torch.cuda.current_stream().wait_event(cfg.addend_ready)
+            add.record_stream(torch.cuda.current_stream())
         out = ops.combine_forward(Y, routing.pos, routing.topk_w, N, k, addend=add)
 
         ctx.set_materialize_grads(False)
@@ -322,14 +348,44 @@ class _FusedMoEFunction(torch.autograd.Function):
         go = _to(grad_out, h.dtype)  # also densifies expanded (stride-0) gradients
 
         gYw, gw = ops.combine_backward(go, Y, topk_w, src, ctx.rows_cap, k)
-        d_act = ops.grouped_gemm(gYw, wd, _lib.B_NMAJOR, E, tile_start, D, H)
-        gU = ops.glu_backward(d_act, pre, tile_start, E, cfg.activation)
-        dXg = ops.grouped_gemm(gU, wu, _lib.B_NMAJOR, E, tile_start, 2 * H, D)
-        dH = ops.combine_forward(dXg, pos, None, N, k)
-        d_wd = ops.grouped_gemm_wgrad(gYw, act, E, tile_start)
-        d_wu = ops.grouped_gemm_wgrad(gU, Xg, E, tile_start)
-        gaux, gz = _loss_grads(routing, N, E, cfg, grad_aux, grad_z)
-        dH, d_gate = ops.route_backward(gw, routing, gaux, gz, h, g, cfg.gating, dH=dH)
+        if _OVERLAP:
+            # main: dAct GEMM -> GLU backward -> dX GEMM -> un-permute (+ routing term)
+            # aux:  routing backward -> dW_down GEMM ............ -> dW_up GEMM
+            main = torch.cuda.current_stream()
+            aux = _get_side_stream("backward_aux")
+            fork = torch.cuda.Event()
+            fork.record(main)
+            with torch.cuda.stream(aux):
+                aux.wait_event(fork)
+                gaux, gz = _loss_grads(routing, N, E, cfg, grad_aux, grad_z)
+                dH_route, d_gate = ops.route_backward(gw, routing, gaux, gz, h, g, cfg.gating, dH=None)
+                route_done = torch.cuda.Event()
+                route_done.record(aux)
+                d_wd = ops.grouped_gemm_wgrad(gYw, act, E, tile_start)
+            d_act = ops.grouped_gemm(gYw, wd, _lib.B_NMAJOR, E, tile_start, D, H)
+            gU = ops.glu_backward(d_act, pre, tile_start, E, cfg.activation)
+            gu_done = torch.cuda.Event()
+            gu_done.record(main)
+            with torch.cuda.stream(aux):
+                aux.wait_event(gu_done)
+                d_wu = ops.grouped_gemm_wgrad(gU, Xg, E, tile_start)
+                join = torch.cuda.Event()
+                join.record(aux)
+            dXg = ops.grouped_gemm(gU, wu, _lib.B_NMAJOR, E, tile_start, 2 * H, D)
+            main.wait_event(route_done)
+            dH = ops.combine_forward(dXg, pos, None, N, k, addend=dH_route)
+            main.wait_event(join)
+            for t_aux in (dH_route, d_gate, d_wd, d_wu):
+                t_aux.record_stream(main)  # allocated on the aux stream, consumed on the main one from here on
+        else:
+            d_act = ops.grouped_gemm(gYw, wd, _lib.B_NMAJOR, E, tile_start, D, H)
+            gU = ops.glu_backward(d_act, pre, tile_start, E, cfg.activation)
+            dXg = ops.grouped_gemm(gU, wu, _lib.B_NMAJOR, E, tile_start, 2 * H, D)
+            dH = ops.combine_forward(dXg, pos, None, N, k)
+            d_wd = ops.grouped_gemm_wgrad(gYw, act, E, tile_start)
+            d_wu = ops.grouped_gemm_wgrad(gU, Xg, E, tile_start)
+            gaux, gz = _loss_grads(routing, N, E, cfg, grad_aux, grad_z)
+            dH, d_gate = ops.route_backward(gw, routing, gaux, gz, h, g, cfg.gating, dH=dH)
 
         dt = ctx.in_dtypes
         d_add = None
@@ -503,15 +559,9 @@ def _small_m_kwargs(enabled, counts):
 
 
 def _compact_send_map(routing, T):
-    """Send-buffer position of every flat slot: the grouped order with the 128-row padding squeezed out.
+    """Send-buffer position of every flat slot: the grouped order with the 256-row padding squeezed out.
     Rows are expert-major, hence destination-rank-major (each rank owns a contiguous block of experts)."""
-    counts = routing.counts.to(torch.int64)
-    starts = torch.cumsum(counts, 0) - counts
-    pad = routing.tile_start[:-1].to(torch.int64) * 128 - starts
-    cpos = (routing.pos.to(torch.int64) - pad[routing.topk_idx.reshape(-1).to(torch.int64)])
-    src_c = torch.empty(T, dtype=torch.int32, device=cpos.device)
-    src_c[cpos] = torch.arange(T, dtype=torch.int32, device=cpos.device)
-    return cpos.to(torch.int32), src_c
+    return ops.compact_positions(routing, T)
 
 
 class _FusedMoEEPFunction(torch.autograd.Function):
@@ -814,6 +864,7 @@ def fused_moe(
     expert_bias=None,
     ep_full_input_grad=False,
     _addend=None,
+    _addend_ready=None,
 ):
     """Fused MoE forward; returns (output [N, D], losses dict). Arguments as in the reference
     (fused_moe.py:1073-1138). `_addend` is a private hook used by MoELayer to fold the shared expert's output
@@ -846,7 +897,7 @@ def fused_moe(
                aux_grad=_AUX_LOSS_GRAD, ep_group=group, ep_full_input_grad=bool(ep_full_input_grad),
                pre_softmax=bool(pre_softmax) and gating == "softmax", n_group=int(n_group) if use_groups else 0,
                topk_group=int(topk_group) if use_groups else 0, capacity=capacity,
-               input_jitter=float(input_jitter or 0.0))
+               input_jitter=float(input_jitter or 0.0), addend_ready=_addend_ready)
 
     if group is not None:
         sw = shared_expert_weights if shared_expert_weights is not None else (None, None, None)

@@ -10,7 +10,7 @@ import math
 import torch
 import torch.nn as nn
 
-from .fused_moe import fused_moe, glu_ffn, set_ep_group
+from .fused_moe import fused_moe, glu_ffn, run_beside, set_ep_group
 
 
 class _GLUFFN(nn.Module):
@@ -92,15 +92,16 @@ class MoELayer(nn.Module):
         x_flat = x.reshape(-1, D)
 
         shared_weights = None
-        addend = None
+        addend = addend_ready = None
         if self.shared_expert is not None:
             if self._ep_group is not None:
                 # EP: the shared expert runs inside fused_moe on a side stream (reference: nn.py:126-132)
                 shared_weights = (self.shared_expert.w_gate.weight, self.shared_expert.w_up.weight,
                                   self.shared_expert.w_down.weight)
             else:
-                # single GPU: computed first, added to the routed output inside the combine kernel
-                addend = self.shared_expert(x_flat)
+                # single GPU: runs on a side stream beside the routing kernels and is added to the routed output
+                # inside the combine kernel
+                addend, addend_ready = run_beside(self.shared_expert, x_flat)
 
         latent_weights = None
         if self.latent_dim is not None:
@@ -113,7 +114,7 @@ class MoELayer(nn.Module):
             recompute_activations=self.recompute_activations,
             max_tokens_per_expert=self.max_tokens_per_expert, allow_dropped_tokens=self.allow_dropped_tokens,
             shared_expert_weights=shared_weights, latent_weights=latent_weights,
-            ep_full_input_grad=self.ep_full_input_grad, _addend=addend)
+            ep_full_input_grad=self.ep_full_input_grad, _addend=addend, _addend_ready=addend_ready)
         return out.reshape(*leading, D), losses
 
     def shard_experts(self, ep_group, ep_backend="nccl"):

@@ -218,6 +218,20 @@ def permute_rows(x, src, rows_cap, top_k):
     return out
 
 
+def compact_positions(routing, T):
+    """(cpos, src_c): send-order position of every flat slot and its inverse (ffm_compact_positions)."""
+    lib = _lib.load()
+    dev = routing.pos.device
+    cpos = torch.empty(T, dtype=torch.int32, device=dev)
+    src_c = torch.empty(T, dtype=torch.int32, device=dev)
+    with _Launch("compact_positions", 1):
+        rc = lib.ffm_compact_positions(_ptr(routing.pos), _ptr(routing.topk_idx), _ptr(routing.counts),
+                                       _ptr(routing.tile_start), T, routing.counts.numel(), _ptr(cpos), _ptr(src_c),
+                                       _stream())
+    _lib.check(rc, "ffm_compact_positions")
+    return cpos, src_c
+
+
 def grouped_gemm_glu(A, w_gate, w_up, group_rows_, groups, tile_start, K, H, activation, want_preact=True,
                      valid_rows=None, tile_rows=0):
     """act = glu(A Wg^T, A Wu^T). w_gate / w_up are tensors whose data pointers address the first gate / up row.

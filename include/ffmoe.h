@@ -238,6 +238,16 @@ int ffm_route_backward(const float* gw, const float* topk_w, const int32_t* topk
                        void* workspace, size_t workspace_bytes, ffm_stream_t stream);
 
 /* -------------------------------------------------------------------------------------------------
+ * ffm_compact_positions: cpos[i] = position of flat slot i in the grouped order without the 256-row padding (the
+ *   order in which an expert-parallel rank sends its rows, expert-major), src_c = the inverse map (int32 [T]).
+ *   Inputs are ffm_route_forward's pos, topk_idx, counts and tile_start. Replaces the stable sort by destination
+ *   rank of the reference's dispatcher (expert_parallel.py:225-236). E <= 256.
+ * ------------------------------------------------------------------------------------------------- */
+int ffm_compact_positions(const int32_t* pos, const int32_t* topk_idx, const int32_t* counts,
+                          const int32_t* tile_start, int64_t T, int E, int32_t* cpos, int32_t* src_c,
+                          ffm_stream_t stream);
+
+/* -------------------------------------------------------------------------------------------------
  * Expert-parallel exchange over NVLink with plain peer stores. Replaces the c10d all_to_all_single calls of the
  * reference's dispatcher (expert_parallel.py:253-258, :290-292; fused_moe.py:901-910).
  * The caller owns the receive buffers and the flag arrays, which must be mapped on every GPU of the group
