@@ -39,7 +39,7 @@ SIGNATURES = {
                                c_void_p, c_size_t, c_void_p, c_void_p]),
     "ffm_group_rows_static": (c_int, [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
                                       c_void_p, c_void_p]),
-    "ffm_permute_rows": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p]),
+    "ffm_permute_rows": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_void_p]),
     "ffm_grouped_gemm_glu": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p, c_int64, c_int, c_int,
                                      c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
     "ffm_grouped_gemm": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p, c_int64, c_int, c_int, c_float,

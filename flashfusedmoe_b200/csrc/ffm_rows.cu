@@ -11,7 +11,7 @@ constexpr int ROW_WARPS = ROW_THREADS / 32;
 
 __global__ void __launch_bounds__(ROW_THREADS)
 permute_rows_kernel(const bf16* __restrict__ x, const int32_t* __restrict__ src, long long rows, int top_k, int D,
-                    bf16* __restrict__ grouped) {
+                    int zero_padding, bf16* __restrict__ grouped) {
   const int lane = threadIdx.x & 31;
   const int chunks = D >> 3;
   for (long long r = static_cast<long long>(blockIdx.x) * ROW_WARPS + (threadIdx.x >> 5); r < rows;
@@ -19,7 +19,9 @@ permute_rows_kernel(const bf16* __restrict__ x, const int32_t* __restrict__ src,
     const int i = src[r];
     uint4* dst = reinterpret_cast<uint4*>(grouped + r * D);
     if (i < 0) {
-      for (int c = lane; c < chunks; c += 32) dst[c] = make_uint4(0, 0, 0, 0);
+      if (zero_padding) {
+        for (int c = lane; c < chunks; c += 32) dst[c] = make_uint4(0, 0, 0, 0);
+      }
     } else {
       const uint4* s = reinterpret_cast<const uint4*>(x + static_cast<long long>(i / top_k) * D);
       for (int c = lane; c < chunks; c += 32) dst[c] = __ldg(s + c);
@@ -48,8 +50,12 @@ combine_forward_kernel(const bf16* __restrict__ Y, const int32_t* __restrict__ p
                        const bf16* __restrict__ addend, long long N, int top_k, int D, bf16* __restrict__ out) {
   const int lane = threadIdx.x & 31;
   const int chunks = D >> 3;
-  for (long long n = static_cast<long long>(blockIdx.x) * ROW_WARPS + (threadIdx.x >> 5); n < N;
-       n += static_cast<long long>(gridDim.x) * ROW_WARPS) {
+  const int cblocks = (chunks + 31) >> 5;  // a warp handles one token and one block of 32 chunks (256 columns)
+  const long long items = N * cblocks;
+  for (long long item = static_cast<long long>(blockIdx.x) * ROW_WARPS + (threadIdx.x >> 5); item < items;
+       item += static_cast<long long>(gridDim.x) * ROW_WARPS) {
+    const long long n = item / cblocks;
+    const int c0 = static_cast<int>(item % cblocks) << 5;
     // lane j < k holds slot j's row and weight
     int my_pos = 0;
     float my_w = 0.0f;
@@ -57,8 +63,8 @@ combine_forward_kernel(const bf16* __restrict__ Y, const int32_t* __restrict__ p
       my_pos = pos[n * top_k + lane];
       my_w = (w != nullptr) ? bf16_round(w[n * top_k + lane]) : 1.0f;
     }
-    // uniform trip count: every lane takes part in the shuffles, lanes past the row end only skip memory
-    for (int c0 = 0; c0 < chunks; c0 += 32) {
+    // every lane takes part in the shuffles, lanes past the row end only skip memory
+    {
       const int c = c0 + lane;
       const bool active = c < chunks;
       float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
@@ -179,14 +185,14 @@ int grid_for_rows(long long rows) {
 
 using namespace ffm;
 
-extern "C" int ffm_permute_rows(const void* x, const int32_t* src, int64_t rows_cap, int top_k, int D, void* grouped,
-                                ffm_stream_t stream) {
+extern "C" int ffm_permute_rows(const void* x, const int32_t* src, int64_t rows_cap, int top_k, int D,
+                                int zero_padding, void* grouped, ffm_stream_t stream) {
   if (!x || !src || !grouped) return FFM_ERR_BAD_ARG;
   if (rows_cap < 0 || top_k < 1 || D <= 0) return FFM_ERR_BAD_ARG;
   if (D % 8 != 0) return FFM_ERR_UNSUPPORTED;
   if (rows_cap == 0) return FFM_OK;
   permute_rows_kernel<<<grid_for_rows(rows_cap), ROW_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const bf16*>(x), src, rows_cap, top_k, D, static_cast<bf16*>(grouped));
+      static_cast<const bf16*>(x), src, rows_cap, top_k, D, zero_padding, static_cast<bf16*>(grouped));
   return cudaGetLastError() == cudaSuccess ? FFM_OK : FFM_ERR_LAUNCH;
 }
 
@@ -196,7 +202,7 @@ extern "C" int ffm_combine_forward(const void* Y, const int32_t* pos, const floa
   if (N < 0 || top_k < 1 || D <= 0) return FFM_ERR_BAD_ARG;
   if (D % 8 != 0 || top_k > 32) return FFM_ERR_UNSUPPORTED;
   if (N == 0) return FFM_OK;
-  combine_forward_kernel<<<grid_for_rows(N), ROW_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
+  combine_forward_kernel<<<grid_for_rows(N * ((D / 8 + 31) / 32)), ROW_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const bf16*>(Y), pos, w, static_cast<const bf16*>(addend), N, top_k, D, static_cast<bf16*>(out));
   return cudaGetLastError() == cudaSuccess ? FFM_OK : FFM_ERR_LAUNCH;
 }

@@ -299,8 +299,9 @@ class _FusedMoEFunction(torch.autograd.Function):
             dropped = ops.route_apply_capacity(routing, cfg.capacity)
         else:
             dropped = torch.zeros(1, dtype=torch.int32, device=h.device)
-        Xg = ops.permute_rows(h, routing.src, routing.rows_cap, k)
         need_grad = any(ctx.needs_input_grad[:5])
+        # (without a backward pass nothing sums over the padding rows, so they are not zeroed)
+        Xg = ops.permute_rows(h, routing.src, routing.rows_cap, k, zero_padding=need_grad)
         keep = need_grad and not cfg.recompute
         # inference with few rows per expert (decode): one CTA per 128-row tile and no work on tiles without rows
         small = _small_m_kwargs(not need_grad and cfg.capacity is None and N * k < 128 * E, routing.counts)
@@ -765,9 +766,25 @@ class _FusedMoEEPFunction(torch.autograd.Function):
                          if M > 0 else recv_grad.new_empty(0, D))
         if M > 0:
             gYg = recv_grad if direct else ops.permute_rows(recv_grad, t["src_l"], rows_l, 1)
-            d_act = ops.grouped_gemm(gYg, wd, _lib.B_NMAJOR, El, t["ts_l"], D, H)
-            gU = ops.glu_backward(d_act, t["pre"], t["ts_l"], El, cfg.activation)
-            d_wd = ops.grouped_gemm_wgrad(gYg, t["act"], El, t["ts_l"], scale=inv_ep)
+            if _OVERLAP:
+                # the down-projection weight gradient does not need the GLU backward: it runs beside it
+                main = torch.cuda.current_stream()
+                aux = _get_side_stream("backward_aux")
+                fork = torch.cuda.Event()
+                fork.record(main)
+                with torch.cuda.stream(aux):
+                    aux.wait_event(fork)
+                    d_wd = ops.grouped_gemm_wgrad(gYg, t["act"], El, t["ts_l"], scale=inv_ep)
+                    join = torch.cuda.Event()
+                    join.record(aux)
+                d_act = ops.grouped_gemm(gYg, wd, _lib.B_NMAJOR, El, t["ts_l"], D, H)
+                gU = ops.glu_backward(d_act, t["pre"], t["ts_l"], El, cfg.activation)
+                main.wait_event(join)
+                d_wd.record_stream(main)
+            else:
+                d_act = ops.grouped_gemm(gYg, wd, _lib.B_NMAJOR, El, t["ts_l"], D, H)
+                gU = ops.glu_backward(d_act, t["pre"], t["ts_l"], El, cfg.activation)
+                d_wd = ops.grouped_gemm_wgrad(gYg, t["act"], El, t["ts_l"], scale=inv_ep)
             d_wu = ops.grouped_gemm_wgrad(gU, t["Xg"], El, t["ts_l"], scale=inv_ep)
             if cfg.ep_full_input_grad:
                 # opt-in: the expert input gradient the reference leaves out (fused_moe.py:1001-1005) travels back

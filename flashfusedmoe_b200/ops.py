@@ -206,15 +206,16 @@ def group_rows(expert_ids, num_experts):
     return counts, tile_start, pos[:T], src, rows_cap
 
 
-def permute_rows(x, src, rows_cap, top_k):
+def permute_rows(x, src, rows_cap, top_k, zero_padding=True):
+    """grouped[r] = x[src[r] // top_k]; padding rows (src < 0) are zeroed unless zero_padding is False."""
     lib = _lib.load()
     _req(x, torch.bfloat16, "x")
     _req(src, torch.int32, "src")
     D = x.shape[1]
     out = torch.empty(rows_cap, D, dtype=torch.bfloat16, device=x.device)
     with _Launch("permute_rows", 1):
-        _lib.check(lib.ffm_permute_rows(_ptr(x), _ptr(src), rows_cap, top_k, D, _ptr(out), _stream()),
-               "ffm_permute_rows")
+        _lib.check(lib.ffm_permute_rows(_ptr(x), _ptr(src), rows_cap, top_k, D, 1 if zero_padding else 0, _ptr(out),
+                                        _stream()), "ffm_permute_rows")
     return out
 
 

@@ -150,12 +150,13 @@ int ffm_group_rows_static(const int32_t* expert_ids, int64_t T, int E, int32_t* 
                           int32_t* pos, int32_t* src, int64_t rows_cap, int32_t* status, ffm_stream_t stream);
 
 /* -------------------------------------------------------------------------------------------------
- * Permute: grouped[r, :] = x[src[r] / k, :] for src[r] >= 0, zero otherwise.
+ * Permute: grouped[r, :] = x[src[r] / k, :] for src[r] >= 0; other rows are zeroed, or with zero_padding == 0 left
+ * as they are (forward without gradients: nothing sums over padding rows).
  * Replaces fused_routing_scatter (kernels/moe_ops.py:53-149) without the padded [E, max_tokens, D] buffer.
  * Limits: D % 8 == 0.
  * ------------------------------------------------------------------------------------------------- */
-int ffm_permute_rows(const void* x, const int32_t* src, int64_t rows_cap, int top_k, int D, void* grouped,
-                     ffm_stream_t stream);
+int ffm_permute_rows(const void* x, const int32_t* src, int64_t rows_cap, int top_k, int D, int zero_padding,
+                     void* grouped, ffm_stream_t stream);
 
 /* -------------------------------------------------------------------------------------------------
  * Grouped GEMMs on tcgen05 / TMEM tiles fed by TMA (256 x 256 x 64 tiles on CTA pairs, fp32 accumulation,

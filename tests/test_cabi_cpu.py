@@ -51,7 +51,7 @@ def test_host_only_entry_points():
 def test_argument_validation_without_gpu():
     lib = _lib.load()
     # null pointers are rejected before any CUDA call
-    assert lib.ffm_permute_rows(0, 0, 128, 1, 64, 0, 0) == -1
+    assert lib.ffm_permute_rows(0, 0, 128, 1, 64, 1, 0, 0) == -1
     assert lib.ffm_grouped_gemm(0, 0, 0, 1, 0, 128, 64, 64, 1.0, 0, 0, 0, 0, 0) == -1
     assert lib.ffm_combine_forward(0, 0, 0, 0, 4, 2, 64, 0, 0) == -1
 

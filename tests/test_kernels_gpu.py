@@ -366,3 +366,93 @@ def test_grouped_gemm_skips_tiles_without_valid_rows(tile_rows):
         end = tsl[e + 1] * 128
         if first_untouched < end:
             assert (sentinel[first_untouched:end] == 7.0).all(), e
+
+
+def test_compact_positions_matches_stable_sort():
+    torch.manual_seed(23)
+    N, D, E, k = 700, 64, 16, 3
+    hidden = torch.randn(N, D, device=DEV).bfloat16()
+    gate = (torch.randn(E, D, device=DEV) * 0.3).bfloat16()
+    r = ops.route_forward(hidden, gate, k, "softmax")
+    cpos, src_c = ops.compact_positions(r, N * k)
+    ops.check_status()
+    order = torch.argsort(r.topk_idx.view(-1).long(), stable=True)        # flat slots sorted by expert
+    assert torch.equal(src_c.long(), order)
+    inv = torch.empty_like(order)
+    inv[order] = torch.arange(N * k, device=DEV)
+    assert torch.equal(cpos.long(), inv)
+
+
+@pytest.mark.parametrize("ep,e_local", [(2, 4), (4, 2), (8, 1), (8, 32), (16, 16)])
+def test_device_exchange_plan_matches_host_plan(ep, e_local):
+    """ffm_p2p_plan (device) against p2p.SegmentPlan (host): same runs, ends, padding, tile_start and totals."""
+    import numpy as np
+    from flashfusedmoe_b200.p2p import SegmentPlan
+    rng = np.random.default_rng(ep * 100 + e_local)
+    E = ep * e_local
+    C = rng.integers(0, 600, size=(ep, E))
+    C[rng.random((ep, E)) < 0.25] = 0
+    C[:, E // 2] = 0
+    lib = _lib.load()
+    Cd = torch.tensor(C, dtype=torch.int32, device=DEV)
+    i64 = dict(dtype=torch.int64, device=DEV)
+    for rank in (0, ep - 1, ep // 2):
+        host = SegmentPlan(C, e_local, rank)
+        d, de = torch.empty(E, 4, **i64), torch.empty(E, **i64)
+        c, ce = torch.empty(e_local * ep, 4, **i64), torch.empty(e_local * ep, **i64)
+        p, pe = torch.empty(e_local, 4, **i64), torch.empty(e_local, **i64)
+        ts = torch.empty(e_local + 1, dtype=torch.int32, device=DEV)
+        tot = torch.empty(4, **i64)
+        rc = lib.ffm_p2p_plan(Cd.data_ptr(), ep, e_local, rank, d.data_ptr(), de.data_ptr(), c.data_ptr(),
+                              ce.data_ptr(), p.data_ptr(), pe.data_ptr(), ts.data_ptr(), tot.data_ptr(),
+                              torch.cuda.current_stream().cuda_stream)
+        assert rc == 0
+        torch.cuda.synchronize()
+
+        def nonempty(seg, end):
+            seg, end = seg.cpu().numpy(), end.cpu().numpy()
+            keep = seg[:, 2] > 0
+            return seg[keep], end[keep]
+
+        for (dev_seg, dev_end), (h_seg, h_end) in (((d, de), host.dispatch), ((c, ce), host.combine),
+                                                   ((p, pe), host.padding)):
+            s, e = nonempty(dev_seg, dev_end)
+            assert np.array_equal(s, h_seg) and np.array_equal(e, h_end)
+        assert ts.cpu().tolist() == host.tile_start[rank].tolist()
+        assert tot.cpu().tolist() == [int(host.send_rows[rank]), int(host.recv_rows[rank]),
+                                      int(host.padding[0][:, 2].sum()), int(host.rows_grouped[rank])]
+
+
+def test_push_rows_gathers_scatters_and_zeroes_locally():
+    """ffm_p2p_push_rows with every destination on this GPU: gather through an index, run-wise scatter, zero rows,
+    and the variant that reads the row total on the device."""
+    torch.manual_seed(29)
+    lib = _lib.load()
+    W = 96
+    src = torch.randn(50, W, device=DEV).bfloat16()
+    index = torch.randint(0, 50 * 2, (40,), dtype=torch.int32, device=DEV)          # flat slots, two per token
+    dst0 = torch.full((64, W), 3.0, device=DEV).bfloat16()
+    dst1 = torch.full((64, W), 3.0, device=DEV).bfloat16()
+    seg = torch.tensor([[0, 10, 7, 0], [7, 0, 0, 1], [7, 5, 20, 1], [27, 40, 13, 0]], dtype=torch.int64, device=DEV)
+    end = torch.cumsum(seg[:, 2], 0)
+    import ctypes
+    bases = (ctypes.c_void_p * 2)(dst0.data_ptr(), dst1.data_ptr())
+    stream = torch.cuda.current_stream().cuda_stream
+    assert lib.ffm_p2p_push_rows(src.data_ptr(), index.data_ptr(), 2, W * 2, seg.data_ptr(), end.data_ptr(), 4, 40,
+                                 bases, 2, stream) == 0
+    torch.cuda.synchronize()
+    rows = src[(index // 2).long()]
+    ref0, ref1 = torch.full_like(dst0, 3.0), torch.full_like(dst1, 3.0)
+    ref0[10:17] = rows[0:7]
+    ref1[5:25] = rows[7:27]
+    ref0[40:53] = rows[27:40]
+    assert torch.equal(dst0, ref0) and torch.equal(dst1, ref1)
+    # zeroing, with the total read on the device
+    zseg = torch.tensor([[0, 60, 4, 1]], dtype=torch.int64, device=DEV)
+    zend = torch.tensor([4], dtype=torch.int64, device=DEV)
+    total = torch.tensor([4], dtype=torch.int64, device=DEV)
+    assert lib.ffm_p2p_push_rows_dev(0, 0, 1, W * 2, zseg.data_ptr(), zend.data_ptr(), 1, total.data_ptr(), 64, bases, 2,
+                                     stream) == 0
+    torch.cuda.synchronize()
+    ref1[60:64] = 0
+    assert torch.equal(dst1, ref1) and torch.equal(dst0, ref0)
