@@ -142,6 +142,7 @@ class _Cfg:
     capacity: Optional[int] = None
     input_jitter: float = 0.0
     addend_ready: object = None   # CUDA event: the addend (shared expert output) was produced on another stream
+    wants_grad: bool = True       # False: no input needs a gradient or grad mode is off (inference shortcuts apply)
 
 
 def _to(t, dtype):
@@ -299,7 +300,7 @@ class _FusedMoEFunction(torch.autograd.Function):
             dropped = ops.route_apply_capacity(routing, cfg.capacity)
         else:
             dropped = torch.zeros(1, dtype=torch.int32, device=h.device)
-        need_grad = any(ctx.needs_input_grad[:5])
+        need_grad = cfg.wants_grad and any(ctx.needs_input_grad[:5])
         # (without a backward pass nothing sums over the padding rows, so they are not zeroed)
         Xg = ops.permute_rows(h, routing.src, routing.rows_cap, k, zero_padding=need_grad)
         keep = need_grad and not cfg.recompute
@@ -589,7 +590,7 @@ class _FusedMoEEPFunction(torch.autograd.Function):
         g = _to(gate_weight, dtype)
         wu = _to(w_up, dtype)
         wd = _to(w_down, dtype)
-        need_grad = any(ctx.needs_input_grad[:9])
+        need_grad = cfg.wants_grad and any(ctx.needs_input_grad[:9])
 
         routing = _route(h, g, cfg, hidden_states.requires_grad)
 
@@ -915,13 +916,16 @@ def fused_moe(
                pre_softmax=bool(pre_softmax) and gating == "softmax", n_group=int(n_group) if use_groups else 0,
                topk_group=int(topk_group) if use_groups else 0, capacity=capacity,
                input_jitter=float(input_jitter or 0.0), addend_ready=_addend_ready)
+    sw_all = shared_expert_weights if shared_expert_weights is not None else ()
+    lw_all = latent_weights if latent_weights is not None else ()
+    cfg.wants_grad = torch.is_grad_enabled() and any(
+        t is not None and t.requires_grad
+        for t in (hidden_states, gate_weight, w_up, w_down, _addend, *sw_all, *lw_all))
 
     if group is not None:
         sw = shared_expert_weights if shared_expert_weights is not None else (None, None, None)
         lw = latent_weights if latent_weights is not None else (None, None)
-        wants_grad = torch.is_grad_enabled() and any(
-            t is not None and t.requires_grad for t in (hidden_states, gate_weight, w_up, w_down, *sw, *lw))
-        if (_EP_STATIC_TOKENS is not None and not wants_grad and lw[0] is None and _EP_TRANSPORT == "p2p"
+        if (_EP_STATIC_TOKENS is not None and not cfg.wants_grad and lw[0] is None and _EP_TRANSPORT == "p2p"
                 and p2p.available() and E % 4 == 0 and E <= 256 and cfg.input_jitter == 0.0):
             out, aux, z, counts, dropped = _ep_forward_static(hidden_states, gate_weight, w_up, w_down, sw, cfg, dtype)
         else:
