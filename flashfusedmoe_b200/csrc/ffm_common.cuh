@@ -139,6 +139,25 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
   return true;
 }
 
+}  // namespace ffm
+
+// Ask for the largest shared-memory carve-out for a kernel that itself needs little or none. The persistent GEMM
+// runs with the largest carve-out; a kernel launched on another stream can only share an SM with it (in the
+// registers, thread slots and few KiB of shared memory the GEMM leaves free) if it does not ask for a different one.
+#define FFM_PREFER_MAX_SHARED(kernel)                                                                              \
+  do {                                                                                                             \
+    static bool ffm_carveout_set = false;                                                                          \
+    if (!ffm_carveout_set) {                                                                                       \
+      ffm_carveout_set = true;                                                                                     \
+      if (cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout,                             \
+                               cudaSharedmemCarveoutMaxShared) != cudaSuccess) {                                   \
+        cudaGetLastError();                                                                                        \
+      }                                                                                                            \
+    }                                                                                                              \
+  } while (0)
+
+namespace ffm {
+
 __device__ __forceinline__ void fence_barrier_init() {
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }

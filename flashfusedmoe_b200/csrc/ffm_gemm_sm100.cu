@@ -55,19 +55,21 @@ constexpr int SMEM_LIMIT = 232448;  // 227 KiB of dynamic shared memory per CTA
 
 enum { EPI_PLAIN = 0, EPI_GLU = 1 };
 
-// Ring depth against staging depth for CTA pairs (measured at 8 x 4096 rows, D 1024, H 2048: every split from
-// 4 to 6 stages runs within 2 % of the others; the GEMMs sit at the board's power limit, not at a pipeline limit).
+// Ring depth against staging depth for CTA pairs. Measured at 8 x 4096 rows, D 1024, H 2048: every split from 4 to
+// 6 stages runs within 2 % of the others (the GEMMs sit at the board's power limit, not at a pipeline limit), so
+// the ring is kept at 4 stages: the ~50-65 KiB of shared memory this leaves free on every SM is what lets blocks
+// of an HBM-bound kernel from another stream run beside the resident GEMM CTA (with 8 KiB free they barely did).
 #ifndef FFM_TUNE_PP_STAGES
-#define FFM_TUNE_PP_STAGES 6
+#define FFM_TUNE_PP_STAGES 4
 #define FFM_TUNE_PP_STEPS 2
 #endif
 #ifndef FFM_TUNE_PG_STAGES
-#define FFM_TUNE_PG_STAGES 5
+#define FFM_TUNE_PG_STAGES 4
 #define FFM_TUNE_PG_STEPS 1
 #endif
 
 // Shared-memory budget per tile shape and epilogue: ring stages against staging boxes per epilogue warp.
-//   CTA pair, plain: 6 stages x 32 KiB + 2 boxes    CTA pair, GLU: 5 stages x 32 KiB + 3 boxes
+//   CTA pair, plain: 4 stages x 32 KiB + 2 boxes    CTA pair, GLU: 4 stages x 32 KiB + 3 boxes
 //   one CTA,  plain: 4 stages x 48 KiB + 2 boxes    one CTA,  GLU: 3 stages x 48 KiB + 3 boxes
 // A GLU step stores three boxes (activation, gate, up) as one bulk group; a plain step stores one box.
 template <int CTA2, int EPI>
@@ -761,7 +763,7 @@ int launch_gemm_shape(const CUtensorMap& tmA, const CUtensorMap& tmB0, const CUt
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = CTA2 ? 1 : 0;  // the one-CTA shape is an ordinary launch
   if (cudaLaunchKernelEx(&cfg, kernel, tmA, tmB0, tmB1, tmC, tmC2, p) != cudaSuccess) {
     cudaGetLastError();
     return FFM_ERR_LAUNCH;

@@ -281,8 +281,9 @@ route_gate_topk(const bf16* __restrict__ hidden, const bf16* __restrict__ gate_w
                 bf16* __restrict__ logits_out, float* __restrict__ topk_w, int32_t* __restrict__ topk_idx,
                 float* __restrict__ lse_out, int32_t* __restrict__ block_hist, float* __restrict__ block_mass,
                 float* __restrict__ block_z) {
-  __shared__ float s_mass[ROUTE_WARPS][MAX_E];
-  __shared__ int s_cnt[ROUTE_WARPS][MAX_E];
+  // sized for the experts this instantiation can see, so that the few-expert variants fit beside a resident GEMM
+  __shared__ float s_mass[ROUTE_WARPS][GW * NG];
+  __shared__ int s_cnt[ROUTE_WARPS][GW * NG];
   __shared__ float s_z[ROUTE_WARPS];
 
   const int warp = threadIdx.x >> 5;
@@ -666,6 +667,8 @@ template <int GW, int NG>
 void launch_route(int blocks, cudaStream_t s, const bf16* hidden, const bf16* gate_w, const float* bias, long long N,
                   int D, int E, int top_k, const RouteOpts& opts, int tpb, bf16* logits, float* topk_w,
                   int32_t* topk_idx, float* lse, const RouteWorkspace& w) {
+  auto kernel = route_gate_topk<GW, NG>;
+  FFM_PREFER_MAX_SHARED(kernel);
   route_gate_topk<GW, NG><<<blocks, ROUTE_THREADS, 0, s>>>(hidden, gate_w, bias, N, D, E, top_k, opts, tpb, logits,
                                                            topk_w, topk_idx, lse, w.block_hist, w.block_mass,
                                                            w.block_z);
@@ -815,6 +818,7 @@ extern "C" int ffm_route_forward(const void* hidden, const void* gate_w, const f
   }
 #undef FFM_ROUTE_CASE
   }
+  FFM_PREFER_MAX_SHARED(route_scan);
   route_scan<<<1, ROUTE_THREADS, 0, s>>>(w.block_hist, w.block_mass, w.block_z, g.blocks, E, w.block_off, counts,
                                          tile_start, stats);
   route_rank<<<g.blocks, ROUTE_THREADS, 0, s>>>(topk_idx, N * top_k, E, g.tokens_per_block * top_k, w.block_off,

@@ -292,6 +292,7 @@ extern "C" int ffm_route_backward(const float* gw, const float* topk_w, const in
   if (N > 0) {
     long long blocks = (N + RB_WARPS - 1) / RB_WARPS;
     if (blocks > 148LL * 16) blocks = 148LL * 16;
+    FFM_PREFER_MAX_SHARED(route_bwd_token);
     route_bwd_token<<<static_cast<int>(blocks), RB_THREADS, 0, s>>>(
         gw, topk_w, topk_idx, static_cast<const bf16*>(logits), lse, gaux, gz, static_cast<const bf16*>(gate_w), N, D,
         E, top_k, gating, accumulate, gl, static_cast<bf16*>(dH));
@@ -299,6 +300,7 @@ extern "C" int ffm_route_backward(const float* gw, const float* topk_w, const in
   DgatePlan p = plan_dgate(N > 0 ? N : 1, D, E);
   if (N > 0) {
     dim3 grid(p.chunks_n, p.col_blocks, p.e_groups);
+    FFM_PREFER_MAX_SHARED(route_bwd_dgate);
     route_bwd_dgate<<<grid, DG_THREADS, 0, s>>>(gl, static_cast<const bf16*>(hidden), N, D, E, p.tokens_per_chunk,
                                                 partial);
   }
@@ -306,6 +308,7 @@ extern "C" int ffm_route_backward(const float* gw, const float* topk_w, const in
     long long total = static_cast<long long>(E) * D;
     long long blocks = (total + 31) / 32;
     if (blocks > 148LL * 8) blocks = 148LL * 8;
+    FFM_PREFER_MAX_SHARED(route_bwd_reduce);
     route_bwd_reduce<<<static_cast<int>(blocks), 256, 0, s>>>(partial, N > 0 ? p.chunks_n : 0, D, E,
                                                               static_cast<bf16*>(dGate));
   }

@@ -191,6 +191,7 @@ extern "C" int ffm_permute_rows(const void* x, const int32_t* src, int64_t rows_
   if (rows_cap < 0 || top_k < 1 || D <= 0) return FFM_ERR_BAD_ARG;
   if (D % 8 != 0) return FFM_ERR_UNSUPPORTED;
   if (rows_cap == 0) return FFM_OK;
+  FFM_PREFER_MAX_SHARED(permute_rows_kernel);
   permute_rows_kernel<<<grid_for_rows(rows_cap), ROW_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const bf16*>(x), src, rows_cap, top_k, D, zero_padding, static_cast<bf16*>(grouped));
   return cudaGetLastError() == cudaSuccess ? FFM_OK : FFM_ERR_LAUNCH;
@@ -202,6 +203,7 @@ extern "C" int ffm_combine_forward(const void* Y, const int32_t* pos, const floa
   if (N < 0 || top_k < 1 || D <= 0) return FFM_ERR_BAD_ARG;
   if (D % 8 != 0 || top_k > 32) return FFM_ERR_UNSUPPORTED;
   if (N == 0) return FFM_OK;
+  FFM_PREFER_MAX_SHARED(combine_forward_kernel);
   combine_forward_kernel<<<grid_for_rows(N * ((D / 8 + 31) / 32)), ROW_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const bf16*>(Y), pos, w, static_cast<const bf16*>(addend), N, top_k, D, static_cast<bf16*>(out));
   return cudaGetLastError() == cudaSuccess ? FFM_OK : FFM_ERR_LAUNCH;
@@ -213,6 +215,7 @@ extern "C" int ffm_combine_backward(const void* go, const void* Y, const float* 
   if (rows_cap < 0 || top_k < 1 || D <= 0) return FFM_ERR_BAD_ARG;
   if (D % 8 != 0) return FFM_ERR_UNSUPPORTED;
   if (rows_cap == 0) return FFM_OK;
+  FFM_PREFER_MAX_SHARED(combine_backward_kernel);
   combine_backward_kernel<<<grid_for_rows(rows_cap), ROW_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const bf16*>(go), static_cast<const bf16*>(Y), w, src, rows_cap, top_k, D,
       static_cast<bf16*>(gYw), gw);
@@ -230,6 +233,7 @@ extern "C" int ffm_glu_backward(const void* dAct, const void* preact, const int3
   long long blocks = (work + ROW_THREADS - 1) / ROW_THREADS;
   const long long cap = 148LL * 32;
   if (blocks > cap) blocks = cap;
+  FFM_PREFER_MAX_SHARED(glu_backward_kernel);
   glu_backward_kernel<<<static_cast<int>(blocks), ROW_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const bf16*>(dAct), static_cast<const bf16*>(preact), tile_start, groups, rows, H, activation,
       static_cast<bf16*>(gU));

@@ -351,34 +351,42 @@ class _FusedMoEFunction(torch.autograd.Function):
 
         gYw, gw = ops.combine_backward(go, Y, topk_w, src, ctx.rows_cap, k)
         if _OVERLAP:
-            # main: dAct GEMM -> GLU backward -> dX GEMM -> un-permute (+ routing term)
-            # aux:  routing backward -> dW_down GEMM ............ -> dW_up GEMM
+            # Two GEMMs never share an SM, so the GEMMs stay in one chain and each HBM-bound kernel is paired with
+            # a GEMM that does not depend on it:
+            #   main:  dAct GEMM -> GLU backward ............ -> dX GEMM -> un-permute (+ routing term)
+            #   gemm:  (after dAct)  dW_down GEMM              (after dX)   dW_up GEMM
+            #   route: routing backward (beside the dAct GEMM)
             main = torch.cuda.current_stream()
-            aux = _get_side_stream("backward_aux")
+            gemm = _get_side_stream("backward_gemm")
+            route = _get_side_stream("backward_route")
             fork = torch.cuda.Event()
             fork.record(main)
-            with torch.cuda.stream(aux):
-                aux.wait_event(fork)
+            with torch.cuda.stream(route):
+                route.wait_event(fork)
                 gaux, gz = _loss_grads(routing, N, E, cfg, grad_aux, grad_z)
                 dH_route, d_gate = ops.route_backward(gw, routing, gaux, gz, h, g, cfg.gating, dH=None)
                 route_done = torch.cuda.Event()
-                route_done.record(aux)
-                d_wd = ops.grouped_gemm_wgrad(gYw, act, E, tile_start)
+                route_done.record(route)
             d_act = ops.grouped_gemm(gYw, wd, _lib.B_NMAJOR, E, tile_start, D, H)
+            dact_done = torch.cuda.Event()
+            dact_done.record(main)
+            with torch.cuda.stream(gemm):
+                gemm.wait_event(dact_done)
+                d_wd = ops.grouped_gemm_wgrad(gYw, act, E, tile_start)
             gU = ops.glu_backward(d_act, pre, tile_start, E, cfg.activation)
-            gu_done = torch.cuda.Event()
-            gu_done.record(main)
-            with torch.cuda.stream(aux):
-                aux.wait_event(gu_done)
+            dXg = ops.grouped_gemm(gU, wu, _lib.B_NMAJOR, E, tile_start, 2 * H, D)
+            dx_done = torch.cuda.Event()
+            dx_done.record(main)
+            with torch.cuda.stream(gemm):
+                gemm.wait_event(dx_done)
                 d_wu = ops.grouped_gemm_wgrad(gU, Xg, E, tile_start)
                 join = torch.cuda.Event()
-                join.record(aux)
-            dXg = ops.grouped_gemm(gU, wu, _lib.B_NMAJOR, E, tile_start, 2 * H, D)
+                join.record(gemm)
             main.wait_event(route_done)
             dH = ops.combine_forward(dXg, pos, None, N, k, addend=dH_route)
             main.wait_event(join)
-            for t_aux in (dH_route, d_gate, d_wd, d_wu):
-                t_aux.record_stream(main)  # allocated on the aux stream, consumed on the main one from here on
+            for t_side in (dH_route, d_gate, d_wd, d_wu):
+                t_side.record_stream(main)  # allocated on a side stream, consumed on the main one from here on
         else:
             d_act = ops.grouped_gemm(gYw, wd, _lib.B_NMAJOR, E, tile_start, D, H)
             gU = ops.glu_backward(d_act, pre, tile_start, E, cfg.activation)
@@ -770,15 +778,15 @@ class _FusedMoEEPFunction(torch.autograd.Function):
             if _OVERLAP:
                 # the down-projection weight gradient does not need the GLU backward: it runs beside it
                 main = torch.cuda.current_stream()
-                aux = _get_side_stream("backward_aux")
-                fork = torch.cuda.Event()
-                fork.record(main)
-                with torch.cuda.stream(aux):
-                    aux.wait_event(fork)
+                gemm = _get_side_stream("backward_gemm")
+                d_act = ops.grouped_gemm(gYg, wd, _lib.B_NMAJOR, El, t["ts_l"], D, H)
+                dact_done = torch.cuda.Event()
+                dact_done.record(main)
+                with torch.cuda.stream(gemm):
+                    gemm.wait_event(dact_done)
                     d_wd = ops.grouped_gemm_wgrad(gYg, t["act"], El, t["ts_l"], scale=inv_ep)
                     join = torch.cuda.Event()
-                    join.record(aux)
-                d_act = ops.grouped_gemm(gYg, wd, _lib.B_NMAJOR, El, t["ts_l"], D, H)
+                    join.record(gemm)
                 gU = ops.glu_backward(d_act, t["pre"], t["ts_l"], El, cfg.activation)
                 main.wait_event(join)
                 d_wd.record_stream(main)
