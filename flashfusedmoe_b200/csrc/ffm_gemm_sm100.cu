@@ -56,20 +56,22 @@ constexpr int SMEM_LIMIT = 232448;  // 227 KiB of dynamic shared memory per CTA
 enum { EPI_PLAIN = 0, EPI_GLU = 1 };
 
 // Ring depth against staging depth for CTA pairs. Measured at 8 x 4096 rows, D 1024, H 2048: every split from 4 to
-// 6 stages runs within 2 % of the others (the GEMMs sit at the board's power limit, not at a pipeline limit), so
-// the ring is kept at 4 stages: the ~50-65 KiB of shared memory this leaves free on every SM is what lets blocks
-// of an HBM-bound kernel from another stream run beside the resident GEMM CTA (with 8 KiB free they barely did).
+// 6 stages runs within 3 % of the others alone (the GEMMs sit at the board's power limit, not at a pipeline limit).
+// A 4-stage ring leaves ~65 KiB of shared memory free on every SM, which is what lets blocks of an HBM-bound kernel
+// from another stream run beside the resident GEMM CTA (with 8 KiB free they do not); in the layer step the two
+// effects cancel to within run-to-run noise, so the deeper ring, which is the faster GEMM on its own, is the default
+// (-DFFM_TUNE_PP_STAGES=4 -DFFM_TUNE_PG_STAGES=4 builds the other one).
 #ifndef FFM_TUNE_PP_STAGES
-#define FFM_TUNE_PP_STAGES 4
+#define FFM_TUNE_PP_STAGES 6
 #define FFM_TUNE_PP_STEPS 2
 #endif
 #ifndef FFM_TUNE_PG_STAGES
-#define FFM_TUNE_PG_STAGES 4
+#define FFM_TUNE_PG_STAGES 5
 #define FFM_TUNE_PG_STEPS 1
 #endif
 
 // Shared-memory budget per tile shape and epilogue: ring stages against staging boxes per epilogue warp.
-//   CTA pair, plain: 4 stages x 32 KiB + 2 boxes    CTA pair, GLU: 4 stages x 32 KiB + 3 boxes
+//   CTA pair, plain: 6 stages x 32 KiB + 2 boxes    CTA pair, GLU: 5 stages x 32 KiB + 3 boxes
 //   one CTA,  plain: 4 stages x 48 KiB + 2 boxes    one CTA,  GLU: 3 stages x 48 KiB + 3 boxes
 // A GLU step stores three boxes (activation, gate, up) as one bulk group; a plain step stores one box.
 template <int CTA2, int EPI>
