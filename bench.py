@@ -331,7 +331,8 @@ def main():
     launches = ops.launch_count - launches0
     ms = t0.elapsed_time(t1)
     edges = [t0] + marks + [t1]
-    step_ms = sorted(edges[i].elapsed_time(edges[i + 1]) for i in range(K))
+    step_series = [edges[i].elapsed_time(edges[i + 1]) for i in range(K)]
+    step_ms = sorted(step_series)
     ops.check_status()
 
     # ---- per-kernel pass: the same K steps again with a CUDA-event pair around every launch of this library ----
@@ -449,6 +450,7 @@ def main():
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
             "ms_per_step": ms / K, "step_ms_median": step_ms[K // 2], "step_ms_max": step_ms[-1],
+            "step_ms_first3": step_series[:3], "step_ms_last3": step_series[-3:],
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
             "config": {"workload": "BASELINE configs[1]: MoELayer d_model=1024 ffn_dim=4096 E=8 top_k=2 swiglu + 1 shared "

@@ -561,6 +561,32 @@ def _ep_forward_static(hidden_states, gate_weight, w_up, w_down, sw, cfg, dtype)
     return out, aux, z, routing.counts, torch.zeros(1, dtype=torch.int32, device=h.device)
 
 
+def _wgrad_split_factor(groups, M, n_out):
+    """How many K ranges to split every group's weight-gradient GEMM into so that its output tiles fill the GPU: with
+    few local experts (expert parallel over many ranks) groups x tiles falls below the 74 CTA pairs."""
+    units = groups * ((M + 255) // 256) * ((n_out + 255) // 256)
+    return 1 if units >= 56 else min(4, max(1, 74 // units))
+
+
+def _split_tile_start(tile_start, S):
+    """tile_start [groups + 1] -> [groups * S + 1]: every group's tile range cut into S ranges of whole tile pairs."""
+    ts = tile_start.to(torch.int64)
+    lo, pairs = ts[:-1], (ts[1:] - ts[:-1]) // 2
+    cuts = torch.stack([lo + 2 * ((pairs * s) // S) for s in range(S)], dim=1).reshape(-1)
+    return torch.cat([cuts, ts[-1:]]).to(torch.int32)
+
+
+def _grouped_wgrad(A, B, groups, tile_start, scale=1.0, split_ts=None):
+    """ops.grouped_gemm_wgrad, split along K into partial products (summed afterwards) when the output is too small
+    to occupy every SM. split_ts: precomputed (S, tile_start of the split groups), else built with a few torch ops."""
+    S = _wgrad_split_factor(groups, A.shape[1], B.shape[1])
+    if S == 1:
+        return ops.grouped_gemm_wgrad(A, B, groups, tile_start, scale=scale)
+    ts = split_ts[1] if split_ts is not None and split_ts[0] == S else _split_tile_start(tile_start, S)
+    part = ops.grouped_gemm_wgrad(A, B, groups * S, ts, scale=scale)
+    return part.view(groups, S, A.shape[1], B.shape[1]).sum(dim=1, dtype=torch.float32).to(part.dtype)
+
+
 def _small_m_kwargs(enabled, counts):
     """Arguments that make the grouped GEMMs use 128-row single-CTA tiles and skip tiles without valid rows."""
     if not enabled:
@@ -784,7 +810,7 @@ class _FusedMoEEPFunction(torch.autograd.Function):
                 dact_done.record(main)
                 with torch.cuda.stream(gemm):
                     gemm.wait_event(dact_done)
-                    d_wd = ops.grouped_gemm_wgrad(gYg, t["act"], El, t["ts_l"], scale=inv_ep)
+                    d_wd = _grouped_wgrad(gYg, t["act"], El, t["ts_l"], scale=inv_ep)
                     join = torch.cuda.Event()
                     join.record(gemm)
                 gU = ops.glu_backward(d_act, t["pre"], t["ts_l"], El, cfg.activation)
@@ -793,8 +819,8 @@ class _FusedMoEEPFunction(torch.autograd.Function):
             else:
                 d_act = ops.grouped_gemm(gYg, wd, _lib.B_NMAJOR, El, t["ts_l"], D, H)
                 gU = ops.glu_backward(d_act, t["pre"], t["ts_l"], El, cfg.activation)
-                d_wd = ops.grouped_gemm_wgrad(gYg, t["act"], El, t["ts_l"], scale=inv_ep)
-            d_wu = ops.grouped_gemm_wgrad(gU, t["Xg"], El, t["ts_l"], scale=inv_ep)
+                d_wd = _grouped_wgrad(gYg, t["act"], El, t["ts_l"], scale=inv_ep)
+            d_wu = _grouped_wgrad(gU, t["Xg"], El, t["ts_l"], scale=inv_ep)
             if cfg.ep_full_input_grad:
                 # opt-in: the expert input gradient the reference leaves out (fused_moe.py:1001-1005) travels back
                 # through a reverse dispatch exchange and is summed over each token's k slots
