@@ -68,14 +68,20 @@ while True:
         out.flush()
     except nv.NVMLError:
         pass
-    time.sleep(0.01)
+    time.sleep(float(sys.argv[3]))
 """
+
+
+# NVML polling period. Measured on this pool: a poll every 10 ms stalled a step of the timed region by 2-24 ms in
+# one run out of three (steps are 1.8 ms), every 100 ms still in two of three, once a second never; 200 ms is the
+# period of the `nvidia-smi -lms 200` line it replaces.
+SAMPLE_S = float(os.environ.get("FFM_BENCH_SAMPLE_MS", "200")) / 1e3
 
 
 class ClockSampler:
     """SM clock, power and throttle reasons of one GPU while the timed regions run. Read-only.
 
-    A child process polls NVML every 10 ms from before the warm-up (the device is looked up by the UUID torch
+    A child process polls NVML every 200 ms from before the warm-up (the device is looked up by the UUID torch
     reports, so CUDA_VISIBLE_DEVICES does not matter) and stamps every sample with the wall clock; begin() and
     stop() bracket the timed regions and only samples between them are used. A child process rather than a thread:
     the step loop is close to CPU-bound at N > 1 and must not share the interpreter lock with the sampler.
@@ -95,7 +101,7 @@ class ClockSampler:
         try:
             import pynvml  # noqa: F401  (only to know whether the child can import it)
             uuid = "GPU-" + str(torch.cuda.get_device_properties(self.gpu_index).uuid)
-            self.proc = subprocess.Popen([sys.executable, "-c", _SAMPLER_SCRIPT, uuid, self.path],
+            self.proc = subprocess.Popen([sys.executable, "-c", _SAMPLER_SCRIPT, uuid, self.path, str(SAMPLE_S)],
                                          stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL)
             self.mode = "nvml"
             # wait until the child has initialised NVML and written its first sample: the first NVML initialisation on
@@ -155,7 +161,7 @@ class ClockSampler:
                     mask |= s[2]
                 return {"sm_mhz": statistics.median(busy), "sm_max_mhz": sm_max, "sm_mhz_min": min(sm),
                         "power_w_max": max(s[1] for s in samples), "samples": len(sm), "samples_under_load": len(busy),
-                        "source": "nvml, child process, 10 ms",
+                        "source": f"nvml, child process, {SAMPLE_S * 1e3:.0f} ms",
                         "reasons": sorted(n for n, bit in self.REASON_BITS if mask & bit)}
             return {"sm_mhz": None, "sm_max_mhz": sm_max, "samples": 0, "reasons": ["no NVML samples in the timed window"]}
         time.sleep(0.25)

@@ -65,7 +65,7 @@ SIGNATURES = {
     "ffm_route_backward_workspace_bytes": (c_size_t, [c_int64, c_int, c_int]),
     "ffm_route_backward": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                    c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
-                                   c_void_p, c_size_t, c_void_p]),
+                                   c_void_p, c_size_t, c_void_p, c_void_p]),
 }
 
 _lib = None

@@ -5,6 +5,10 @@
 //                      two skinny GEMMs, then dH[n, :] (+)= gl[n, :] * gate_w, skipping zero entries.
 //   route_bwd_dgate    dGate partial sums over chunks of tokens (fp32), 8 experts x 8 columns per thread.
 //   route_bwd_reduce   fixed-order sum of the partials -> bf16 dGate.
+// Many experts (E a multiple of 64, D a multiple of 64, at least 1024 tokens): dGate = gl^T hidden is a GEMM with the
+// token dimension as K, so it runs on the tensor cores instead (ffm_grouped_gemm_wgrad over DG_SPLITS ranges of the
+// tokens, partial products in bf16, summed in fixed order by dgate_sum_splits); the dense CUDA-core reduction costs
+// N E D multiply-adds, 285 us at N = 16384, E = 64, D = 2048.
 #include "ffm_common.cuh"
 
 namespace ffm {
@@ -235,6 +239,27 @@ route_bwd_reduce(const float* __restrict__ partial, int chunks_n, int D, int E, 
   }
 }
 
+constexpr int DG_SPLITS = 8;
+
+// tile_start of DG_SPLITS equal ranges (whole tile pairs) over `pairs` pairs of 128-row tiles
+__global__ void dgate_split_tiles(int32_t* __restrict__ ts, int pairs) {
+  const int s = threadIdx.x;
+  if (s <= DG_SPLITS) ts[s] = 2 * static_cast<int>((static_cast<long long>(pairs) * s) / DG_SPLITS);
+}
+
+__global__ void __launch_bounds__(256) dgate_sum_splits(const bf16* __restrict__ part, long long total,
+                                                        bf16* __restrict__ dGate) {
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float t = 0.0f;
+#pragma unroll
+    for (int k = 0; k < DG_SPLITS; ++k) t += __bfloat162float(part[k * total + i]);
+    dGate[i] = __float2bfloat16_rn(t);
+  }
+}
+
+bool dgate_on_tensor_cores(long long N, int D, int E) { return E % 64 == 0 && D % 64 == 0 && N >= 1024; }
+
 struct DgatePlan {
   int chunks_n;
   int tokens_per_chunk;
@@ -267,17 +292,22 @@ using namespace ffm;
 extern "C" size_t ffm_route_backward_workspace_bytes(int64_t N, int D, int E) {
   if (N < 0 || D <= 0 || E < 1) return 0;
   const int ldg_ = (E + 7) & ~7;
+  const size_t gl_bytes = align256(static_cast<size_t>(N > 0 ? N : 1) * ldg_ * 2);
+  if (dgate_on_tensor_cores(N, D, E)) {
+    return gl_bytes + align256(static_cast<size_t>(DG_SPLITS) * E * D * 2) + 256;  // partials (bf16) + tile_start
+  }
   DgatePlan p = plan_dgate(N > 0 ? N : 1, D, E);
-  return align256(static_cast<size_t>(N > 0 ? N : 1) * ldg_ * 2) +
-         align256(static_cast<size_t>(p.chunks_n) * ldg_ * D * 4);
+  return gl_bytes + align256(static_cast<size_t>(p.chunks_n) * ldg_ * D * 4);
 }
 
 extern "C" int ffm_route_backward(const float* gw, const float* topk_w, const int32_t* topk_idx, const void* logits,
                                   const float* lse, const float* gaux, const float* gz, const void* hidden,
                                   const void* gate_w, int64_t N, int D, int E, int top_k, int gating, int accumulate,
-                                  void* dH, void* dGate, void* workspace, size_t workspace_bytes,
+                                  void* dH, void* dGate, void* workspace, size_t workspace_bytes, int32_t* status,
                                   ffm_stream_t stream) {
-  if (!gw || !topk_w || !topk_idx || !hidden || !gate_w || !dH || !dGate || !workspace) return FFM_ERR_BAD_ARG;
+  if (!gw || !topk_w || !topk_idx || !hidden || !gate_w || !dH || !dGate || !workspace || !status) {
+    return FFM_ERR_BAD_ARG;
+  }
   if (N < 0 || D <= 0 || E < 1 || top_k < 1) return FFM_ERR_BAD_ARG;
   if (gating != FFM_GATING_SOFTMAX && gating != FFM_GATING_SIGMOID) return FFM_ERR_BAD_ARG;
   const bool need_logits = gating == FFM_GATING_SIGMOID || gz != nullptr;
@@ -296,6 +326,21 @@ extern "C" int ffm_route_backward(const float* gw, const float* topk_w, const in
     route_bwd_token<<<static_cast<int>(blocks), RB_THREADS, 0, s>>>(
         gw, topk_w, topk_idx, static_cast<const bf16*>(logits), lse, gaux, gz, static_cast<const bf16*>(gate_w), N, D,
         E, top_k, gating, accumulate, gl, static_cast<bf16*>(dH));
+  }
+  if (dgate_on_tensor_cores(N, D, E)) {
+    // gl is [N, E] contiguous here (E % 8 == 0). dGate[e, :] = sum_n gl[n, e] hidden[n, :]
+    uint8_t* base = static_cast<uint8_t*>(workspace) + align256(static_cast<size_t>(N) * ldg_ * 2);
+    bf16* part = reinterpret_cast<bf16*>(base);
+    int32_t* ts = reinterpret_cast<int32_t*>(base + align256(static_cast<size_t>(DG_SPLITS) * E * D * 2));
+    const int pairs = static_cast<int>((N + 255) / 256);
+    dgate_split_tiles<<<1, 32, 0, s>>>(ts, pairs);
+    const int rc = ffm_grouped_gemm_wgrad(gl, hidden, DG_SPLITS, ts, N, E, D, 1.0f, part, status, stream);
+    if (rc != FFM_OK) return rc;
+    const long long total = static_cast<long long>(E) * D;
+    long long blocks = (total + 255) / 256;
+    if (blocks > 148LL * 8) blocks = 148LL * 8;
+    dgate_sum_splits<<<static_cast<int>(blocks), 256, 0, s>>>(part, total, static_cast<bf16*>(dGate));
+    return cudaGetLastError() == cudaSuccess ? FFM_OK : FFM_ERR_LAUNCH;
   }
   DgatePlan p = plan_dgate(N > 0 ? N : 1, D, E);
   if (N > 0) {

@@ -335,6 +335,6 @@ def route_backward(gw, routing, gaux, gz, hidden, gate_w, gating, dH=None):
         rc = lib.ffm_route_backward(_ptr(gw), _ptr(routing.topk_w), _ptr(routing.topk_idx), _ptr(routing.logits),
                                     _ptr(routing.lse), _ptr(gaux), _ptr(gz), _ptr(hidden), _ptr(gate_w), N, D, E,
                                     routing.top_k, _lib.GATING[gating], 1 if accumulate else 0, _ptr(dH), _ptr(dGate),
-                                    _ptr(ws), ws.numel(), _stream())
+                                    _ptr(ws), ws.numel(), _ptr(status_tensor(dev)), _stream())
     _lib.check(rc, "ffm_route_backward")
     return dH, dGate

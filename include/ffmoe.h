@@ -230,13 +230,14 @@ int ffm_glu_backward(const void* dAct, const void* preact, const int32_t* tile_s
  * gaux [E] f32 or NULL: d loss / d P_e (softmax gating: added to gw of every slot routed to e).
  * gz: device pointer to one f32 = d loss / d (sum_n lse^2 / N), i.e. z_loss_coeff * upstream gradient;
  *     NULL (or a stored 0) disables the term. A device scalar keeps the backward pass free of host syncs.
- * workspace: ffm_route_backward_workspace_bytes(N, D, E).
+ * workspace: ffm_route_backward_workspace_bytes(N, D, E). status: the library's status word (with E % 64 == 0,
+ * D % 64 == 0 and N >= 1024 the dGate product runs as a tensor-core GEMM over the tokens, whose waits report there).
  * ------------------------------------------------------------------------------------------------- */
 size_t ffm_route_backward_workspace_bytes(int64_t N, int D, int E);
 int ffm_route_backward(const float* gw, const float* topk_w, const int32_t* topk_idx, const void* logits,
                        const float* lse, const float* gaux, const float* gz, const void* hidden, const void* gate_w,
                        int64_t N, int D, int E, int top_k, int gating, int accumulate, void* dH, void* dGate,
-                       void* workspace, size_t workspace_bytes, ffm_stream_t stream);
+                       void* workspace, size_t workspace_bytes, int32_t* status, ffm_stream_t stream);
 
 /* -------------------------------------------------------------------------------------------------
  * ffm_compact_positions: cpos[i] = position of flat slot i in the grouped order without the 256-row padding (the

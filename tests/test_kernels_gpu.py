@@ -301,7 +301,8 @@ def test_glu_backward(activation):
 
 
 @pytest.mark.parametrize("gating", ["softmax", "sigmoid"])
-@pytest.mark.parametrize("N,D,E,k", [(33, 64, 4, 2), (512, 256, 8, 2), (200, 128, 64, 6), (64, 2048, 256, 8)])
+@pytest.mark.parametrize("N,D,E,k", [(33, 64, 4, 2), (512, 256, 8, 2), (200, 128, 64, 6), (64, 2048, 256, 8),
+                                     (2500, 256, 64, 6), (1024, 128, 128, 4)])  # the last two: dGate on tensor cores
 def test_route_backward(N, D, E, k, gating):
     torch.manual_seed(N + k)
     hidden = torch.randn(N, D, device=DEV).bfloat16()
