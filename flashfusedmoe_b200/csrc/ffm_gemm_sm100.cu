@@ -5,6 +5,10 @@
 //   warp 1      MMA issuer     (one lane issues tcgen05.mma; the warp owns the TMEM allocation)
 //   warps 2..5  epilogue       (tcgen05.ld of the fp32 accumulator one chunk ahead, math, bf16 rows staged in
 //                               swizzled shared memory and written out with cp.async.bulk.tensor stores)
+//   warps 6..13 passenger      (optional, PASS = 1: eight more warps run an independent HBM-bound job, the GLU
+//                               backward, while the tensor pipe works. A resident GEMM CTA leaves no room on its SM
+//                               for blocks of another kernel, so a memory-bound kernel launched beside a GEMM on
+//                               another stream simply waits; riding inside the GEMM's own CTAs is how it overlaps.)
 //
 // Two tile shapes from one template:
 //   CTA2 = 0   one CTA per 128 x 256 tile, tcgen05.mma.cta_group::1, 4 stages of (A 16 KiB + B 32 KiB)
@@ -45,6 +49,7 @@ constexpr int UMMA_K = 16;
 constexpr int NUM_ACC = 2;
 constexpr int TMEM_COLS = 512;
 constexpr int GEMM_THREADS = 192;
+constexpr int PASSENGER_THREADS = 256;
 constexpr int EPI_WARPS = 4;
 constexpr int MAX_GROUPS = 256;
 constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KiB
@@ -107,6 +112,13 @@ struct GemmParams {
   int n_tiles;            // number of BN (GLU: 128-column) blocks over n_cols
   int32_t* status;
   long long wait_cycles;
+  // passenger job (PASS = 1): gU = GLU backward of (dAct, pre-activations), see ffm_glu_backward
+  const bf16* pz_dact;
+  const bf16* pz_pre;
+  bf16* pz_gu;
+  long long pz_rows;
+  int pz_h;
+  int pz_act;
 };
 
 struct Ctrl {
@@ -270,8 +282,53 @@ __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 
-template <int A_MN, int B_MN, int EPI, int GROUPK, int CTA2>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+// GLU backward over rows [0, pz_rows): (d gate | d up)[r, :] from dAct[r, :] and the saved pre-activations.
+// `tid` / `nthreads` enumerate the passenger threads of the whole grid; four independent 16-byte column chunks per
+// thread and trip keep enough loads in flight for 256 threads per SM to stream at HBM speed.
+__device__ __forceinline__ void passenger_glu_backward(const GemmParams& p, long long tid, long long nthreads) {
+  const int H = p.pz_h;
+  const int chunks = H >> 3;
+  const long long total = p.pz_rows * chunks;
+  for (long long base = tid; base < total; base += 4 * nthreads) {
+    uint4 ga[4], gg[4], uu[4];
+    long long r[4];
+    int c[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const long long idx = base + u * nthreads;
+      if (idx < total) {
+        r[u] = idx / chunks;
+        c[u] = static_cast<int>(idx % chunks);
+        ga[u] = __ldg(reinterpret_cast<const uint4*>(p.pz_dact + r[u] * H) + c[u]);
+        gg[u] = __ldg(reinterpret_cast<const uint4*>(p.pz_pre + r[u] * 2 * H) + c[u]);
+        uu[u] = __ldg(reinterpret_cast<const uint4*>(p.pz_pre + r[u] * 2 * H + H) + c[u]);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const long long idx = base + u * nthreads;
+      if (idx < total) {
+        const uint32_t gav[4] = {ga[u].x, ga[u].y, ga[u].z, ga[u].w};
+        const uint32_t ggv[4] = {gg[u].x, gg[u].y, gg[u].z, gg[u].w};
+        const uint32_t uuv[4] = {uu[u].x, uu[u].y, uu[u].z, uu[u].w};
+        uint32_t dg[4], du[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float2 a = unpack_bf16x2(gav[q]), g = unpack_bf16x2(ggv[q]), v = unpack_bf16x2(uuv[q]);
+          const float2 r0 = glu_bwd(p.pz_act, a.x, g.x, v.x);
+          const float2 r1 = glu_bwd(p.pz_act, a.y, g.y, v.y);
+          dg[q] = pack_bf16x2(r0.x, r1.x);
+          du[q] = pack_bf16x2(r0.y, r1.y);
+        }
+        reinterpret_cast<uint4*>(p.pz_gu + r[u] * 2 * H)[c[u]] = make_uint4(dg[0], dg[1], dg[2], dg[3]);
+        reinterpret_cast<uint4*>(p.pz_gu + r[u] * 2 * H + H)[c[u]] = make_uint4(du[0], du[1], du[2], du[3]);
+      }
+    }
+  }
+}
+
+template <int A_MN, int B_MN, int EPI, int GROUPK, int CTA2, int PASS = 0>
+__global__ void __launch_bounds__(GEMM_THREADS + PASS * PASSENGER_THREADS, 1)
 ffm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB0,
                 const __grid_constant__ CUtensorMap tmB1, const __grid_constant__ CUtensorMap tmC,
                 const __grid_constant__ CUtensorMap tmC2, const GemmParams p) {
@@ -312,7 +369,7 @@ ffm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   }
   if (!GROUPK && p.group_rows != nullptr) {
     // walk only the tiles that hold valid rows: per group ceil(rows / 128), rounded up to a pair with CTA2
-    for (int i = threadIdx.x; i < p.groups; i += GEMM_THREADS) {
+    for (int i = threadIdx.x; i < p.groups; i += blockDim.x) {
       const int tiles = (p.group_rows[i] + BM - 1) / BM;
       ctrl->tile_start[i + 1] = CTA2 ? ((tiles + 1) & ~1) : tiles;
     }
@@ -326,7 +383,7 @@ ffm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       }
     }
   } else if (p.tile_start != nullptr) {
-    for (int i = threadIdx.x; i <= p.groups; i += GEMM_THREADS) ctrl->tile_start[i] = p.tile_start[i];
+    for (int i = threadIdx.x; i <= p.groups; i += blockDim.x) ctrl->tile_start[i] = p.tile_start[i];
   } else if (threadIdx.x == 0) {
     ctrl->tile_start[0] = 0;
     ctrl->tile_start[1] = p.dense_m_tiles;
@@ -481,6 +538,10 @@ ffm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         }
       }
     }
+  } else if (PASS && warp >= 2 + EPI_WARPS) {
+    // ================= passenger (warps 6..13) =================
+    passenger_glu_backward(p, static_cast<long long>(blockIdx.x) * PASSENGER_THREADS + (threadIdx.x - GEMM_THREADS),
+                           static_cast<long long>(gridDim.x) * PASSENGER_THREADS);
   } else {
     // ================= epilogue (warps 2..5) =================
     const int quarter = warp & 3;  // TMEM lanes [32 * quarter, 32 * quarter + 32) belong to this warp
@@ -718,11 +779,12 @@ bool use_cta_pair() {
   return g_cta_pair != 0;
 }
 
-template <int A_MN, int B_MN, int EPI, int GROUPK, int CTA2>
+template <int A_MN, int B_MN, int EPI, int GROUPK, int CTA2, int PASS = 0>
 int launch_gemm_shape(const CUtensorMap& tmA, const CUtensorMap& tmB0, const CUtensorMap& tmB1, const CUtensorMap& tmC,
                       const CUtensorMap& tmC2, const GemmParams& p, long long max_units, cudaStream_t stream) {
   static int max_ctas = 0;  // persistent grid size, found once per instantiation
-  auto kernel = ffm_gemm_kernel<A_MN, B_MN, EPI, GROUPK, CTA2>;
+  auto kernel = ffm_gemm_kernel<A_MN, B_MN, EPI, GROUPK, CTA2, PASS>;
+  constexpr int threads = GEMM_THREADS + PASS * PASSENGER_THREADS;
   constexpr int smem_bytes = Shape<CTA2, EPI>::SMEM_BYTES;
   if (max_ctas == 0) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess) {
@@ -734,7 +796,7 @@ int launch_gemm_shape(const CUtensorMap& tmA, const CUtensorMap& tmB0, const CUt
       // co-resident CTA pairs: a GPC with an odd number of usable SMs leaves one SM without a partner
       cudaLaunchConfig_t q = {};
       q.gridDim = dim3(num_sms() & ~1, 1, 1);
-      q.blockDim = dim3(GEMM_THREADS, 1, 1);
+      q.blockDim = dim3(threads, 1, 1);
       q.dynamicSmemBytes = smem_bytes;
       cudaLaunchAttribute qa[1];
       qa[0].id = cudaLaunchAttributeClusterDimension;
@@ -751,12 +813,13 @@ int launch_gemm_shape(const CUtensorMap& tmA, const CUtensorMap& tmB0, const CUt
       max_ctas = 2 * clusters;
     }
   }
-  if (max_units <= 0) return FFM_OK;
+  if (max_units <= 0 && !(PASS && p.pz_rows > 0)) return FFM_OK;
   long long ctas = CTA2 ? 2 * max_units : max_units;
+  if (PASS && p.pz_rows > 0) ctas = max_ctas;  // the passenger job wants every SM, whatever the GEMM's tile count
   if (ctas > max_ctas) ctas = max_ctas;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(ctas), 1, 1);
-  cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
+  cfg.blockDim = dim3(threads, 1, 1);
   cfg.dynamicSmemBytes = smem_bytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -775,16 +838,17 @@ int launch_gemm_shape(const CUtensorMap& tmA, const CUtensorMap& tmB0, const CUt
 
 // max_m_tiles: upper bound on the 128-row tiles of M the walker can see (per group for grouped-K);
 // multiplier: tiles per M tile (N blocks, times groups for grouped-K).
-template <int A_MN, int B_MN, int EPI, int GROUPK>
+template <int A_MN, int B_MN, int EPI, int GROUPK, int PASS = 0>
 int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB0, const CUtensorMap& tmB1, const CUtensorMap& tmC,
                 const CUtensorMap& tmC2, const GemmParams& p, long long max_m_tiles, long long multiplier,
                 cudaStream_t stream, int tile_rows = 0) {
   const bool pair = tile_rows == 256 ? true : (tile_rows == 128 ? false : use_cta_pair());
   if (pair) {
-    return launch_gemm_shape<A_MN, B_MN, EPI, GROUPK, 1>(tmA, tmB0, tmB1, tmC, tmC2, p,
+    return launch_gemm_shape<A_MN, B_MN, EPI, GROUPK, 1, PASS>(tmA, tmB0, tmB1, tmC, tmC2, p,
                                                          ((max_m_tiles + 1) / 2) * multiplier, stream);
   }
-  return launch_gemm_shape<A_MN, B_MN, EPI, GROUPK, 0>(tmA, tmB0, tmB1, tmC, tmC2, p, max_m_tiles * multiplier, stream);
+  return launch_gemm_shape<A_MN, B_MN, EPI, GROUPK, 0, PASS>(tmA, tmB0, tmB1, tmC, tmC2, p, max_m_tiles * multiplier,
+                                                              stream);
 }
 
 }  // namespace
@@ -910,6 +974,40 @@ extern "C" int ffm_grouped_gemm_wgrad(const void* A, const void* B, int groups, 
   p.status = status;
   p.wait_cycles = g_wait_cycles;
   return launch_gemm<1, 1, EPI_PLAIN, 1>(tmA, tmB, tmB, tmC, tmC, p, p.m_tiles_per_group,
+                                         static_cast<long long>(groups) * p.n_tiles,
+                                         static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int ffm_grouped_gemm_wgrad_glu_backward(const void* A, const void* B, int groups, const int32_t* tile_start,
+                                                   int64_t rows_cap, int M, int Nout, float scale, void* dW,
+                                                   const void* dAct, const void* preact, int64_t glu_rows, int H,
+                                                   int activation, void* gU, int32_t* status, ffm_stream_t stream) {
+  if (!dAct || !preact || !gU || glu_rows < 0 || H <= 0 || H % 8 != 0) return FFM_ERR_BAD_ARG;
+  if (activation < 0 || activation > 3) return FFM_ERR_BAD_ARG;
+  if (!A || !B || !dW || !status || !tile_start) return FFM_ERR_BAD_ARG;
+  if (groups < 1 || groups > MAX_GROUPS || rows_cap <= 0 || M <= 0 || Nout <= 0) return FFM_ERR_BAD_ARG;
+  if (M % 64 != 0 || Nout % 64 != 0) return FFM_ERR_UNSUPPORTED;
+  CUtensorMap tmA, tmB, tmC;
+  int rc;
+  if ((rc = make_map_2d(&tmA, A, rows_cap, M, 64, 64)) != FFM_OK) return rc;
+  if ((rc = make_map_2d(&tmB, B, rows_cap, Nout, 64, 64)) != FFM_OK) return rc;
+  if ((rc = make_out_map(&tmC, dW, groups, M, Nout)) != FFM_OK) return rc;
+  GemmParams p = {};
+  p.tile_start = tile_start;
+  p.groups = groups;
+  p.n_cols = Nout;
+  p.scale = scale;
+  p.m_tiles_per_group = (M + BM - 1) / BM;
+  p.n_tiles = (Nout + BN - 1) / BN;
+  p.status = status;
+  p.wait_cycles = g_wait_cycles;
+  p.pz_dact = static_cast<const bf16*>(dAct);
+  p.pz_pre = static_cast<const bf16*>(preact);
+  p.pz_gu = static_cast<bf16*>(gU);
+  p.pz_rows = glu_rows;
+  p.pz_h = H;
+  p.pz_act = activation;
+  return launch_gemm<1, 1, EPI_PLAIN, 1, 1>(tmA, tmB, tmB, tmC, tmC, p, p.m_tiles_per_group,
                                          static_cast<long long>(groups) * p.n_tiles,
                                          static_cast<cudaStream_t>(stream));
 }

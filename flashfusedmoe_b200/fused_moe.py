@@ -47,9 +47,9 @@ _EP_TRANSPORT = os.environ.get("FFM_EP_TRANSPORT", "p2p")
 # Measurement aid: when set, the row exchanges move nothing (the receive buffers keep whatever they held) while
 # every other kernel of the step still runs; the difference against a normal step is the exposed exchange time.
 _EP_DRY_EXCHANGE = False
-# Single GPU: run the HBM-bound kernels of the backward (routing backward, GLU backward, un-permute) beside the
-# tensor-core GEMMs that do not depend on them, on a second stream (the persistent GEMM leaves registers, threads
-# and a few KiB of shared memory free on every SM, so their blocks co-reside). FFM_OVERLAP=0 keeps one stream.
+# Overlap of HBM-bound kernels with the tensor-core GEMMs: the routing backward and the shared expert on side streams
+# (they fill the gaps and tails between GEMMs), the GLU backward as a passenger inside the dW_down GEMM's CTAs.
+# FFM_OVERLAP=0 keeps one stream and separate kernels.
 _OVERLAP = os.environ.get("FFM_OVERLAP", "1") != "0"
 # Peer-store transport only: move rows straight into the receivers' grouped layout (FFM_EP_DIRECT=0 keeps the
 # contiguous-range exchange with a permute on either side, the layout the NCCL transport also uses).
@@ -205,18 +205,22 @@ def _glu_ffn_forward(x, w_gate, w_up, w_down, activation, want_preact):
 def _glu_ffn_backward(go, x, act, pre, w_gate, w_up, w_down, activation):
     Hs, D = w_gate.shape
     d_act = ops.grouped_gemm(go, w_down, _lib.B_NMAJOR, 1, None, D, Hs)
-    gU = ops.glu_backward(d_act, pre, None, 1, activation)
-    w_cat = torch.cat([w_gate, w_up], dim=0)
-    dx = ops.grouped_gemm(gU, w_cat, _lib.B_NMAJOR, 1, None, 2 * Hs, D)
     ts = _dense_ts(x.shape[0], x.device)
-    d_wcat = ops.grouped_gemm_wgrad(gU, x, 1, ts)[0]
     # [D, Hs] has few output tiles (32 CTA-pair tiles at D = 1024, Hs = 2048 for 74 pairs): split the token
     # dimension in two halves, each accumulated in fp32, and add the two bf16 results
     tiles = (x.shape[0] + 127) // 128
-    if tiles >= 64 and (D // 256) * ((Hs + 255) // 256) <= 40:
-        d_wdown = ops.grouped_gemm_wgrad(go, act, 2, _dense_ts(x.shape[0], x.device, split=2)).sum(dim=0)
+    split = 2 if tiles >= 64 and (D // 256) * ((Hs + 255) // 256) <= 40 else 1
+    ts_down = _dense_ts(x.shape[0], x.device, split=2) if split == 2 else ts
+    if _OVERLAP:
+        # the GLU backward rides on extra warps of the dW_down GEMM, which does not depend on it
+        d_wdown, gU = ops.grouped_gemm_wgrad_glu_backward(go, act, split, ts_down, d_act, pre, activation)
     else:
-        d_wdown = ops.grouped_gemm_wgrad(go, act, 1, ts)[0]
+        gU = ops.glu_backward(d_act, pre, None, 1, activation)
+        d_wdown = ops.grouped_gemm_wgrad(go, act, split, ts_down)
+    d_wdown = d_wdown.sum(dim=0) if split == 2 else d_wdown[0]
+    w_cat = torch.cat([w_gate, w_up], dim=0)
+    dx = ops.grouped_gemm(gU, w_cat, _lib.B_NMAJOR, 1, None, 2 * Hs, D)
+    d_wcat = ops.grouped_gemm_wgrad(gU, x, 1, ts)[0]
     return dx, d_wcat[:Hs], d_wcat[Hs:], d_wdown
 
 
@@ -353,9 +357,9 @@ class _FusedMoEFunction(torch.autograd.Function):
         if _OVERLAP:
             # Two GEMMs never share an SM, so the GEMMs stay in one chain and each HBM-bound kernel is paired with
             # a GEMM that does not depend on it:
-            #   main:  dAct GEMM -> GLU backward ............ -> dX GEMM -> un-permute (+ routing term)
-            #   gemm:  (after dAct)  dW_down GEMM              (after dX)   dW_up GEMM
-            #   route: routing backward (beside the dAct GEMM)
+            #   main:  dAct GEMM -> dW_down GEMM with the GLU backward as passenger -> dX GEMM -> un-permute (+ routing term)
+            #   gemm:  (after dX) dW_up GEMM
+            #   route: routing backward (fills the gaps between GEMMs)
             main = torch.cuda.current_stream()
             gemm = _get_side_stream("backward_gemm")
             route = _get_side_stream("backward_route")
@@ -368,12 +372,8 @@ class _FusedMoEFunction(torch.autograd.Function):
                 route_done = torch.cuda.Event()
                 route_done.record(route)
             d_act = ops.grouped_gemm(gYw, wd, _lib.B_NMAJOR, E, tile_start, D, H)
-            dact_done = torch.cuda.Event()
-            dact_done.record(main)
-            with torch.cuda.stream(gemm):
-                gemm.wait_event(dact_done)
-                d_wd = ops.grouped_gemm_wgrad(gYw, act, E, tile_start)
-            gU = ops.glu_backward(d_act, pre, tile_start, E, cfg.activation)
+            # the GLU backward rides on extra warps of the dW_down GEMM (one launch)
+            d_wd, gU = ops.grouped_gemm_wgrad_glu_backward(gYw, act, E, tile_start, d_act, pre, cfg.activation)
             dXg = ops.grouped_gemm(gU, wu, _lib.B_NMAJOR, E, tile_start, 2 * H, D)
             dx_done = torch.cuda.Event()
             dx_done.record(main)
@@ -385,7 +385,7 @@ class _FusedMoEFunction(torch.autograd.Function):
             main.wait_event(route_done)
             dH = ops.combine_forward(dXg, pos, None, N, k, addend=dH_route)
             main.wait_event(join)
-            for t_side in (dH_route, d_gate, d_wd, d_wu):
+            for t_side in (dH_route, d_gate, d_wu):
                 t_side.record_stream(main)  # allocated on a side stream, consumed on the main one from here on
         else:
             d_act = ops.grouped_gemm(gYw, wd, _lib.B_NMAJOR, E, tile_start, D, H)
@@ -576,15 +576,21 @@ def _split_tile_start(tile_start, S):
     return torch.cat([cuts, ts[-1:]]).to(torch.int32)
 
 
-def _grouped_wgrad(A, B, groups, tile_start, scale=1.0, split_ts=None):
+def _grouped_wgrad(A, B, groups, tile_start, scale=1.0, passenger=None):
     """ops.grouped_gemm_wgrad, split along K into partial products (summed afterwards) when the output is too small
-    to occupy every SM. split_ts: precomputed (S, tile_start of the split groups), else built with a few torch ops."""
+    to occupy every SM. passenger = (d_act, preact, activation): the GLU backward rides in the same launch and the
+    result is (dW, gU)."""
     S = _wgrad_split_factor(groups, A.shape[1], B.shape[1])
-    if S == 1:
-        return ops.grouped_gemm_wgrad(A, B, groups, tile_start, scale=scale)
-    ts = split_ts[1] if split_ts is not None and split_ts[0] == S else _split_tile_start(tile_start, S)
-    part = ops.grouped_gemm_wgrad(A, B, groups * S, ts, scale=scale)
-    return part.view(groups, S, A.shape[1], B.shape[1]).sum(dim=1, dtype=torch.float32).to(part.dtype)
+    ts = tile_start if S == 1 else _split_tile_start(tile_start, S)
+    gU = None
+    if passenger is not None:
+        part, gU = ops.grouped_gemm_wgrad_glu_backward(A, B, groups * S, ts, passenger[0], passenger[1], passenger[2],
+                                                       scale=scale)
+    else:
+        part = ops.grouped_gemm_wgrad(A, B, groups * S, ts, scale=scale)
+    if S > 1:
+        part = part.view(groups, S, A.shape[1], B.shape[1]).sum(dim=1, dtype=torch.float32).to(part.dtype)
+    return part if passenger is None else (part, gU)
 
 
 def _small_m_kwargs(enabled, counts):
@@ -802,20 +808,10 @@ class _FusedMoEEPFunction(torch.autograd.Function):
         if M > 0:
             gYg = recv_grad if direct else ops.permute_rows(recv_grad, t["src_l"], rows_l, 1)
             if _OVERLAP:
-                # the down-projection weight gradient does not need the GLU backward: it runs beside it
-                main = torch.cuda.current_stream()
-                gemm = _get_side_stream("backward_gemm")
+                # the down-projection weight gradient does not need the GLU backward: it carries it as a passenger
                 d_act = ops.grouped_gemm(gYg, wd, _lib.B_NMAJOR, El, t["ts_l"], D, H)
-                dact_done = torch.cuda.Event()
-                dact_done.record(main)
-                with torch.cuda.stream(gemm):
-                    gemm.wait_event(dact_done)
-                    d_wd = _grouped_wgrad(gYg, t["act"], El, t["ts_l"], scale=inv_ep)
-                    join = torch.cuda.Event()
-                    join.record(gemm)
-                gU = ops.glu_backward(d_act, t["pre"], t["ts_l"], El, cfg.activation)
-                main.wait_event(join)
-                d_wd.record_stream(main)
+                d_wd, gU = _grouped_wgrad(gYg, t["act"], El, t["ts_l"], scale=inv_ep,
+                                          passenger=(d_act, t["pre"], cfg.activation))
             else:
                 d_act = ops.grouped_gemm(gYg, wd, _lib.B_NMAJOR, El, t["ts_l"], D, H)
                 gU = ops.glu_backward(d_act, t["pre"], t["ts_l"], El, cfg.activation)

@@ -280,6 +280,29 @@ def grouped_gemm_wgrad(A, B, groups, tile_start, scale=1.0):
     return out
 
 
+def grouped_gemm_wgrad_glu_backward(A, B, groups, tile_start, d_act, preact, activation, scale=1.0):
+    """(dW, gU): grouped_gemm_wgrad(A, B) and glu_backward(d_act, preact) in one launch, the second riding on extra
+    warps of the GEMM's CTAs (ffm_grouped_gemm_wgrad_glu_backward). Bit-identical to the two separate calls on the
+    rows in use (the passenger also converts the unused rows past the last group, which nobody reads)."""
+    lib = _lib.load()
+    _req(A, torch.bfloat16, "A")
+    _req(B, torch.bfloat16, "B")
+    _req(d_act, torch.bfloat16, "d_act")
+    _req(preact, torch.bfloat16, "preact")
+    rows_cap, M = A.shape
+    n_out = B.shape[1]
+    rows, H = d_act.shape
+    out = torch.empty(groups, M, n_out, dtype=torch.bfloat16, device=A.device)
+    gU = torch.empty(rows, 2 * H, dtype=torch.bfloat16, device=A.device)
+    with _Launch("gemm_wgrad", 1):
+        rc = lib.ffm_grouped_gemm_wgrad_glu_backward(_ptr(A), _ptr(B), groups, _ptr(tile_start), rows_cap, M, n_out,
+                                                     float(scale), _ptr(out), _ptr(d_act), _ptr(preact), rows, H,
+                                                     _lib.ACTIVATION[activation], _ptr(gU),
+                                                     _ptr(status_tensor(A.device)), _stream())
+    _lib.check(rc, "ffm_grouped_gemm_wgrad_glu_backward")
+    return out, gU
+
+
 def combine_forward(Y, pos, w, N, top_k, addend=None):
     lib = _lib.load()
     _req(Y, torch.bfloat16, "Y")

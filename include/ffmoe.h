@@ -194,6 +194,15 @@ int ffm_grouped_gemm(const void* A, const void* B, int b_major, int groups, cons
                      int tile_rows, int32_t* status, ffm_stream_t stream);
 int ffm_grouped_gemm_wgrad(const void* A, const void* B, int groups, const int32_t* tile_start, int64_t rows_cap,
                            int M, int Nout, float scale, void* dW, int32_t* status, ffm_stream_t stream);
+/* ffm_grouped_gemm_wgrad with a passenger: the same launch also computes gU = GLU backward of (dAct [glu_rows, H],
+ * preact [glu_rows, 2H]) exactly as ffm_glu_backward does, on eight extra warps per CTA that stream through HBM while
+ * the tensor pipe works on the weight gradient. The two jobs are independent (in the layer: dW_down needs the output
+ * gradient and the activations, the GLU backward needs dAct); a GEMM CTA leaves no room on its SM for another
+ * kernel's blocks, so this is how the HBM-bound job overlaps a GEMM. Results are bit-identical to the two calls. */
+int ffm_grouped_gemm_wgrad_glu_backward(const void* A, const void* B, int groups, const int32_t* tile_start,
+                                        int64_t rows_cap, int M, int Nout, float scale, void* dW, const void* dAct,
+                                        const void* preact, int64_t glu_rows, int H, int activation, void* gU,
+                                        int32_t* status, ffm_stream_t stream);
 
 /* -------------------------------------------------------------------------------------------------
  * Combine forward: out[n, :] = sum_j w[n, j] * Y[pos[n k + j], :] (+ addend[n, :]), fp32 accumulation.

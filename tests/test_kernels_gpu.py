@@ -457,3 +457,24 @@ def test_push_rows_gathers_scatters_and_zeroes_locally():
     torch.cuda.synchronize()
     ref1[60:64] = 0
     assert torch.equal(dst1, ref1) and torch.equal(dst0, ref0)
+
+
+@pytest.mark.parametrize("activation", ["swiglu", "relu_squared"])
+@pytest.mark.parametrize("counts,M,Nout,H", [([5, 0, 200, 128], 64, 64, 64), ([300, 17, 129, 64], 192, 320, 96),
+                                             ([2048] * 8, 1024, 2048, 2048)])
+def test_wgrad_with_glu_backward_passenger(counts, M, Nout, H, activation):
+    """The weight-gradient GEMM that carries the GLU backward on extra warps equals the two separate kernels bit for
+    bit, for both jobs (the passenger's rows are independent of the GEMM's groups)."""
+    torch.manual_seed(M + H)
+    A, ts, row_expert, rows_cap = _grouped_case(counts, M)
+    E = len(counts)
+    Bx = torch.randn(rows_cap, Nout, device=DEV).bfloat16()
+    Bx[row_expert == -1] = 0
+    d_act = torch.randn(rows_cap + 37, H, device=DEV).bfloat16()       # the passenger has its own row count
+    pre = torch.randn(rows_cap + 37, 2 * H, device=DEV).bfloat16()
+    dW_ref = ops.grouped_gemm_wgrad(A, Bx, E, ts, scale=0.5)
+    gU_ref = ops.glu_backward(d_act, pre, None, 1, activation)
+    dW, gU = ops.grouped_gemm_wgrad_glu_backward(A, Bx, E, ts, d_act, pre, activation, scale=0.5)
+    ops.check_status()
+    assert torch.equal(dW, dW_ref)
+    assert torch.equal(gU, gU_ref)
