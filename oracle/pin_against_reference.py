@@ -1,7 +1,7 @@
 """Pins oracle/moe_oracle.py against the unmodified reference and writes the golden vectors.
 
-Runs only where the reference checkout is available (argument or FFM_REFERENCE_DIR, default
-/root/reference); it is never imported by tests, bench.py or the package. The reference's Triton kernels run
+Runs only where the reference checkout is available (its directory is the first argument, or the environment
+variable FFM_REFERENCE_DIR); it is never imported by tests, bench.py or the package. The reference's Triton kernels run
 through Triton's CPU interpreter; its autotuner is told to run each candidate once.
 
     python oracle/pin_against_reference.py [reference_dir]
@@ -20,7 +20,9 @@ os.environ["TRITON_INTERPRET"] = "1"
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
-REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("FFM_REFERENCE_DIR", "/root/reference")
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("FFM_REFERENCE_DIR")
+if not REF or not os.path.isdir(os.path.join(REF, "src")):
+    raise SystemExit("usage: python oracle/pin_against_reference.py <reference checkout>  (or set FFM_REFERENCE_DIR)")
 sys.path.insert(0, os.path.join(REF, "src"))
 sys.path.insert(0, ROOT)
 
