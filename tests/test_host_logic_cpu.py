@@ -216,3 +216,22 @@ def test_segment_plan_moves_every_row_to_the_grouped_layout_and_back():
                 for j in range(rows):
                     back[s][dst0 + j] = grouped[d][src0 + j]
         assert back == send
+
+
+def test_weight_gradient_split_helpers():
+    """Host helpers of the split-K weight gradient: split factor and the tile ranges of the split groups."""
+    import sys
+    import torch
+    import flashfusedmoe_b200  # noqa: F401
+    fm = sys.modules["flashfusedmoe_b200.fused_moe"]
+    # one expert per rank at D = 1024, H = 2048: dW_down [1024, 2048] has 32 tile pairs -> split in two; dW_up has 64
+    assert fm._wgrad_split_factor(1, 1024, 2048) == 2
+    assert fm._wgrad_split_factor(1, 4096, 1024) == 1
+    assert fm._wgrad_split_factor(8, 1024, 2048) == 1
+    assert fm._wgrad_split_factor(4, 256, 256) == 4
+    ts = torch.tensor([0, 6, 6, 20, 22], dtype=torch.int32)
+    for S in (2, 3, 4):
+        cut = fm._split_tile_start(ts, S)
+        assert cut.dtype == torch.int32 and cut.numel() == 4 * S + 1
+        assert (cut[1:] >= cut[:-1]).all() and (cut % 2 == 0).all()          # whole tile pairs, in order
+        assert cut[::S].tolist() == ts.tolist()                               # group boundaries are kept
