@@ -46,9 +46,6 @@ SIGNATURES = {
                                  c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
     "ffm_grouped_gemm_wgrad": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int, c_int, c_float,
                                        c_void_p, c_void_p, c_void_p]),
-    "ffm_grouped_gemm_wgrad_combine": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int, c_int, c_float,
-                                               c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int,
-                                               c_void_p, c_void_p, c_void_p]),
     "ffm_grouped_gemm_wgrad_glu_backward": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int, c_int, c_float,
                                                     c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p,
                                                     c_void_p, c_void_p]),

@@ -11,6 +11,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libffmoe.so")
+PTXAS_LOG = os.path.join(HERE, "libffmoe.ptxas.txt")
 SOURCES = ["ffm_api.cu", "ffm_route.cu", "ffm_rows.cu", "ffm_route_bwd.cu", "ffm_gemm_sm100.cu", "ffm_p2p.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -36,12 +37,18 @@ def build(force=False, verbose=False):
         objs.append(obj)
         cmd = [nvcc] + NVCC_FLAGS + ["-c", os.path.join(CSRC, src), "-o", obj]
         procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
+    log = []
     for src, p in procs:
         out, _ = p.communicate()
+        log.append(out)
         if verbose or p.returncode != 0:
             sys.stderr.write(out)
         if p.returncode != 0:
             raise RuntimeError(f"nvcc failed on {src}")
+    # ptxas -v output (registers, spills, shared memory per kernel), kept beside the library: the GLU-epilogue GEMM
+    # is sensitive to register allocation (tests/test_cabi_cpu.py checks it)
+    with open(PTXAS_LOG, "w") as f:
+        f.write("".join(log))
     cmd = [nvcc, "-shared", "-o", LIB] + objs + ["-lcudart"]
     subprocess.check_call(cmd)
     return LIB

@@ -139,23 +139,6 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
   return true;
 }
 
-// acc[0..7] += the eight bf16 values of v times w; pack8 rounds eight floats back to bf16
-__device__ __forceinline__ void fma8(float (&acc)[8], const uint4& v, float w) {
-  const float2 a = unpack_bf16x2(v.x), b = unpack_bf16x2(v.y), c = unpack_bf16x2(v.z), d = unpack_bf16x2(v.w);
-  acc[0] = fmaf(a.x, w, acc[0]);
-  acc[1] = fmaf(a.y, w, acc[1]);
-  acc[2] = fmaf(b.x, w, acc[2]);
-  acc[3] = fmaf(b.y, w, acc[3]);
-  acc[4] = fmaf(c.x, w, acc[4]);
-  acc[5] = fmaf(c.y, w, acc[5]);
-  acc[6] = fmaf(d.x, w, acc[6]);
-  acc[7] = fmaf(d.y, w, acc[7]);
-}
-
-__device__ __forceinline__ uint4 pack8(const float (&a)[8]) {
-  return make_uint4(pack_bf16x2(a[0], a[1]), pack_bf16x2(a[2], a[3]), pack_bf16x2(a[4], a[5]), pack_bf16x2(a[6], a[7]));
-}
-
 }  // namespace ffm
 
 // Ask for the largest shared-memory carve-out for a kernel that itself needs little or none. The persistent GEMM

@@ -112,18 +112,13 @@ struct GemmParams {
   int n_tiles;            // number of BN (GLU: 128-column) blocks over n_cols
   int32_t* status;
   long long wait_cycles;
-  // passenger job (PASS = 1), pz_kind 1: gU = GLU backward of (dAct, pre-activations), see ffm_glu_backward;
-  // pz_kind 2: out[n] = sum_j w[n, j] * Y[pos[n k + j]] (+ addend[n]), see ffm_combine_forward (Y in pz_dact,
-  // addend in pz_pre, out in pz_gu, N in pz_rows, D in pz_h, top_k in pz_act)
-  int pz_kind;
+  // passenger job (PASS = 1): gU = GLU backward of (dAct, pre-activations), see ffm_glu_backward
   const bf16* pz_dact;
   const bf16* pz_pre;
   bf16* pz_gu;
   long long pz_rows;
   int pz_h;
   int pz_act;
-  const int32_t* pz_pos;
-  const float* pz_w;
 };
 
 struct Ctrl {
@@ -328,43 +323,6 @@ __device__ __forceinline__ void passenger_glu_backward(const GemmParams& p, long
         reinterpret_cast<uint4*>(p.pz_gu + r[u] * 2 * H)[c[u]] = make_uint4(dg[0], dg[1], dg[2], dg[3]);
         reinterpret_cast<uint4*>(p.pz_gu + r[u] * 2 * H + H)[c[u]] = make_uint4(du[0], du[1], du[2], du[3]);
       }
-    }
-  }
-}
-
-// Weighted gather-reduce of k rows per token (the combine / un-permute step), one warp per (token, 256-column block).
-__device__ __forceinline__ void passenger_combine_forward(const GemmParams& p, long long warp_id, long long nwarps,
-                                                          int lane) {
-  const int D = p.pz_h, top_k = p.pz_act;
-  const int chunks = D >> 3;
-  const int cblocks = (chunks + 31) >> 5;
-  const long long items = p.pz_rows * cblocks;
-  for (long long item = warp_id; item < items; item += nwarps) {
-    const long long n = item / cblocks;
-    const int c = (static_cast<int>(item % cblocks) << 5) + lane;
-    int my_pos = 0;
-    float my_w = 0.0f;
-    if (lane < top_k) {
-      my_pos = p.pz_pos[n * top_k + lane];
-      my_w = (p.pz_w != nullptr) ? bf16_round(p.pz_w[n * top_k + lane]) : 1.0f;
-    }
-    const bool active = c < chunks;
-    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    for (int j = 0; j < top_k; ++j) {
-      const int pj = __shfl_sync(0xffffffffu, my_pos, j);
-      const float wj = __shfl_sync(0xffffffffu, my_w, j);
-      if (active) fma8(acc, __ldg(reinterpret_cast<const uint4*>(p.pz_dact + static_cast<long long>(pj) * D) + c), wj);
-    }
-    if (!active) continue;
-    if (p.pz_pre != nullptr) {
-      const uint4 r = pack8(acc);
-      const uint4 a = __ldg(reinterpret_cast<const uint4*>(p.pz_pre + n * D) + c);
-      float sum[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-      fma8(sum, r, 1.0f);
-      fma8(sum, a, 1.0f);
-      reinterpret_cast<uint4*>(p.pz_gu + n * D)[c] = pack8(sum);
-    } else {
-      reinterpret_cast<uint4*>(p.pz_gu + n * D)[c] = pack8(acc);
     }
   }
 }
@@ -582,13 +540,8 @@ ffm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     }
   } else if (PASS && warp >= 2 + EPI_WARPS) {
     // ================= passenger (warps 6..13) =================
-    if (p.pz_kind == 2) {
-      passenger_combine_forward(p, static_cast<long long>(blockIdx.x) * (PASSENGER_THREADS / 32) + (warp - 2 - EPI_WARPS),
-                                static_cast<long long>(gridDim.x) * (PASSENGER_THREADS / 32), lane);
-    } else {
-      passenger_glu_backward(p, static_cast<long long>(blockIdx.x) * PASSENGER_THREADS + (threadIdx.x - GEMM_THREADS),
-                             static_cast<long long>(gridDim.x) * PASSENGER_THREADS);
-    }
+    passenger_glu_backward(p, static_cast<long long>(blockIdx.x) * PASSENGER_THREADS + (threadIdx.x - GEMM_THREADS),
+                           static_cast<long long>(gridDim.x) * PASSENGER_THREADS);
   } else {
     // ================= epilogue (warps 2..5) =================
     const int quarter = warp & 3;  // TMEM lanes [32 * quarter, 32 * quarter + 32) belong to this warp
@@ -1048,50 +1001,12 @@ extern "C" int ffm_grouped_gemm_wgrad_glu_backward(const void* A, const void* B,
   p.n_tiles = (Nout + BN - 1) / BN;
   p.status = status;
   p.wait_cycles = g_wait_cycles;
-  p.pz_kind = 1;
   p.pz_dact = static_cast<const bf16*>(dAct);
   p.pz_pre = static_cast<const bf16*>(preact);
   p.pz_gu = static_cast<bf16*>(gU);
   p.pz_rows = glu_rows;
   p.pz_h = H;
   p.pz_act = activation;
-  return launch_gemm<1, 1, EPI_PLAIN, 1, 1>(tmA, tmB, tmB, tmC, tmC, p, p.m_tiles_per_group,
-                                         static_cast<long long>(groups) * p.n_tiles,
-                                         static_cast<cudaStream_t>(stream));
-}
-
-extern "C" int ffm_grouped_gemm_wgrad_combine(const void* A, const void* B, int groups, const int32_t* tile_start,
-                                              int64_t rows_cap, int M, int Nout, float scale, void* dW, const void* Y,
-                                              const int32_t* pos, const float* w, const void* addend, int64_t N,
-                                              int top_k, int D, void* out, int32_t* status, ffm_stream_t stream) {
-  if (!Y || !pos || !out || N < 0 || top_k < 1 || D <= 0) return FFM_ERR_BAD_ARG;
-  if (D % 8 != 0 || top_k > 32) return FFM_ERR_UNSUPPORTED;
-  if (!A || !B || !dW || !status || !tile_start) return FFM_ERR_BAD_ARG;
-  if (groups < 1 || groups > MAX_GROUPS || rows_cap <= 0 || M <= 0 || Nout <= 0) return FFM_ERR_BAD_ARG;
-  if (M % 64 != 0 || Nout % 64 != 0) return FFM_ERR_UNSUPPORTED;
-  CUtensorMap tmA, tmB, tmC;
-  int rc;
-  if ((rc = make_map_2d(&tmA, A, rows_cap, M, 64, 64)) != FFM_OK) return rc;
-  if ((rc = make_map_2d(&tmB, B, rows_cap, Nout, 64, 64)) != FFM_OK) return rc;
-  if ((rc = make_out_map(&tmC, dW, groups, M, Nout)) != FFM_OK) return rc;
-  GemmParams p = {};
-  p.tile_start = tile_start;
-  p.groups = groups;
-  p.n_cols = Nout;
-  p.scale = scale;
-  p.m_tiles_per_group = (M + BM - 1) / BM;
-  p.n_tiles = (Nout + BN - 1) / BN;
-  p.status = status;
-  p.wait_cycles = g_wait_cycles;
-  p.pz_kind = 2;
-  p.pz_dact = static_cast<const bf16*>(Y);
-  p.pz_pre = static_cast<const bf16*>(addend);
-  p.pz_gu = static_cast<bf16*>(out);
-  p.pz_rows = N;
-  p.pz_h = D;
-  p.pz_act = top_k;
-  p.pz_pos = pos;
-  p.pz_w = w;
   return launch_gemm<1, 1, EPI_PLAIN, 1, 1>(tmA, tmB, tmB, tmC, tmC, p, p.m_tiles_per_group,
                                          static_cast<long long>(groups) * p.n_tiles,
                                          static_cast<cudaStream_t>(stream));

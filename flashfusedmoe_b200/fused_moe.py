@@ -51,7 +51,6 @@ _EP_DRY_EXCHANGE = False
 # (they fill the gaps and tails between GEMMs), the GLU backward as a passenger inside the dW_down GEMM's CTAs.
 # FFM_OVERLAP=0 keeps one stream and separate kernels.
 _OVERLAP = os.environ.get("FFM_OVERLAP", "1") != "0"
-_PASSENGER_COMBINE = os.environ.get("FFM_PASSENGER_COMBINE", "1") != "0"
 # Peer-store transport only: move rows straight into the receivers' grouped layout (FFM_EP_DIRECT=0 keeps the
 # contiguous-range exchange with a permute on either side, the layout the NCCL transport also uses).
 _EP_DIRECT = os.environ.get("FFM_EP_DIRECT", "1") != "0"
@@ -358,10 +357,11 @@ class _FusedMoEFunction(torch.autograd.Function):
         if _OVERLAP:
             # Two GEMMs never share an SM, so the GEMMs stay in one chain and each HBM-bound kernel is paired with
             # a GEMM that does not depend on it:
-            #   main:  dAct GEMM -> dW_down GEMM carrying the GLU backward -> dX GEMM -> dW_up GEMM carrying the
-            #          un-permute (+ routing term)
+            #   main:  dAct GEMM -> dW_down GEMM with the GLU backward as passenger -> dX GEMM -> un-permute (+ routing term)
+            #   gemm:  (after dX) dW_up GEMM
             #   route: routing backward (fills the gaps between GEMMs)
             main = torch.cuda.current_stream()
+            gemm = _get_side_stream("backward_gemm")
             route = _get_side_stream("backward_route")
             fork = torch.cuda.Event()
             fork.record(main)
@@ -375,14 +375,17 @@ class _FusedMoEFunction(torch.autograd.Function):
             # the GLU backward rides on extra warps of the dW_down GEMM (one launch)
             d_wd, gU = ops.grouped_gemm_wgrad_glu_backward(gYw, act, E, tile_start, d_act, pre, cfg.activation)
             dXg = ops.grouped_gemm(gU, wu, _lib.B_NMAJOR, E, tile_start, 2 * H, D)
-            main.wait_event(route_done)
-            if _PASSENGER_COMBINE:
-                # the un-permute (plus the routing term as its addend) rides on extra warps of the dW_up GEMM
-                d_wu, dH = ops.grouped_gemm_wgrad_combine(gU, Xg, E, tile_start, dXg, pos, None, N, k, addend=dH_route)
-            else:
-                dH = ops.combine_forward(dXg, pos, None, N, k, addend=dH_route)
+            dx_done = torch.cuda.Event()
+            dx_done.record(main)
+            with torch.cuda.stream(gemm):
+                gemm.wait_event(dx_done)
                 d_wu = ops.grouped_gemm_wgrad(gU, Xg, E, tile_start)
-            for t_side in (dH_route, d_gate):
+                join = torch.cuda.Event()
+                join.record(gemm)
+            main.wait_event(route_done)
+            dH = ops.combine_forward(dXg, pos, None, N, k, addend=dH_route)
+            main.wait_event(join)
+            for t_side in (dH_route, d_gate, d_wu):
                 t_side.record_stream(main)  # allocated on a side stream, consumed on the main one from here on
         else:
             d_act = ops.grouped_gemm(gYw, wd, _lib.B_NMAJOR, E, tile_start, D, H)

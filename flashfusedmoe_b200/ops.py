@@ -303,26 +303,6 @@ def grouped_gemm_wgrad_glu_backward(A, B, groups, tile_start, d_act, preact, act
     return out, gU
 
 
-def grouped_gemm_wgrad_combine(A, B, groups, tile_start, Y, pos, w, N, top_k, addend=None, scale=1.0):
-    """(dW, out): grouped_gemm_wgrad(A, B) and combine_forward(Y, pos, w, N, top_k, addend) in one launch, the second
-    riding on extra warps of the GEMM's CTAs (ffm_grouped_gemm_wgrad_combine). Bit-identical to the two calls."""
-    lib = _lib.load()
-    _req(A, torch.bfloat16, "A")
-    _req(B, torch.bfloat16, "B")
-    _req(Y, torch.bfloat16, "Y")
-    rows_cap, M = A.shape
-    n_out = B.shape[1]
-    D = Y.shape[1]
-    dW = torch.empty(groups, M, n_out, dtype=torch.bfloat16, device=A.device)
-    out = torch.empty(N, D, dtype=torch.bfloat16, device=A.device)
-    with _Launch("gemm_wgrad", 1):
-        rc = lib.ffm_grouped_gemm_wgrad_combine(_ptr(A), _ptr(B), groups, _ptr(tile_start), rows_cap, M, n_out,
-                                                float(scale), _ptr(dW), _ptr(Y), _ptr(pos), _ptr(w), _ptr(addend), N,
-                                                top_k, D, _ptr(out), _ptr(status_tensor(A.device)), _stream())
-    _lib.check(rc, "ffm_grouped_gemm_wgrad_combine")
-    return dW, out
-
-
 def combine_forward(Y, pos, w, N, top_k, addend=None):
     lib = _lib.load()
     _req(Y, torch.bfloat16, "Y")

@@ -203,13 +203,6 @@ int ffm_grouped_gemm_wgrad_glu_backward(const void* A, const void* B, int groups
                                         int64_t rows_cap, int M, int Nout, float scale, void* dW, const void* dAct,
                                         const void* preact, int64_t glu_rows, int H, int activation, void* gU,
                                         int32_t* status, ffm_stream_t stream);
-/* The same with ffm_combine_forward (Y, pos, w, addend, N, top_k, D -> out) as the passenger: in the layer the
- * un-permute of the expert input gradient rides inside the dW_up GEMM. Bit-identical to the two calls. */
-int ffm_grouped_gemm_wgrad_combine(const void* A, const void* B, int groups, const int32_t* tile_start,
-                                   int64_t rows_cap, int M, int Nout, float scale, void* dW, const void* Y,
-                                   const int32_t* pos, const float* w, const void* addend, int64_t N, int top_k, int D,
-                                   void* out, int32_t* status, ffm_stream_t stream);
-
 /* -------------------------------------------------------------------------------------------------
  * Combine forward: out[n, :] = sum_j w[n, j] * Y[pos[n k + j], :] (+ addend[n, :]), fp32 accumulation.
  * w (f32) is rounded to bf16 before the multiply, as the reference does (fused_moe.py:412); w == NULL

@@ -65,3 +65,20 @@ def test_product_path_has_no_cpu_fallback():
     wd = torch.randn(4, 64, 64).bfloat16()
     with pytest.raises(RuntimeError, match="no CPU path"):
         fused_moe(h, g, wu, wd, top_k=2)
+
+
+def test_gemm_register_allocation_canary():
+    """ptxas figures of the build: no GEMM instantiation spills, and the GLU-epilogue GEMM keeps its wide register
+    allocation. (Growing the kernel's parameter struct by three fields once made ptxas pick 185 instead of 234
+    registers for it, with no spills reported and a 30 % slower kernel: two 32-column chunks of gate and up no longer
+    stayed in flight.)"""
+    import re
+    from flashfusedmoe_b200 import build
+    build.build(force=not os.path.exists(build.PTXAS_LOG))
+    text = open(build.PTXAS_LOG).read()
+    blocks = re.findall(r"Compiling entry function '(\S*ffm_gemm_kernel\S*)'.*?Used (\d+) registers", text, flags=re.S)
+    assert len(blocks) >= 10, "ptxas output of the GEMM instantiations not found"
+    spills = re.findall(r"ffm_gemm_kernel\S*\n\s*(\d+) bytes stack frame, (\d+) bytes spill stores, (\d+) bytes spill loads", text)
+    assert spills and all(int(a) == 0 and int(b) == 0 for _, a, b in spills), "a GEMM instantiation spills registers"
+    glu = [int(r) for name, r in blocks if "ILi0ELi0ELi1ELi0E" in name]   # <A K-major, B K-major, EPI_GLU, grouped-M>
+    assert glu and min(glu) >= 200, f"GLU-epilogue GEMM register allocation changed: {glu}"

@@ -478,25 +478,3 @@ def test_wgrad_with_glu_backward_passenger(counts, M, Nout, H, activation):
     ops.check_status()
     assert torch.equal(dW, dW_ref)
     assert torch.equal(gU, gU_ref)
-
-
-@pytest.mark.parametrize("N,D,E,k,with_addend", [(300, 128, 8, 2, True), (128, 72, 16, 5, False), (16384, 1024, 8, 2, True)])
-def test_wgrad_with_combine_passenger(N, D, E, k, with_addend):
-    """The weight-gradient GEMM that carries the combine / un-permute on extra warps equals the two kernels bit for bit."""
-    torch.manual_seed(N + D)
-    hidden = torch.randn(N, D, device=DEV).bfloat16()
-    gate = (torch.randn(E, D, device=DEV) * 0.3).bfloat16()
-    r = ops.route_forward(hidden, gate, k, "softmax")
-    Y = torch.randn(r.rows_cap, D, device=DEV).bfloat16()
-    add = torch.randn(N, D, device=DEV).bfloat16() if with_addend else None
-    A = torch.randn(r.rows_cap, 64, device=DEV).bfloat16()
-    Bx = torch.randn(r.rows_cap, 128, device=DEV).bfloat16()
-    A[r.src.long()[: r.rows_cap] < 0] = 0
-    dW_ref = ops.grouped_gemm_wgrad(A, Bx, E, r.tile_start)
-    out_ref = ops.combine_forward(Y, r.pos, None, N, k, addend=add)
-    out_w_ref = ops.combine_forward(Y, r.pos, r.topk_w, N, k, addend=add)
-    dW, out = ops.grouped_gemm_wgrad_combine(A, Bx, E, r.tile_start, Y, r.pos, None, N, k, addend=add)
-    dW2, out_w = ops.grouped_gemm_wgrad_combine(A, Bx, E, r.tile_start, Y, r.pos, r.topk_w, N, k, addend=add)
-    ops.check_status()
-    assert torch.equal(dW, dW_ref) and torch.equal(dW2, dW_ref)
-    assert torch.equal(out, out_ref) and torch.equal(out_w, out_w_ref)
