@@ -235,3 +235,23 @@ def test_weight_gradient_split_helpers():
         assert cut.dtype == torch.int32 and cut.numel() == 4 * S + 1
         assert (cut[1:] >= cut[:-1]).all() and (cut % 2 == 0).all()          # whole tile pairs, in order
         assert cut[::S].tolist() == ts.tolist()                               # group boundaries are kept
+
+
+def test_small_helpers_without_a_gpu():
+    import sys
+    import torch
+    import flashfusedmoe_b200  # noqa: F401
+    fm = sys.modules["flashfusedmoe_b200.fused_moe"]
+    # run_beside: CPU tensors (or overlap switched off) call the function in place and return no event
+    out, ev = fm.run_beside(lambda t: t * 2, torch.ones(3))
+    assert ev is None and out.tolist() == [2.0, 2.0, 2.0]
+    # inference shortcut arguments of the grouped GEMMs
+    assert fm._small_m_kwargs(False, None) == {}
+    kw = fm._small_m_kwargs(True, torch.tensor([3, 0, 7], dtype=torch.int64))
+    assert kw["tile_rows"] == 128 and kw["valid_rows"].dtype == torch.int32 and kw["valid_rows"].tolist() == [3, 0, 7]
+    # the static expert-parallel forward is off unless declared
+    assert fm._EP_STATIC_TOKENS is None
+    fm.set_ep_static_forward(128)
+    assert fm._EP_STATIC_TOKENS == 128
+    fm.set_ep_static_forward(None)
+    assert fm._EP_STATIC_TOKENS is None
