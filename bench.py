@@ -246,6 +246,182 @@ def oracle_sample_tokens_per_s(sample_tokens, threads, repeats=1):
     return sample_tokens / best, best
 
 
+
+def _rel(a, b):
+    a, b = a.detach().float(), b.detach().float()
+    return ((a - b).abs().max() / (b.abs().max() + 1e-12)).item()
+
+
+def routing_only_input_grad(x, go, gate, w_up, w_down, shared, idx):
+    """fp32 autograd restatement (on the GPU) of the input gradient the expert-parallel backward returns: the
+    routing-weight path and the shared expert, with the experts' own input treated as a constant (the reference's
+    contract, src/flashfusemoe/fused_moe.py:1001-1005). `idx` [n, k] are the kernel's expert assignments."""
+    F = torch.nn.functional
+    n, D = x.shape
+    E = gate.shape[0]
+    H = w_up.shape[1] // 2
+    xf = x.float().requires_grad_()
+    w = torch.softmax((xf @ gate.float().T).gather(1, idx.long()), dim=-1)
+    xd = x.float()
+    routed = torch.zeros(n, D, device=x.device)
+    for e in range(E):
+        rows, slot = (idx == e).nonzero(as_tuple=True)
+        if rows.numel() == 0:
+            continue
+        pre = xd[rows] @ w_up[e].float().T
+        y = (F.silu(pre[:, :H]) * pre[:, H:]) @ w_down[e].float().T
+        routed = routed.index_add(0, rows, w[rows, slot].unsqueeze(1) * y)
+    sg, su, sd = (t.float() for t in shared)
+    dense = (F.silu(xf @ sg.T) * (xf @ su.T)) @ sd.T
+    ((routed + dense) * go.float()).sum().backward()
+    return xf.grad
+
+
+def ep_parity_check(device, group, rank, world, tokens=2048):
+    """Expert-parallel layer against this package's single-GPU layer on the same tokens and the same (unsharded)
+    weights, outside every timed region; mirrors the reference's tests/test_multigpu.py:96-212. Every rank draws
+    its own tokens. Returns a dict of the worst figures over all ranks with "ok"."""
+    import torch.distributed as dist
+    import flashfusedmoe_b200 as ffm
+    from flashfusedmoe_b200 import ops
+    fm = sys.modules["flashfusedmoe_b200.fused_moe"]
+    k, E, D = CFG["top_k"], CFG["num_experts"], CFG["d_model"]
+    full = build_layer(device, None)
+    sharded = build_layer(device, group)          # same seed, same weights; keeps this rank's experts
+    el = E // world
+    torch.manual_seed(CFG["seed"] + 5000 + rank)
+    x = torch.randn(tokens, D, device=device).bfloat16()
+    go = torch.randn(tokens, D, device=device).bfloat16()
+
+    def shared_of(layer):
+        se = layer.shared_expert
+        return (se.w_gate.weight, se.w_up.weight, se.w_down.weight)
+
+    xe = x.clone().requires_grad_()
+    out_e, m_e = ffm.fused_moe(xe, sharded.gate.weight, sharded.w_up, sharded.w_down, top_k=k, ep_group=group,
+                               shared_expert_weights=shared_of(sharded), return_metrics=True)
+    out_e.backward(go)
+    ops.check_status()
+    # the same tokens through the single-GPU path with the full weights
+    ffm.set_ep_group(None)
+    xs = x.clone().requires_grad_()
+    addend = fm.glu_ffn(xs, *shared_of(full))
+    out_1, m_1 = ffm.fused_moe(xs, full.gate.weight, full.w_up, full.w_down, top_k=k, return_metrics=True,
+                               _addend=addend)
+    out_1.backward(go)
+    idx = ops.route_forward(x, full.gate.weight.detach(), k).topk_idx
+    ops.check_status()
+    ffm.set_ep_group(group)
+    # expert weight gradients: summed over every rank's tokens and scaled by 1 / ep (fused_moe.py:961-966)
+    g_up, g_down = full.w_up.grad.float().clone(), full.w_down.grad.float().clone()
+    dist.all_reduce(g_up, group=group)
+    dist.all_reduce(g_down, group=group)
+    dh_ref = routing_only_input_grad(x, go, full.gate.weight.detach(), full.w_up.detach(), full.w_down.detach(),
+                                     [t.detach() for t in shared_of(full)], idx)
+    res = {
+        "counts_equal": float(torch.equal(m_e["tokens_per_expert"], m_1["tokens_per_expert"])),
+        "out": _rel(out_e, out_1),
+        "dW_up": _rel(sharded.w_up.grad, g_up[rank * el:(rank + 1) * el] / world),
+        "dW_down": _rel(sharded.w_down.grad, g_down[rank * el:(rank + 1) * el] / world),
+        "dGate": _rel(sharded.gate.weight.grad, full.gate.weight.grad),
+        "dW_shared": max(_rel(a.grad, b.grad) for a, b in zip(shared_of(sharded), shared_of(full))),
+        "dH": _rel(xe.grad, dh_ref),
+    }
+    t = torch.tensor([res["out"], res["dW_up"], res["dW_down"], res["dGate"], res["dW_shared"], res["dH"],
+                      1.0 - res["counts_equal"]], device=device, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+    out, dwu, dwd, dg, dws, dh, cnt_bad = (float(v) for v in t)
+    tol = {"out": 1e-6, "dW_up": 2e-2, "dW_down": 2e-2, "dGate": 1e-3, "dW_shared": 1e-6, "dH": 2e-2}
+    worst = {"out": out, "dW_up": dwu, "dW_down": dwd, "dGate": dg, "dW_shared": dws, "dH": dh}
+    ok = cnt_bad == 0.0 and all(worst[n] <= tol[n] for n in tol)
+    del full, sharded
+    torch.cuda.empty_cache()
+    return {"ok": bool(ok), "counts_equal": cnt_bad == 0.0, **worst, "tolerance": tol, "tokens_per_rank": tokens,
+            "against": "single-GPU path of this package on the same tokens and unsharded weights (out, dW, dGate, "
+                       "counts); fp32 autograd restatement on the GPU for the routing-only + shared-expert dH; "
+                       "maximum over ranks of max|a-b| / max|b|"}
+
+
+def measure_peer_copy(group, device, rank, world, nbytes=256 << 20, repeats=5):
+    """NVLink bandwidth per direction while every rank copies `nbytes` to its right-hand neighbour at once: with the
+    copy engine (torch copy_ into the neighbour's symmetric buffer) and with this library's plain-store push kernel.
+    Returns GB/s (best of `repeats`, maximum time over ranks), or None when symmetric memory is unavailable."""
+    import ctypes
+    import torch.distributed as dist
+    from flashfusedmoe_b200 import _lib, ops
+    try:
+        import torch.distributed._symmetric_memory as symm_mem
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=device)
+        hdl = symm_mem.rendezvous(buf, group)
+        nxt = (rank + 1) % world
+        peer = hdl.get_buffer(nxt, (nbytes,), torch.uint8)
+        peer_ptr = int(hdl.buffer_ptrs[nxt])
+    except Exception as exc:  # no symmetric memory on this build
+        return {"unavailable": str(exc)[:200]}
+    src = torch.empty(nbytes, dtype=torch.uint8, device=device).random_(0, 255)
+    lib = _lib.load()
+
+    def best_ms(fn):
+        best = None
+        for _ in range(repeats + 1):
+            torch.cuda.synchronize()
+            dist.barrier(group)
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            ms = a.elapsed_time(b)
+            best = ms if best is None else min(best, ms)
+        t = torch.tensor([best], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+        return float(t[0])
+
+    def push():
+        srcs = (ctypes.c_void_p * 1)(src.data_ptr())
+        dsts = (ctypes.c_void_p * 1)(peer_ptr)
+        sizes = (ctypes.c_int64 * 1)(nbytes)
+        _lib.check(lib.ffm_p2p_push(1, srcs, dsts, sizes, ops._stream()), "ffm_p2p_push")
+
+    copy_ms = best_ms(lambda: peer.copy_(src, non_blocking=True))
+    push_ms = best_ms(push)
+    torch.cuda.synchronize()
+    dist.barrier(group)
+    del peer, hdl, buf
+    return {"bytes": nbytes, "copy_engine_gbs": nbytes / (copy_ms * 1e-3) / 1e9,
+            "push_kernel_gbs": nbytes / (push_ms * 1e-3) / 1e9,
+            "pattern": "every rank to its right-hand neighbour at the same time, per direction"}
+
+
+def other_configs(group, rank, world, device):
+    """The other BASELINE shapes, a few steps each: configs[2] (Mixtral-shaped, Zipf gate bias) and, expert parallel
+    only, configs[3] (fine-grained with latent projection) as tokens/s forward + backward; configs[4] (decode shape,
+    forward only) as p50 / p99 latency, eager and replayed from a CUDA graph. Rank 0 gets the dict."""
+    from flashfusedmoe_b200 import bench_configs, bench_decode
+    out = {}
+    try:
+        out["configs[2]"] = bench_configs.run(3, 6, 3, group, rank, world, device, per_kernel=False)
+        torch.cuda.empty_cache()
+        if world > 1:
+            out["configs[3]"] = bench_configs.run(4, 8, 3, group, rank, world, device, per_kernel=False)
+            torch.cuda.empty_cache()
+        else:
+            out["configs[3]"] = {"skipped": "expert-parallel configuration (latent projection around the exchange): N >= 2"}
+        out["configs[4]_eager"] = bench_decode.run(60, 10, 128, False, group, rank, world, device)
+        torch.cuda.empty_cache()
+        out["configs[4]_graph"] = bench_decode.run(60, 10, 128, True, group, rank, world, device)
+        torch.cuda.empty_cache()
+    except Exception as exc:   # the headline line must still be printed
+        out["error"] = f"{type(exc).__name__}: {str(exc)[:300]}"
+    if rank != 0:
+        return None
+    keep = ("value", "unit", "ms_per_step", "gemm_tflops_per_gpu_whole_step", "p50", "p99", "min", "mode",
+            "weight_stream_bound_ms", "tokens_per_gpu", "iters", "steps", "config", "skipped")
+    return {n: ({k: v for k, v in d.items() if k in keep} if isinstance(d, dict) else d) for n, d in out.items()}
+
+
 def run_reference_arm(args, rank):
     if rank != 0:
         return
@@ -276,6 +452,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the seconds-long sustained region and the other BASELINE configurations")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -297,6 +475,12 @@ def main():
         group = dist.group.WORLD
     W = max(args.warmup, 3)
     K = args.steps
+
+    # ---- expert parallel only: numerics of the sharded layer against the single-GPU path, before anything is timed
+    ep_parity = nvlink = None
+    if world > 1:
+        ep_parity = ep_parity_check(device, group, rank, world)
+        nvlink = measure_peer_copy(group, device, rank, world)
 
     layer = build_layer(device, group)
     tokens = CFG["batch"] * CFG["seq"]
@@ -325,10 +509,6 @@ def main():
     import gc
     gc.collect()
     gc.disable()
-    try:
-        os.nice(-10)   # the hosts are shared: a descheduled launch thread starves the GPU for milliseconds
-    except OSError:
-        pass
     fence()
     if sampler:
         sampler.begin()
@@ -352,12 +532,10 @@ def main():
 
     # ---- per-kernel pass: the same K steps again with a CUDA-event pair around every launch of this library ----
     # (kept out of the timed region above: the ~60 extra event records per step cost about 5 % of a 2 ms step)
-    # On one GPU this pass also keeps every kernel on a single stream: in the timed region the HBM-bound kernels
-    # share the GPU with GEMMs of another stream, and an event pair around such a kernel would time the sharing.
-    _fm = sys.modules["flashfusedmoe_b200.fused_moe"]
-    overlap_was = _fm._OVERLAP
-    if world == 1:
-        _fm._OVERLAP = False
+    # Same schedule as the timed region: same streams, and the GLU backward riding inside the dW_down GEMM launch,
+    # whose event pair therefore times that whole launch against dW_down's FLOPs alone. An event pair around an
+    # HBM-bound kernel that shares the GPU with a GEMM of another stream times the sharing, so the figures of the
+    # non-GEMM kernels are upper bounds.
     time.sleep(0.5)   # let the board recover the power headroom the timed region started with
     for _ in range(2):
         step()
@@ -367,7 +545,6 @@ def main():
         step()
     fence()
     ops.set_timer(None)
-    _fm._OVERLAP = overlap_was
     a2a_bytes = ops.a2a_bytes_sent - a2a_bytes0
 
     # ---- expert parallel only: K steps whose row exchanges move nothing (everything else runs) -----------------
@@ -447,12 +624,40 @@ def main():
     assert len(read) == K and all(v == v for v in read)
     e2e_ms = e0.elapsed_time(e1)
     clocks = sampler.stop() if sampler else None  # sampled from the start of the timed region to here
+
+    # ---- sustained: the same step for at least two seconds (the board settles at its power cap) -------------------
+    sus_ms, sus_steps, sus_clocks = 0.0, 0, None
+    if not args.no_extras:
+        sus_steps = max(K, int(2500.0 / max(ms / K, 1e-3)) + 1)
+        sampler2 = ClockSampler(local_rank) if rank == 0 else None
+        if sampler2:
+            sampler2.start()
+        fence()
+        if sampler2:
+            sampler2.begin()
+        s0 = torch.cuda.Event(enable_timing=True)
+        s1 = torch.cuda.Event(enable_timing=True)
+        s0.record()
+        for _ in range(sus_steps):
+            step()
+        s1.record()
+        fence()
+        sus_ms = s0.elapsed_time(s1)
+        sus_clocks = sampler2.stop() if sampler2 else None
+        ops.check_status()
     gc.enable()
 
-    t = torch.tensor([ms, e2e_ms, dry_ms if dry_ms is not None else 0.0], device=device, dtype=torch.float64)
+    t = torch.tensor([ms, e2e_ms, dry_ms if dry_ms is not None else 0.0, sus_ms], device=device, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms, e2e_ms, dry_ms = float(t[0]), float(t[1]), float(t[2])
+    ms, e2e_ms, dry_ms, sus_ms = float(t[0]), float(t[1]), float(t[2]), float(t[3])
+
+    # ---- the other BASELINE configurations, a few steps each, after every timed region of the headline workload ----
+    other = None
+    if not args.no_extras:
+        del layer, step, x, go, x_bufs
+        torch.cuda.empty_cache()
+        other = other_configs(group, rank, world, device)
 
     if rank == 0:
         peaks = measured_peaks()
@@ -463,6 +668,12 @@ def main():
         gemm_launches = sum(kt[n][0] for n in gemm_names if n in kt)
         achieved = fl["gemm"] * K / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else None
         value = tokens * world * K / (ms * 1e-3)
+        sm_mhz = (clocks or {}).get("sm_mhz")
+        sm_max = (clocks or {}).get("sm_max_mhz")
+        # the hardware's dense bf16 rate at the clock sampled during the timed regions (2250 TFLOP/s at the maximum)
+        hw_rate = 2250.0 * sm_mhz / sm_max if sm_mhz and sm_max else None
+        D_, H_, k_ = CFG["d_model"], CFG["ffn_dim"] // 2, CFG["top_k"]
+        rows_ = tokens * k_   # routed rows a GPU's grouped GEMMs see (balanced routing)
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
             "ms_per_step": ms / K, "step_ms_median": step_ms[K // 2], "step_ms_max": step_ms[-1],
@@ -478,33 +689,54 @@ def main():
             "gpu_launches": launches,
             "clocks": clocks,
             "roofline": {
-                "bound": "tensor", "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
-                "frac": (achieved / peaks["tflops"]) if achieved else None,
-                # dram__bytes_read.sum + dram__bytes_write.sum of the largest grouped-GEMM launch of a step
-                # (up-projection + GLU of the routed experts: 134.4 MB + 350.4 MB against 536 MB algorithmic),
-                # from the ncu capture summarised in profiles/gemm_up_glu_pair_config2_ncu_full.md
-                "traffic": 484.8e6 if world == 1 else None,
+                # the timed regions are sub-second bursts, so the burst cuBLAS figure is the denominator
+                "bound": "tensor", "achieved": achieved, "peak": peaks["tflops_burst"], "unit": "TFLOP/s",
+                "frac": (achieved / peaks["tflops_burst"]) if achieved else None,
+                # not captured by this run (ncu is never in a timed run); the ncu figures are in the profile summaries
+                "traffic": None,
+                # what the largest grouped-GEMM launch of a step (up-projection + GLU of the routed experts) must
+                # move: grouped rows x D in, weights in, activations and pre-activations out
+                "algorithmic_bytes_largest_launch": 2.0 * (rows_ * D_ + CFG["num_experts"] // world * 2 * H_ * D_
+                                                           + rows_ * 3 * H_),
                 "kernel": "ffm_gemm_kernel (tcgen05 grouped GEMM, all instantiations)",
-                "measured_in": "a second pass of the same K steps after the timed region, every kernel on one stream, "
-                               "with a CUDA-event pair around every kernel launch of the library",
-                "peak_source": f"{peaks['source']} sustained cuBLAS bf16 (burst {peaks['tflops_burst']})",
+                "measured_in": "a second pass of the same K steps after the timed region, same streams and same "
+                               "kernels as the timed region (GLU backward riding in the dW_down launch), with a "
+                               "CUDA-event pair around every kernel launch of the library",
+                "peak_source": f"{peaks['source']} cuBLAS bf16 burst (sustained {peaks['tflops']})",
                 "frac_of_burst": (achieved / peaks["tflops_burst"]) if achieved else None,
+                "frac_of_sustained": (achieved / peaks["tflops"]) if achieved else None,
                 "frac_of_nominal_2250": (achieved / 2250.0) if achieved else None,
+                "frac_of_hw_rate_at_sampled_clock": (achieved / hw_rate) if achieved and hw_rate else None,
+                "whole_step_tflops": fl["gemm"] * K / (ms * 1e-3) / 1e12,
                 "gemm_launches": gemm_launches, "gemm_ms_per_step": gemm_ms / K,
                 "algorithmic_tflop_per_step": fl["gemm"] / 1e12,
                 "other_kernels_ms_per_step": {n: v[1] / K for n, v in kt.items()
                                               if n not in gemm_names and n != "all_to_all"},
             },
         }
+        if sus_steps:
+            line["sustained"] = {"value": tokens * world * sus_steps / (sus_ms * 1e-3), "unit": UNIT,
+                                 "steps": sus_steps, "seconds": sus_ms * 1e-3, "ms_per_step": sus_ms / sus_steps,
+                                 "whole_step_tflops": fl["gemm"] * sus_steps / (sus_ms * 1e-3) / 1e12,
+                                 "clocks": sus_clocks}
+        if ep_parity is not None:
+            line["ep_parity"] = ep_parity
+        if other is not None:
+            line["other_configs"] = other
         if world > 1 and "all_to_all" in kt:
             # expert-parallel exchange on this rank: three all-to-alls per step (dispatch, combine, backward).
             # Time is from CUDA events around each call on its issuing stream, so it includes waiting for peers;
-            # the NVLink fraction is against the 770 GB/s per-direction peer-copy figure measured on this pool.
+            # the NVLink fraction is against the per-direction peer copy measured by this run (measure_peer_copy).
             n_a2a, a2a_ms = kt["all_to_all"]
             gbs = a2a_bytes / (a2a_ms * 1e-3) / 1e9 if a2a_ms > 0 else None
+            link = (nvlink or {}).get("copy_engine_gbs")
             line["expert_parallel"] = {"all_to_all_calls_per_step": n_a2a / K, "all_to_all_ms_per_step": a2a_ms / K,
                                        "bytes_sent_per_step": a2a_bytes / K, "achieved_gbs_per_direction": gbs,
-                                       "nvlink_frac_of_770": (gbs / 770.0) if gbs else None,
+                                       "nvlink_peer_copy": nvlink,
+                                       "nvlink_frac_of_measured_peer_copy": (gbs / link) if gbs and link else None,
+                                       "nvlink_frac_of_nominal_900": (gbs / 900.0) if gbs else None,
+                                       "note": ("E = 8 experts over 8 ranks: one local expert per rank, the "
+                                                "degenerate case of this weak-scaling workload" if world == 8 else None),
                                        "share_of_step_in_kernel_pass": (a2a_ms / K) / (ms / K),
                                        # exposed = step time minus the time of the same step with exchanges that move
                                        # nothing; hidden = 1 - exposed / (event time of the exchanges)
@@ -521,6 +753,8 @@ def main():
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+    if ep_parity is not None and not ep_parity["ok"]:
+        sys.exit(1)   # the throughput of a layer whose numbers are wrong is not a result
 
 
 if __name__ == "__main__":

@@ -33,23 +33,10 @@ def zipf_bias(E, seed, s=1.1):
     return bias - bias.mean()
 
 
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--config", type=int, required=True, choices=[3, 4])
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
-    a = ap.parse_args()
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    group = None
-    if world > 1:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
-        group = dist.group.WORLD
-
+def run(config, steps, warmup, group, rank, world, dev, per_kernel=True):
+    """Time `steps` forward + backward passes of one configuration on an initialised process group (or a single
+    GPU, group None). Returns the result dict on rank 0 and None elsewhere."""
+    a = argparse.Namespace(config=config, steps=steps, warmup=warmup)
     if a.config == 3:
         D, F, E, k, N = 4096, 28672, 8, 2, 8192
         H = F // 2
@@ -85,7 +72,7 @@ def main():
         name = "BASELINE configs[2]: D=4096 E=8 top_k=2 swiglu ffn_dim=2x14336, 8192 tokens/GPU, Zipf(1.1) gate bias"
     else:
         if world < 2:
-            raise SystemExit("config 4 is an expert-parallel configuration: run it under torchrun with N >= 2")
+            raise ValueError("config 4 is an expert-parallel configuration: run it under torchrun with N >= 2")
         D, F, E, k, N, L = 2048, 2816, 64, 6, 16384, 512
         H = F // 2
         torch.manual_seed(3)
@@ -132,26 +119,57 @@ def main():
     fence()
     ms = t0.elapsed_time(t1)
     timer = ops.KernelTimer()
-    ops.set_timer(timer)
-    for _ in range(a.steps):
-        step()
-    fence()
-    ops.set_timer(None)
+    if per_kernel:
+        ops.set_timer(timer)
+        for _ in range(a.steps):
+            step()
+        fence()
+        ops.set_timer(None)
     ops.check_status()
     t = torch.tensor([ms], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    line = None
     if rank == 0:
         kt = timer.totals_ms()
         gemm_ms = sum(kt[n][1] for n in ("gemm_up_glu", "gemm", "gemm_wgrad") if n in kt)
         line = {"metric": "moe_layer_tokens_per_s_fwd_bwd", "config": name, "n_gpus": world, "steps": a.steps,
                 "value": N * world * a.steps / (float(t[0]) * 1e-3), "unit": "tokens/s",
                 "ms_per_step": float(t[0]) / a.steps, "dtype": "bf16", "data": "synthetic",
-                "gemm_ms_per_step": gemm_ms / a.steps,
-                "gemm_tflops_per_gpu_nominal_flops": flops * a.steps / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else None,
-                "kernel_ms_per_step": {n: v[1] / a.steps for n, v in kt.items()}}
+                "algorithmic_gemm_tflop_per_step_per_gpu": flops / 1e12,
+                "gemm_tflops_per_gpu_whole_step": flops * a.steps / (float(t[0]) * 1e-3) / 1e12}
+        if per_kernel:
+            line.update({"gemm_ms_per_step": gemm_ms / a.steps,
+                         "gemm_tflops_per_gpu_nominal_flops": (flops * a.steps / (gemm_ms * 1e-3) / 1e12
+                                                               if gemm_ms > 0 else None),
+                         "kernel_ms_per_step": {n: v[1] / a.steps for n, v in kt.items()}})
         if "tpe" in counts_seen:
             line["tokens_per_expert_rank0"] = counts_seen["tpe"].tolist()
+    if a.config == 4:
+        sync.remove_hooks()
+    return line
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--config", type=int, required=True, choices=[3, 4])
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    a = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    group = None
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+        group = dist.group.WORLD
+    if a.config == 4 and world < 2:
+        raise SystemExit("config 4 is an expert-parallel configuration: run it under torchrun with N >= 2")
+    line = run(a.config, a.steps, a.warmup, group, rank, world, dev)
+    if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

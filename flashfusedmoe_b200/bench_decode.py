@@ -18,27 +18,13 @@ import torch
 import torch.distributed as dist
 
 from . import MoELayer, ops
+from .fused_moe import set_ep_static_forward
 
 
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--iters", type=int, default=200)
-    ap.add_argument("--warmup", type=int, default=20)
-    ap.add_argument("--tokens", type=int, default=128)
-    ap.add_argument("--graph", action="store_true",
-                    help="capture the forward pass in a CUDA graph and time replays (expert parallel: uses the "
-                         "host-sync-free forward, set_ep_static_forward)")
-    a = ap.parse_args()
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    group = None
-    if world > 1:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
-        group = dist.group.WORLD
+def run(iters, warmup, tokens, graph, group, rank, world, dev):
+    """Per-iteration latency of the decode-shaped layer on an initialised process group (or one GPU, group None).
+    Returns the result dict on rank 0 and None elsewhere."""
+    a = argparse.Namespace(iters=iters, warmup=warmup, tokens=tokens, graph=graph)
     D, F, E, k = 7168, 4096, 256, 8
     e_local = E // world
     # build only this rank's experts (the full expert set is 22.5 GB); same seed on every rank for the replicated parts
@@ -65,7 +51,6 @@ def main():
     with torch.no_grad():
         if a.graph:
             if world > 1:
-                from .fused_moe import set_ep_static_forward
                 set_ep_static_forward(a.tokens)
             side = torch.cuda.Stream()
             side.wait_stream(torch.cuda.current_stream())
@@ -97,9 +82,12 @@ def main():
                 times.append(s.elapsed_time(e))
     ops.set_timer(None)
     ops.check_status()
+    if a.graph and world > 1:
+        set_ep_static_forward(None)
     t = torch.tensor(times, device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    line = None
     if rank == 0:
         ts = torch.sort(t).values
         kt = timer.totals_ms()
@@ -116,6 +104,30 @@ def main():
                 "kernel_ms_per_iter": {n: v[1] / a.iters for n, v in kt.items()}}
         if "all_to_all" in kt:
             line["all_to_all_ms_per_iter"] = kt["all_to_all"][1] / a.iters
+    return line
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--iters", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--tokens", type=int, default=128)
+    ap.add_argument("--graph", action="store_true",
+                    help="capture the forward pass in a CUDA graph and time replays (expert parallel: uses the "
+                         "host-sync-free forward, set_ep_static_forward)")
+    a = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    group = None
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+        group = dist.group.WORLD
+    line = run(a.iters, a.warmup, a.tokens, a.graph, group, rank, world, dev)
+    if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

@@ -38,6 +38,16 @@ __device__ __forceinline__ float warp_sum(float v) {
 
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + __expf(-x)); }
 
+// Sigmoid of a routing logit, for the scores that expert selection compares: 1 / (1 + exp(-x)) with every step
+// rounded to fp32 as written (exp evaluated in double and rounded once, IEEE add and divide), the value a fp32
+// evaluation of the reference's formula (kernels/fused_topk.py: tl.sigmoid) rounds to. The fast-math sigmoid above
+// is off by a few units in the last place, enough to reorder experts whose scores nearly tie (saturated scores
+// close to 1 above all), and top-k on sigmoid scores breaks ties by index.
+__device__ __forceinline__ float sigmoid_rn(float x) {
+  const float e = static_cast<float>(exp(-static_cast<double>(x)));
+  return __fdiv_rn(1.0f, __fadd_rn(1.0f, e));
+}
+
 // GLU activation codes shared by every kernel and by the C ABI (FFM_ACT_*).
 //   0 swiglu        : silu(g) * u
 //   1 geglu (tanh)  : 0.5 g (1 + tanh(c (g + 0.044715 g^3))) * u, tanh(x) = 2 sigmoid(2x) - 1

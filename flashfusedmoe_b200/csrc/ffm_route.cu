@@ -143,7 +143,7 @@ __device__ __forceinline__ void route_token(const float (&logit)[NG], long long 
     const float lg = logit[g];
     float v;
     if (o.gating == FFM_GATING_SIGMOID) {
-      v = sigmoidf_(lg);
+      v = sigmoid_rn(lg);
     } else if (o.pre_softmax) {
       v = __expf(lg - lse);
     } else {

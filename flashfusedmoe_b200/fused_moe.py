@@ -63,6 +63,8 @@ def set_ep_dry_exchange(enable):
 
 _side_streams = {}
 _dense_tile_start = {}
+# Backward exchanges issued so far per process group: picks the receive region of the next one (see _backward_region).
+_bwd_exchanges = {}
 
 
 def set_aux_loss_grad(mode):
@@ -305,8 +307,11 @@ class _FusedMoEFunction(torch.autograd.Function):
         else:
             dropped = torch.zeros(1, dtype=torch.int32, device=h.device)
         need_grad = cfg.wants_grad and any(ctx.needs_input_grad[:5])
-        # (without a backward pass nothing sums over the padding rows, so they are not zeroed)
-        Xg = ops.permute_rows(h, routing.src, routing.rows_cap, k, zero_padding=need_grad)
+        # Without a backward pass nothing sums over the padding rows, so they are not zeroed -- except with capacity
+        # dropping: a dropped slot keeps its grouped row (now a padding row) with weight 0, and 0 * (whatever the
+        # GEMMs make of uninitialised memory, possibly NaN) would reach the output through the combine.
+        Xg = ops.permute_rows(h, routing.src, routing.rows_cap, k,
+                              zero_padding=need_grad or cfg.capacity is not None)
         keep = need_grad and not cfg.recompute
         # inference with few rows per expert (decode): one CTA per 128-row tile and no work on tiles without rows
         small = _small_m_kwargs(not need_grad and cfg.capacity is None and N * k < 128 * E, routing.counts)
@@ -419,7 +424,11 @@ class _EPPlan:
         all_counts = torch.empty(ep, counts.numel(), dtype=counts.dtype, device=counts.device)
         torch.distributed.all_gather_into_tensor(all_counts, counts.contiguous(), group=group)
         self.recv_counts = all_counts[:, self.rank * e_local:(self.rank + 1) * e_local].to(torch.int64)  # [ep, E_local]
-        C = all_counts.cpu().numpy()                      # [ep, E] rows rank s routes to expert e (the host sync)
+        # the host sync of the call: the [ep, E] count matrix and, in the same copy, the device status word (a bounded
+        # wait that ran out in an earlier kernel must not go on to produce garbage silently)
+        host = torch.cat([all_counts.reshape(-1), ops.status_tensor(counts.device).to(all_counts.dtype)]).cpu()
+        ops.raise_on_status(host[-1], counts.device)
+        C = host[:-1].view(ep, -1).numpy()                # [ep, E] rows rank s routes to expert e
         self.cnt = [[int(v) for v in row] for row in C.reshape(ep, ep, e_local).sum(-1)]
         self.cnt_t = [[self.cnt[d][s] for d in range(ep)] for s in range(ep)]
         self.send_splits = self.cnt[self.rank]
@@ -591,6 +600,21 @@ def _grouped_wgrad(A, B, groups, tile_start, scale=1.0, passenger=None):
     if S > 1:
         part = part.view(groups, S, A.shape[1], B.shape[1]).sum(dim=1, dtype=torch.float32).to(part.dtype)
     return part if passenger is None else (part, gU)
+
+
+def _backward_region(group):
+    """Receive region of the next backward exchange of `group`: regions 2 and 3 in turn.
+
+    The rows a backward exchange delivers are read in place by that layer's GEMMs, after the exchange's flag barrier.
+    A peer that has left the barrier may already push the next layer's gradient rows, and nothing orders that push
+    after this rank's reads, so two consecutive backward exchanges must not share a region. With two regions a peer's
+    push n + 2 (the next one into the same region) comes after it has seen this rank's signal n + 1, which this rank
+    issues, in stream order, after the reads of exchange n. Every rank runs the same sequence of layers, so the
+    count, and with it the region, agrees across the group."""
+    key = id(group)
+    n = _bwd_exchanges.get(key, 0)
+    _bwd_exchanges[key] = n + 1
+    return 2 + (n & 1)
 
 
 def _small_m_kwargs(enabled, counts):
@@ -782,12 +806,13 @@ class _FusedMoEEPFunction(torch.autograd.Function):
         a2a = _get_side_stream("a2a")
         ready2 = torch.cuda.Event()
         ready2.record()
+        region = _backward_region(group)
         with torch.cuda.stream(a2a):
             a2a.wait_event(ready2)
             if direct:
-                recv_grad, grad_is_view = plan.dispatch_grouped(send, None, 1, 2), True   # grouped [rows_l, W]
+                recv_grad, grad_is_view = plan.dispatch_grouped(send, None, 1, region), True   # grouped [rows_l, W]
             else:
-                recv_grad, grad_is_view = plan.exchange(send, False, 2)
+                recv_grad, grad_is_view = plan.exchange(send, False, region)
         a2a_done = torch.cuda.Event()
         a2a_done.record(a2a)
         send.record_stream(a2a)
@@ -973,6 +998,9 @@ def fused_moe(
                     f"given by max_tokens_per_expert. Fix options:\n"
                     f"  1. Set max_tokens_per_expert={actual_max} (or higher) via calibration\n"
                     f"  2. Set allow_dropped_tokens=True to suppress this error")
+
+    # a device-side failure of an earlier call (bounded wait that ran out, bad index) raises here; no GPU wait
+    ops.poll_status(hidden_states.device)
 
     losses = {}
     if aux_loss_coeff > 0.0:

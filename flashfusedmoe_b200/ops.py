@@ -105,6 +105,49 @@ def check_status(device=None):
         raise RuntimeError(f"libffmoe device status {code}: {_lib.error_string(code)}")
 
 
+_status_host = {}
+
+
+def poll_status(device=None, enqueue=True):
+    """Host-side check of the status word that never waits for the GPU.
+
+    The word is copied to pinned host memory asynchronously (one 4-byte copy on the current stream, queued by an
+    earlier poll); once that copy has finished its value is read here and a non-zero code raises, so a bounded wait
+    that ran out inside one call surfaces at the next call instead of as silent garbage. With `enqueue` a fresh copy
+    is queued for the next poll. Does nothing while the current stream is being captured into a CUDA graph."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    if torch.cuda.is_current_stream_capturing():
+        return
+    key = dev.index if dev.index is not None else torch.cuda.current_device()
+    entry = _status_host.get(key)
+    if entry is None:
+        entry = _status_host[key] = [torch.zeros(1, dtype=torch.int32).pin_memory(), None]
+    host, event = entry
+    if event is not None:
+        if not event.query():
+            return  # the last copy is still in flight: look again at the next call
+        entry[1] = None
+        code = int(host[0])
+        if code != 0:
+            host[0] = 0
+            status_tensor(dev).zero_()
+            raise RuntimeError(f"libffmoe device status {code}: {_lib.error_string(code)} "
+                               "(reported by a kernel of an earlier call; its results are not valid)")
+    if enqueue:
+        host.copy_(status_tensor(dev), non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        entry[1] = ev
+
+
+def raise_on_status(code, device):
+    """Raise for a status code the caller already holds on the host (read together with other data)."""
+    code = int(code)
+    if code != 0:
+        status_tensor(device).zero_()
+        raise RuntimeError(f"libffmoe device status {code}: {_lib.error_string(code)}")
+
+
 def rows_capacity(T, E):
     return int(_lib.load().ffm_rows_capacity(int(T), int(E)))
 

@@ -7,8 +7,10 @@ receive regions, `ffm_p2p_signal_wait` publishes an epoch flag to every peer and
 offsets come from the [ep, ep] matrix of row counts every rank already knows, so nothing but rows and flags crosses
 NVLink. No multicast object is bound (TORCH_SYMM_MEM_DISABLE_MULTICAST=1) and no multimem instruction is used.
 
-Region reuse is safe without extra barriers because every exchange is a full barrier of the group and the layer
-consumes (or copies) a region before it takes part in the exchange that could overwrite it.
+Region reuse needs no extra barrier as long as a rank has consumed (or copied) a region, in stream order, before it
+signals the exchange after which a peer may push into that region again. The forward pass alternates regions 0 and
+1, so this holds by construction; rows of a backward exchange are read in place after its barrier, so consecutive
+backward exchanges alternate between regions 2 and 3 (fused_moe._backward_region).
 """
 
 import ctypes
@@ -27,7 +29,8 @@ DEV_FLAGS_OFFSET = 2048
 DEV_COUNTER_OFFSET = 3072
 COUNTS_OFFSET = 4096
 COUNTS_BYTES = 16 * 256 * 4
-NUM_REGIONS = 3  # dispatch, combine (also the reverse-dispatch of the full input gradient), backward
+# dispatch, combine (also the reverse-dispatch of the full input gradient), and two backward regions used in turn
+NUM_REGIONS = 4
 
 _exchanges = {}
 
