@@ -202,6 +202,14 @@ def build_layer(device, ep_group):
     return layer
 
 
+def layer_counts(layer, x):
+    """Rows this rank routes to every expert (int64 [E], host) for input x."""
+    from flashfusedmoe_b200 import ops
+    xf = x.detach().reshape(-1, x.shape[-1])
+    r = ops.route_forward(xf, layer.gate.weight.detach(), layer.top_k, layer.gating)
+    return r.counts.to(torch.int64).cpu()
+
+
 def make_step(layer, x, go):
     def step():
         for p in layer.parameters():
@@ -210,6 +218,26 @@ def make_step(layer, x, go):
         out, _ = layer(x)
         out.backward(go)
     return step
+
+
+def capture_step(fn, warm=2):
+    """fn() captured into a CUDA graph after `warm` eager runs on a side stream. Every stream the step forks to is
+    joined again before it returns, so the whole forward + backward becomes one graph. Returns (graph, kernels of
+    this library per replay)."""
+    from flashfusedmoe_b200 import ops
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(warm):
+            fn()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    n0 = ops.launch_count
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        fn()
+    torch.cuda.synchronize()
+    return graph, ops.launch_count - n0
 
 
 def oracle_sample_tokens_per_s(sample_tokens, threads, repeats=1):
@@ -452,6 +480,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--launch", default="graph", choices=["graph", "eager"],
+                    help="graph: the step is captured once into a CUDA graph and the timed regions replay it (the "
+                         "launch thread then cannot starve the GPU); eager: every kernel launched from Python. "
+                         "Falls back to eager where the step cannot be captured (it reads counts on the host).")
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the seconds-long sustained region and the other BASELINE configurations")
     args = ap.parse_args()
@@ -478,12 +510,19 @@ def main():
 
     # ---- expert parallel only: numerics of the sharded layer against the single-GPU path, before anything is timed
     ep_parity = nvlink = None
+    tokens = CFG["batch"] * CFG["seq"]
+    # Host-sync-free expert parallelism (set_ep_static_forward): buffers sized for the worst case, exchange tables built
+    # on the device, no host read of the routing counts, so the training step can be captured into a CUDA graph like
+    # the single-GPU one. FFM_BENCH_EP_STATIC=0 measures the host-planned path (one host sync per call, eager only).
+    ep_static = world > 1 and os.environ.get("FFM_BENCH_EP_STATIC", "1") != "0"
+    if ep_static:
+        import flashfusedmoe_b200 as _ffm
+        _ffm.set_ep_static_forward(tokens)
     if world > 1:
         ep_parity = ep_parity_check(device, group, rank, world)
         nvlink = measure_peer_copy(group, device, rank, world)
 
     layer = build_layer(device, group)
-    tokens = CFG["batch"] * CFG["seq"]
     torch.manual_seed(CFG["seed"] + 1000 + rank)  # different tokens on every rank
     x_host = torch.randn(CFG["batch"], CFG["seq"], CFG["d_model"]).bfloat16().pin_memory()
     go = torch.randn(CFG["batch"], CFG["seq"], CFG["d_model"], device=device).bfloat16()
@@ -504,31 +543,62 @@ def main():
         step()
     ops.check_status()
     timer = ops.KernelTimer()
-    # The launch loop runs only a step or so ahead of the GPU right after the fence, so a pause of the launching
-    # thread shows up as a stalled step: keep the cyclic garbage collector out of the timed regions.
+    # The eager launch loop runs only a step or so ahead of the GPU right after the fence, so a pause of the launching
+    # thread (a descheduled process on a shared host, the garbage collector, a driver lock taken by a monitoring
+    # call) shows up as a stalled step. A captured step has no such dependence: K replays are queued at once.
     import gc
     gc.collect()
     gc.disable()
-    fence()
+    graph = None
+    graph_note = None
+    launches_per_replay = 0
+    can_capture = world == 1 or ep_static   # the host-planned expert-parallel step reads the row counts on the host
+    if args.launch == "graph" and can_capture:
+        try:
+            graph, launches_per_replay = capture_step(step)
+        except Exception as exc:   # keep measuring, eagerly
+            graph, graph_note = None, f"capture failed: {type(exc).__name__}: {str(exc)[:200]}"
+            torch.cuda.synchronize()
+    elif args.launch == "graph":
+        graph_note = "not capturable: the host-planned expert-parallel step reads the row counts on the host"
+    run_step = graph.replay if graph is not None else step
+    graph_used = graph is not None
+
+    def timed_region(fn):
+        fence()
+        a = torch.cuda.Event(enable_timing=True)
+        b = torch.cuda.Event(enable_timing=True)
+        marks = [torch.cuda.Event(enable_timing=True) for _ in range(K - 1)]  # per-step marks: a view into the region
+        a.record()
+        for i in range(K):
+            fn()
+            if i < K - 1:
+                marks[i].record()
+        b.record()
+        fence()
+        edges = [a] + marks + [b]
+        return a.elapsed_time(b), [edges[i].elapsed_time(edges[i + 1]) for i in range(K)]
+
+    for _ in range(2):
+        run_step()
     if sampler:
+        fence()
         sampler.begin()
     launches0 = ops.launch_count
-    t0 = torch.cuda.Event(enable_timing=True)
-    t1 = torch.cuda.Event(enable_timing=True)
-    marks = [torch.cuda.Event(enable_timing=True) for _ in range(K - 1)]  # per-step marks: a view into the region
-    t0.record()
-    for i in range(K):
-        step()
-        if i < K - 1:
-            marks[i].record()
-    t1.record()
-    fence()
-    launches = ops.launch_count - launches0
-    ms = t0.elapsed_time(t1)
-    edges = [t0] + marks + [t1]
-    step_series = [edges[i].elapsed_time(edges[i + 1]) for i in range(K)]
+    ms, step_series = timed_region(run_step)
+    launches = (ops.launch_count - launches0) if graph is None else launches_per_replay * K
     step_ms = sorted(step_series)
     ops.check_status()
+    eager = None
+    eager_ms = 0.0
+    if graph is not None:
+        # the same K steps launched kernel by kernel from Python, for comparison (not the reported value)
+        time.sleep(0.3)
+        for _ in range(2):
+            step()
+        eager_ms, eager_series = timed_region(step)
+        eager = {"value": tokens * world * K / (eager_ms * 1e-3), "unit": UNIT, "ms_per_step": eager_ms / K,
+                 "step_ms_median": sorted(eager_series)[K // 2], "step_ms_max": max(eager_series)}
 
     # ---- per-kernel pass: the same K steps again with a CUDA-event pair around every launch of this library ----
     # (kept out of the timed region above: the ~60 extra event records per step cost about 5 % of a 2 ms step)
@@ -546,6 +616,13 @@ def main():
     fence()
     ops.set_timer(None)
     a2a_bytes = ops.a2a_bytes_sent - a2a_bytes0
+    if ep_static:
+        # the host never sees the counts in this mode: one extra call tells how many of this rank's routed rows leave
+        # it; a step moves them three times (dispatch, combine, backward)
+        el = CFG["num_experts"] // world
+        tpe = layer_counts(layer, x)
+        remote_rows = int(tpe.sum() - tpe[rank * el:(rank + 1) * el].sum())
+        a2a_bytes = 3 * K * remote_rows * CFG["d_model"] * 2
 
     # ---- expert parallel only: K steps whose row exchanges move nothing (everything else runs) -----------------
     # step time minus this = the exchange time that compute did not hide
@@ -586,6 +663,29 @@ def main():
             x_bufs[i % 2].copy_(x_host, non_blocking=True)
             uploaded[i % 2].record(copy_stream)
 
+    e2e_graph = None
+    x_in = torch.empty_like(x).requires_grad_()
+    loss_cell = [None]
+
+    def e2e_body():
+        for p in layer.parameters():
+            p.grad = None
+        x_in.grad = None
+        out, _ = layer(x_in)
+        loss = (out * go).sum(dtype=torch.float32)
+        loss.backward()
+        loss_cell[0] = loss.detach().reshape(1)
+
+    if graph is not None:
+        try:
+            with torch.no_grad():
+                x_in.copy_(x)
+            e2e_graph, _ = capture_step(e2e_body)
+        except Exception as exc:
+            e2e_graph = None
+            graph_note = f"end-to-end capture failed: {type(exc).__name__}: {str(exc)[:200]}"
+            torch.cuda.synchronize()
+
     def e2e_run(steps):
         losses_read = []
         main = torch.cuda.current_stream()
@@ -596,14 +696,23 @@ def main():
             if i + 1 < steps:
                 upload(i + 1)
             main.wait_event(uploaded[i % 2])
-            for p in layer.parameters():
-                p.grad = None
-            xd = x_bufs[i % 2].detach().requires_grad_()
-            out, _ = layer(xd)
-            loss = (out * go).sum(dtype=torch.float32)
-            loss.backward()
-            consumed[i % 2].record(main)
-            loss_host[i % 2:i % 2 + 1].copy_(loss.detach().reshape(1), non_blocking=True)
+            if e2e_graph is not None:
+                # the graph reads a fixed input buffer: this step's upload is moved into it on the device
+                with torch.no_grad():
+                    x_in.copy_(x_bufs[i % 2])
+                consumed[i % 2].record(main)
+                e2e_graph.replay()
+                loss = loss_cell[0]
+            else:
+                for p in layer.parameters():
+                    p.grad = None
+                xd = x_bufs[i % 2].detach().requires_grad_()
+                out, _ = layer(xd)
+                loss = (out * go).sum(dtype=torch.float32)
+                loss.backward()
+                consumed[i % 2].record(main)
+                loss = loss.detach().reshape(1)
+            loss_host[i % 2:i % 2 + 1].copy_(loss, non_blocking=True)
             loss_ready[i % 2].record(main)
             if i >= 1:
                 loss_ready[(i - 1) % 2].synchronize()
@@ -628,7 +737,7 @@ def main():
     # ---- sustained: the same step for at least two seconds (the board settles at its power cap) -------------------
     sus_ms, sus_steps, sus_clocks = 0.0, 0, None
     if not args.no_extras:
-        sus_steps = max(K, int(2500.0 / max(ms / K, 1e-3)) + 1)
+        sus_steps = max(K, int(2600.0 / max(step_ms[K // 2], 1e-3)) + 1)
         sampler2 = ClockSampler(local_rank) if rank == 0 else None
         if sampler2:
             sampler2.start()
@@ -639,7 +748,7 @@ def main():
         s1 = torch.cuda.Event(enable_timing=True)
         s0.record()
         for _ in range(sus_steps):
-            step()
+            run_step()
         s1.record()
         fence()
         sus_ms = s0.elapsed_time(s1)
@@ -647,15 +756,19 @@ def main():
         ops.check_status()
     gc.enable()
 
-    t = torch.tensor([ms, e2e_ms, dry_ms if dry_ms is not None else 0.0, sus_ms], device=device, dtype=torch.float64)
+    t = torch.tensor([ms, e2e_ms, dry_ms if dry_ms is not None else 0.0, sus_ms, eager_ms], device=device,
+                     dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms, e2e_ms, dry_ms, sus_ms = float(t[0]), float(t[1]), float(t[2]), float(t[3])
+    ms, e2e_ms, dry_ms, sus_ms, eager_ms = (float(v) for v in t)
+    if eager is not None:
+        eager.update(value=tokens * world * K / (eager_ms * 1e-3), ms_per_step=eager_ms / K)
 
     # ---- the other BASELINE configurations, a few steps each, after every timed region of the headline workload ----
     other = None
     if not args.no_extras:
-        del layer, step, x, go, x_bufs
+        del layer, step, x, go, x_bufs, x_in, graph, e2e_graph, run_step
+        loss_cell[0] = None
         torch.cuda.empty_cache()
         other = other_configs(group, rank, world, device)
 
@@ -683,6 +796,12 @@ def main():
             "config": {"workload": "BASELINE configs[1]: MoELayer d_model=1024 ffn_dim=4096 E=8 top_k=2 swiglu + 1 shared "
                                    "expert (ffn_dim 4096), x [8,2048,1024] bf16 seed 1, weights N(0,0.02), forward+backward",
                        "tokens_per_gpu": tokens, "expert_parallel": world,
+                       "launch": ("one forward + backward step captured into a CUDA graph, replayed K times"
+                                  if graph_used else "eager: every kernel launched from Python"),
+                       "launch_note": graph_note,
+                       "expert_parallel_mode": (None if world == 1 else
+                                                "host-sync-free (set_ep_static_forward)" if ep_static else
+                                                "host-planned (one host read of the routing counts per call)"),
                        "l2": "no explicit flush: one step streams > 1 GB of activations and weights, 8x the 126 MB L2"},
             "e2e": {"value": tokens * world * K / (e2e_ms * 1e-3), "unit": UNIT,
                     "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": 4},
@@ -714,6 +833,8 @@ def main():
                                               if n not in gemm_names and n != "all_to_all"},
             },
         }
+        if eager is not None:
+            line["eager"] = eager
         if sus_steps:
             line["sustained"] = {"value": tokens * world * sus_steps / (sus_ms * 1e-3), "unit": UNIT,
                                  "steps": sus_steps, "seconds": sus_ms * 1e-3, "ms_per_step": sus_ms / sus_steps,
@@ -728,6 +849,7 @@ def main():
             # Time is from CUDA events around each call on its issuing stream, so it includes waiting for peers;
             # the NVLink fraction is against the per-direction peer copy measured by this run (measure_peer_copy).
             n_a2a, a2a_ms = kt["all_to_all"]
+            ref_ms = eager["ms_per_step"] * K if eager is not None else ms
             gbs = a2a_bytes / (a2a_ms * 1e-3) / 1e9 if a2a_ms > 0 else None
             link = (nvlink or {}).get("copy_engine_gbs")
             line["expert_parallel"] = {"all_to_all_calls_per_step": n_a2a / K, "all_to_all_ms_per_step": a2a_ms / K,
@@ -741,8 +863,9 @@ def main():
                                        # exposed = step time minus the time of the same step with exchanges that move
                                        # nothing; hidden = 1 - exposed / (event time of the exchanges)
                                        "ms_per_step_without_exchange_payload": dry_ms / K,
-                                       "exposed_exchange_ms_per_step": max(0.0, (ms - dry_ms) / K),
-                                       "hidden_frac": (min(1.0, max(0.0, 1.0 - (ms - dry_ms) / a2a_ms))
+                                       # (both eager: a replayed graph is compared with nothing here)
+                                       "exposed_exchange_ms_per_step": max(0.0, (ref_ms - dry_ms) / K),
+                                       "hidden_frac": (min(1.0, max(0.0, 1.0 - (ref_ms - dry_ms) / a2a_ms))
                                                        if a2a_ms > 0 else None),
                                        "transport": os.environ.get("FFM_EP_TRANSPORT", "p2p")}
         if world == 1 and not args.no_cpu_baseline:

@@ -282,13 +282,15 @@ __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 
-// GLU backward over rows [0, pz_rows): (d gate | d up)[r, :] from dAct[r, :] and the saved pre-activations.
+// GLU backward over rows [0, rows): (d gate | d up)[r, :] from dAct[r, :] and the saved pre-activations. `rows` is
+// pz_rows cut at the end of the last group's tiles (buffers sized for a worst case hold far more rows than are used).
 // `tid` / `nthreads` enumerate the passenger threads of the whole grid; four independent 16-byte column chunks per
 // thread and trip keep enough loads in flight for 256 threads per SM to stream at HBM speed.
-__device__ __forceinline__ void passenger_glu_backward(const GemmParams& p, long long tid, long long nthreads) {
+__device__ __forceinline__ void passenger_glu_backward(const GemmParams& p, long long rows, long long tid,
+                                                       long long nthreads) {
   const int H = p.pz_h;
   const int chunks = H >> 3;
-  const long long total = p.pz_rows * chunks;
+  const long long total = rows * chunks;
   for (long long base = tid; base < total; base += 4 * nthreads) {
     uint4 ga[4], gg[4], uu[4];
     long long r[4];
@@ -540,7 +542,11 @@ ffm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     }
   } else if (PASS && warp >= 2 + EPI_WARPS) {
     // ================= passenger (warps 6..13) =================
-    passenger_glu_backward(p, static_cast<long long>(blockIdx.x) * PASSENGER_THREADS + (threadIdx.x - GEMM_THREADS),
+    long long pz_rows = p.pz_rows;
+    const long long used = static_cast<long long>(ctrl->tile_start[p.groups]) * BM;
+    if (used < pz_rows) pz_rows = used;
+    passenger_glu_backward(p, pz_rows,
+                           static_cast<long long>(blockIdx.x) * PASSENGER_THREADS + (threadIdx.x - GEMM_THREADS),
                            static_cast<long long>(gridDim.x) * PASSENGER_THREADS);
   } else {
     // ================= epilogue (warps 2..5) =================

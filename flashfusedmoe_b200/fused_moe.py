@@ -500,74 +500,199 @@ class _EPPlan:
             return all_to_all_rows(rows, out_splits, in_splits, self.group), False
 
 
-# Host-sync-free forward (inference): set_ep_static_forward(max_tokens_per_rank) declares, with the same value on
-# every rank, the most tokens a rank passes per call. Without gradients the expert-parallel forward then sizes its
-# buffers for the worst case (every routed row of every rank arriving at one rank), shares the counts and builds the
-# exchange tables on the device, and never reads anything back: the call is a fixed launch sequence that a CUDA graph
-# can capture and replay.
+# Host-sync-free expert parallelism: set_ep_static_forward(max_tokens_per_rank) declares, with the same value on
+# every rank, the most tokens a rank passes per call. The expert-parallel layer (forward and backward, without latent
+# projection) then sizes its buffers for the worst case (every routed row of every rank arriving at one rank), shares
+# the counts and builds the exchange tables on the device, and never reads anything back: a call is a fixed launch
+# sequence that a CUDA graph can capture and replay. Kernels only touch the rows in use (the persistent GEMM stops at
+# the last real tile), so the worst-case sizes cost address space and memory, not time.
 _EP_STATIC_TOKENS = None
 
 
 def set_ep_static_forward(max_tokens_per_rank):
-    """Enable (int, identical on every rank) or disable (None) the host-sync-free expert-parallel forward."""
+    """Enable (int, identical on every rank) or disable (None) host-sync-free expert parallelism: inference and
+    training calls without latent projection then run without reading the routing counts on the host."""
     global _EP_STATIC_TOKENS
     _EP_STATIC_TOKENS = None if max_tokens_per_rank is None else int(max_tokens_per_rank)
 
 
-def _ep_forward_static(hidden_states, gate_weight, w_up, w_down, sw, cfg, dtype):
-    """Expert-parallel forward without a host read: routing -> counts to every rank (peer stores) -> tables built on
+class _FusedMoEEPStaticFunction(torch.autograd.Function):
+    """Expert-parallel layer without a host read: routing -> counts to every rank (peer stores) -> tables built on
     the device (ffm_p2p_plan) -> rows into the owners' grouped layouts -> grouped GEMMs over the worst-case buffer
-    (the persistent kernel stops at the last real tile) -> rows back -> weighted combine."""
-    group = cfg.ep_group
-    ep = torch.distributed.get_world_size(group)
-    N, D = hidden_states.shape
-    El = w_up.shape[0]
-    E = ep * El
-    H = w_up.shape[1] // 2
-    k = cfg.top_k
-    T = N * k
-    if N > _EP_STATIC_TOKENS:
-        raise RuntimeError(f"static expert-parallel forward was declared for at most {_EP_STATIC_TOKENS} tokens per "
-                           f"rank, got {N}")
-    h, g, wu, wd = _to(hidden_states, dtype), _to(gate_weight, dtype), _to(w_up, dtype), _to(w_down, dtype)
-    routing = _route(h, g, cfg, False)
-    shared_out = None
-    if sw[0] is not None:
-        swg, swu, swd = _to(sw[0], dtype), _to(sw[1], dtype), _to(sw[2], dtype)
-        side = _get_side_stream("shared", priority=-1)
-        ready = torch.cuda.Event()
-        ready.record()
-        with torch.cuda.stream(side):
-            side.wait_event(ready)
-            shared_out, _, _ = _glu_ffn_forward(h, swg, swu, swd, cfg.shared_activation, want_preact=False)
-        shared_done = torch.cuda.Event()
-        shared_done.record(side)
-    rb = D * h.element_size()
-    cap_rows = (ep * _EP_STATIC_TOKENS * k + 256 * El + 255) // 256 * 256   # every row of every rank lands here
-    px = p2p.get_exchange(group, h.device, cap_rows * rb)
-    C = px.share_counts(routing.counts)
-    t = px.plan_dev(C, El)
-    cpos, src_c = _compact_send_map(routing, T)
-    tot = t["totals"]
-    px.push_rows_dev(h, src_c, k, rb, t["dispatch"], t["dispatch_end"], tot[0:1], T, 0)
-    px.barrier_dev()
-    # (the padding rows of the grouped layout stay as they are: without a backward pass nothing sums over them, and
-    # a GEMM row only depends on its own input row)
-    Xg = px.region_view(0, cap_rows, D, h.dtype)
-    small = _small_m_kwargs(ep * _EP_STATIC_TOKENS * k < 128 * E, None)
-    if small:
-        small["valid_rows"] = C[:, px.rank * El:(px.rank + 1) * El].sum(0, dtype=torch.int32)
-    act, _ = ops.grouped_gemm_glu(Xg, wu, wu.view(-1, D)[H:], 2 * H, El, t["tile_start"], D, H, cfg.activation,
-                                  want_preact=False, **small)
-    Y = ops.grouped_gemm(act, wd, _lib.B_KMAJOR, El, t["tile_start"], H, D, **small)
-    px.push_rows_dev(Y, None, 1, rb, t["combine"], t["combine_end"], tot[1:2], cap_rows, 1)
-    px.barrier_dev()
-    returned = px.region_view(1, T, D, h.dtype)
-    if shared_out is not None:
-        torch.cuda.current_stream().wait_event(shared_done)
-    out = ops.combine_forward(returned, cpos, routing.topk_w, N, k, addend=shared_out)
-    aux, z = _loss_tensors(routing, N, E, cfg)
-    return out, aux, z, routing.counts, torch.zeros(1, dtype=torch.int32, device=h.device)
+    -> rows back -> weighted combine. The backward pass reuses the forward's device tables for its one exchange of
+    the weighted output gradient (and the reverse exchange of cfg.ep_full_input_grad). Same results, bit for bit, as
+    _FusedMoEEPFunction with the peer-store transport."""
+
+    @staticmethod
+    def forward(ctx, hidden_states, gate_weight, w_up, w_down, sw_gate, sw_up, sw_down, cfg, dtype):
+        group = cfg.ep_group
+        ep = torch.distributed.get_world_size(group)
+        N, D = hidden_states.shape
+        El = w_up.shape[0]
+        E = ep * El
+        H = w_up.shape[1] // 2
+        k = cfg.top_k
+        T = N * k
+        if N > _EP_STATIC_TOKENS:
+            raise RuntimeError(f"static expert-parallel mode was declared for at most {_EP_STATIC_TOKENS} tokens per "
+                               f"rank, got {N}")
+        has_shared = sw_gate is not None
+        h, g, wu, wd = _to(hidden_states, dtype), _to(gate_weight, dtype), _to(w_up, dtype), _to(w_down, dtype)
+        need_grad = cfg.wants_grad and any(ctx.needs_input_grad[:7])
+        routing = _route(h, g, cfg, hidden_states.requires_grad)
+        shared = None
+        if has_shared:
+            swg, swu, swd = _to(sw_gate, dtype), _to(sw_up, dtype), _to(sw_down, dtype)
+            side = _get_side_stream("shared", priority=-1)
+            ready = torch.cuda.Event()
+            ready.record()
+            with torch.cuda.stream(side):
+                side.wait_event(ready)
+                s_out, s_act, s_pre = _glu_ffn_forward(h, swg, swu, swd, cfg.shared_activation, want_preact=need_grad)
+            shared_done = torch.cuda.Event()
+            shared_done.record(side)
+            shared = (s_out, s_act, s_pre, swg, swu, swd)
+        rb = D * h.element_size()
+        cap_rows = (ep * _EP_STATIC_TOKENS * k + 256 * El + 255) // 256 * 256   # every row of every rank lands here
+        px = p2p.get_exchange(group, h.device, cap_rows * rb)
+        C = px.share_counts(routing.counts)
+        t = px.plan_dev(C, El)
+        cpos, src_c = _compact_send_map(routing, T)
+        tot = t["totals"]
+        dry = _EP_DRY_EXCHANGE   # measurement aid: the row exchanges move nothing and their barriers are skipped
+        if not dry:
+            px.push_rows_dev(h, src_c, k, rb, t["dispatch"], t["dispatch_end"], tot[0:1], T, 0)
+        if need_grad:
+            # the weight-gradient GEMMs sum over whole 64-row blocks: the padding rows of the grouped layout are zeroed
+            # (without a backward pass nothing sums over them, and a GEMM row only depends on its own input row)
+            px.push_rows_dev(None, None, 1, rb, t["padding"], t["padding_end"], tot[2:3], 256 * El, 0,
+                             name="zero_padding")
+        if not dry:
+            px.barrier_dev()
+        Xg = px.region_view(0, cap_rows, D, h.dtype)
+        if need_grad:
+            Xg = px.keep_rows_dev(Xg, tot[3:4], cap_rows)   # saved for backward; the region is overwritten by the next call
+        small = _small_m_kwargs(not need_grad and ep * _EP_STATIC_TOKENS * k < 128 * E, None)
+        if small:
+            small["valid_rows"] = C[:, px.rank * El:(px.rank + 1) * El].sum(0, dtype=torch.int32)
+        act, pre = ops.grouped_gemm_glu(Xg, wu, wu.view(-1, D)[H:], 2 * H, El, t["tile_start"], D, H, cfg.activation,
+                                        want_preact=need_grad, **small)
+        Y = ops.grouped_gemm(act, wd, _lib.B_KMAJOR, El, t["tile_start"], H, D, **small)
+        if not dry:
+            px.push_rows_dev(Y, None, 1, rb, t["combine"], t["combine_end"], tot[1:2], cap_rows, 1)
+            px.barrier_dev()
+        returned = px.region_view(1, T, D, h.dtype)
+        if need_grad:
+            returned = returned.clone()
+        if has_shared:
+            torch.cuda.current_stream().wait_event(shared_done)
+        out = ops.combine_forward(returned, cpos, routing.topk_w, N, k, addend=shared[0] if has_shared else None)
+        aux, z = _loss_tensors(routing, N, E, cfg)
+
+        ctx.set_materialize_grads(False)
+        ctx.cfg = cfg
+        ctx.dims = (N, D, E, El, H, k, ep, cap_rows)
+        ctx.has_shared = has_shared
+        ctx.px = px
+        ctx.in_dtypes = tuple(None if x is None else x.dtype for x in
+                              (hidden_states, gate_weight, w_up, w_down, sw_gate, sw_up, sw_down))
+        ctx.rows_cap = routing.rows_cap
+        if need_grad:
+            tensors = dict(h=h, g=g, wu=wu, wd=wd, topk_w=routing.topk_w, topk_idx=routing.topk_idx,
+                           logits=routing.logits, lse=routing.lse, counts=routing.counts, src_c=src_c, cpos=cpos,
+                           returned=returned, Xg=Xg, act=act, pre=pre, ts_l=t["tile_start"], totals=tot,
+                           dispatch=t["dispatch"], dispatch_end=t["dispatch_end"], combine=t["combine"],
+                           combine_end=t["combine_end"], padding=t["padding"], padding_end=t["padding_end"])
+            if has_shared:
+                tensors.update(s_act=shared[1], s_pre=shared[2], swg=shared[3], swu=shared[4], swd=shared[5])
+            ctx.names = list(tensors)
+            ctx.save_for_backward(*tensors.values())
+        counts = routing.counts
+        dropped = torch.zeros(1, dtype=torch.int32, device=h.device)
+        ctx.mark_non_differentiable(counts, dropped)
+        return out, aux, z, counts, dropped
+
+    @staticmethod
+    def backward(ctx, grad_out, grad_aux, grad_z, _grad_counts, _grad_dropped):
+        cfg = ctx.cfg
+        group = cfg.ep_group
+        N, D, E, El, H, k, ep, cap_rows = ctx.dims
+        px = ctx.px
+        t = dict(zip(ctx.names, ctx.saved_tensors))
+        h, g, wu, wd = t["h"], t["g"], t["wu"], t["wd"]
+        T = N * k
+        rb = D * h.element_size()
+        tot = t["totals"]
+        if grad_out is None:
+            grad_out = torch.zeros(N, D, dtype=h.dtype, device=h.device)
+        go = _to(grad_out, h.dtype)
+        inv_ep = 1.0 / ep
+
+        if ctx.has_shared:
+            side = _get_side_stream("shared", priority=-1)
+            ready = torch.cuda.Event()
+            ready.record()
+            with torch.cuda.stream(side):
+                side.wait_event(ready)
+                s_dx, s_dwg, s_dwu, s_dwd = _glu_ffn_backward(go, h, t["s_act"], t["s_pre"], t["swg"], t["swu"],
+                                                              t["swd"], cfg.shared_activation)
+            shared_done = torch.cuda.Event()
+            shared_done.record(side)
+
+        # routing-weight gradient and weighted output gradient in send order, then the one exchange of the backward
+        # pass on a side stream while the routing backward runs on the main one
+        gYw, gw = ops.combine_backward(go, t["returned"], t["topk_w"], t["src_c"], T, k)
+        a2a = _get_side_stream("a2a")
+        ready2 = torch.cuda.Event()
+        ready2.record()
+        region = _backward_region(group)
+        dry = _EP_DRY_EXCHANGE
+        with torch.cuda.stream(a2a):
+            a2a.wait_event(ready2)
+            if not dry:
+                px.push_rows_dev(gYw, None, 1, rb, t["dispatch"], t["dispatch_end"], tot[0:1], T, region)
+            px.push_rows_dev(None, None, 1, rb, t["padding"], t["padding_end"], tot[2:3], 256 * El, region,
+                             name="zero_padding")
+            if not dry:
+                px.barrier_dev()
+        a2a_done = torch.cuda.Event()
+        a2a_done.record(a2a)
+        gYw.record_stream(a2a)
+        gYg = px.region_view(region, cap_rows, D, h.dtype)
+
+        routing = ops.Routing(t["topk_w"], t["topk_idx"], t["logits"], t["lse"], t["counts"], None, None, None, None,
+                              ctx.rows_cap, k, E)
+        gaux, gz = _loss_grads(routing, N, E, cfg, grad_aux, grad_z)
+        dH, d_gate = ops.route_backward(gw, routing, gaux, gz, h, g, cfg.gating, dH=None)
+
+        torch.cuda.current_stream().wait_event(a2a_done)
+        ts_l = t["ts_l"]
+        d_act = ops.grouped_gemm(gYg, wd, _lib.B_NMAJOR, El, ts_l, D, H)
+        if _OVERLAP:
+            d_wd, gU = _grouped_wgrad(gYg, t["act"], El, ts_l, scale=inv_ep, passenger=(d_act, t["pre"], cfg.activation))
+        else:
+            gU = ops.glu_backward(d_act, t["pre"], ts_l, El, cfg.activation)
+            d_wd = _grouped_wgrad(gYg, t["act"], El, ts_l, scale=inv_ep)
+        d_wu = _grouped_wgrad(gU, t["Xg"], El, ts_l, scale=inv_ep)
+        if cfg.ep_full_input_grad:
+            dXg = ops.grouped_gemm(gU, wu, _lib.B_NMAJOR, El, ts_l, 2 * H, D)
+            if not dry:
+                px.push_rows_dev(dXg, None, 1, rb, t["combine"], t["combine_end"], tot[1:2], cap_rows, 1)
+                px.barrier_dev()
+            d_send = px.region_view(1, T, D, h.dtype)
+            dH = dH + ops.combine_forward(d_send, t["cpos"], None, N, k)
+        s_grads = (None, None, None)
+        if ctx.has_shared:
+            torch.cuda.current_stream().wait_event(shared_done)
+            dH = dH + s_dx
+            s_grads = (s_dwg, s_dwu, s_dwd)
+        dt = ctx.in_dtypes
+
+        def cast(x, i):
+            return None if x is None or dt[i] is None else x.to(dt[i])
+
+        return (cast(dH, 0), cast(d_gate, 1), cast(d_wu, 2), cast(d_wd, 3), cast(s_grads[0], 4), cast(s_grads[1], 5),
+                cast(s_grads[2], 6), None, None)
 
 
 def _wgrad_split_factor(groups, M, n_out):
@@ -980,9 +1105,10 @@ def fused_moe(
     if group is not None:
         sw = shared_expert_weights if shared_expert_weights is not None else (None, None, None)
         lw = latent_weights if latent_weights is not None else (None, None)
-        if (_EP_STATIC_TOKENS is not None and not cfg.wants_grad and lw[0] is None and _EP_TRANSPORT == "p2p"
-                and p2p.available() and E % 4 == 0 and E <= 256 and cfg.input_jitter == 0.0):
-            out, aux, z, counts, dropped = _ep_forward_static(hidden_states, gate_weight, w_up, w_down, sw, cfg, dtype)
+        if (_EP_STATIC_TOKENS is not None and lw[0] is None and _EP_TRANSPORT == "p2p" and p2p.available()
+                and E % 4 == 0 and E <= 256 and torch.distributed.get_world_size(group) <= 16):
+            out, aux, z, counts, dropped = _FusedMoEEPStaticFunction.apply(hidden_states, gate_weight, w_up, w_down,
+                                                                           sw[0], sw[1], sw[2], cfg, dtype)
         else:
             out, aux, z, counts, dropped = _FusedMoEEPFunction.apply(hidden_states, gate_weight, w_up, w_down, sw[0],
                                                                      sw[1], sw[2], lw[0], lw[1], cfg, dtype)

@@ -111,33 +111,38 @@ _status_host = {}
 def poll_status(device=None, enqueue=True):
     """Host-side check of the status word that never waits for the GPU.
 
-    The word is copied to pinned host memory asynchronously (one 4-byte copy on the current stream, queued by an
-    earlier poll); once that copy has finished its value is read here and a non-zero code raises, so a bounded wait
-    that ran out inside one call surfaces at the next call instead of as silent garbage. With `enqueue` a fresh copy
-    is queued for the next poll. Does nothing while the current stream is being captured into a CUDA graph."""
+    The word is copied to pinned host memory asynchronously (a 4-byte copy on a stream of its own, ordered after
+    the work queued so far, so the compute streams never wait for it); once that copy has finished its value is
+    read here and a non-zero code raises, so a bounded wait that ran out inside one call surfaces at a later call
+    instead of as silent garbage. With `enqueue` a fresh copy is queued for the next poll. Does nothing while the
+    current stream is being captured into a CUDA graph."""
     dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
     if torch.cuda.is_current_stream_capturing():
         return
     key = dev.index if dev.index is not None else torch.cuda.current_device()
     entry = _status_host.get(key)
     if entry is None:
-        entry = _status_host[key] = [torch.zeros(1, dtype=torch.int32).pin_memory(), None]
-    host, event = entry
-    if event is not None:
-        if not event.query():
+        entry = _status_host[key] = {"host": torch.zeros(1, dtype=torch.int32).pin_memory(), "pending": False,
+                                     "stream": torch.cuda.Stream(device=dev), "ready": torch.cuda.Event(),
+                                     "done": torch.cuda.Event()}
+    if entry["pending"]:
+        if not entry["done"].query():
             return  # the last copy is still in flight: look again at the next call
-        entry[1] = None
-        code = int(host[0])
+        entry["pending"] = False
+        code = int(entry["host"][0])
         if code != 0:
-            host[0] = 0
+            entry["host"][0] = 0
             status_tensor(dev).zero_()
             raise RuntimeError(f"libffmoe device status {code}: {_lib.error_string(code)} "
                                "(reported by a kernel of an earlier call; its results are not valid)")
     if enqueue:
-        host.copy_(status_tensor(dev), non_blocking=True)
-        ev = torch.cuda.Event()
-        ev.record()
-        entry[1] = ev
+        side = entry["stream"]
+        entry["ready"].record()
+        side.wait_event(entry["ready"])
+        with torch.cuda.stream(side):
+            entry["host"].copy_(status_tensor(dev), non_blocking=True)
+            entry["done"].record(side)
+        entry["pending"] = True
 
 
 def raise_on_status(code, device):
@@ -325,8 +330,8 @@ def grouped_gemm_wgrad(A, B, groups, tile_start, scale=1.0):
 
 def grouped_gemm_wgrad_glu_backward(A, B, groups, tile_start, d_act, preact, activation, scale=1.0):
     """(dW, gU): grouped_gemm_wgrad(A, B) and glu_backward(d_act, preact) in one launch, the second riding on extra
-    warps of the GEMM's CTAs (ffm_grouped_gemm_wgrad_glu_backward). Bit-identical to the two separate calls on the
-    rows in use (the passenger also converts the unused rows past the last group, which nobody reads)."""
+    warps of the GEMM's CTAs (ffm_grouped_gemm_wgrad_glu_backward). Bit-identical to the two separate calls; rows past
+    the last group's tiles are left untouched."""
     lib = _lib.load()
     _req(A, torch.bfloat16, "A")
     _req(B, torch.bfloat16, "B")

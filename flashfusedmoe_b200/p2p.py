@@ -260,6 +260,25 @@ class PeerExchange:
                                                  total_dev.data_ptr(), int(max_rows), bases, n, ops._stream()),
                        "ffm_p2p_push_rows_dev")
 
+    def keep_rows_dev(self, src, rows_dev, max_rows):
+        """A copy of the first *rows_dev rows of `src` ([max_rows, W]; the count is an int64 [1] device tensor) in a
+        new tensor of the same shape; the rows beyond the count stay uninitialised. Costs what the rows in use cost,
+        whatever the worst-case size of the buffer."""
+        lib = _lib.load()
+        dst = torch.empty_like(src)
+        if not hasattr(self, "_self_copy_head"):
+            self._self_copy_head = torch.zeros(2, dtype=torch.int64, device=self.buf.device)
+            self._self_copy_rank = torch.full((1,), self.rank, dtype=torch.int64, device=self.buf.device)
+        rows_dev = rows_dev.reshape(1)
+        seg = torch.cat([self._self_copy_head, rows_dev, self._self_copy_rank])   # {src row 0, dst row 0, rows, self}
+        n = self.world
+        bases = (ctypes.c_void_p * n)(*[dst.data_ptr()] * n)
+        with ops._Launch("keep_rows", 1):
+            _lib.check(lib.ffm_p2p_push_rows_dev(src.data_ptr(), 0, 1, int(src.shape[1] * src.element_size()),
+                                                 seg.data_ptr(), rows_dev.data_ptr(), 1, rows_dev.data_ptr(),
+                                                 int(max_rows), bases, n, ops._stream()), "ffm_p2p_push_rows_dev")
+        return dst
+
     def region_view(self, region, rows, width, dtype):
         lo = FLAG_BYTES + region * self.region_bytes
         nbytes = rows * width * torch.empty(0, dtype=dtype).element_size()

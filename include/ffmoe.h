@@ -198,7 +198,9 @@ int ffm_grouped_gemm_wgrad(const void* A, const void* B, int groups, const int32
  * preact [glu_rows, 2H]) exactly as ffm_glu_backward does, on eight extra warps per CTA that stream through HBM while
  * the tensor pipe works on the weight gradient. The two jobs are independent (in the layer: dW_down needs the output
  * gradient and the activations, the GLU backward needs dAct); a GEMM CTA leaves no room on its SM for another
- * kernel's blocks, so this is how the HBM-bound job overlaps a GEMM. Results are bit-identical to the two calls. */
+ * kernel's blocks, so this is how the HBM-bound job overlaps a GEMM. Results are bit-identical to the two calls.
+ * Only rows below tile_start[groups] * 128 are converted (as ffm_glu_backward does when given tile_start): the row
+ * buffers may be sized for a worst case far above the rows in use. */
 int ffm_grouped_gemm_wgrad_glu_backward(const void* A, const void* B, int groups, const int32_t* tile_start,
                                         int64_t rows_cap, int M, int Nout, float scale, void* dW, const void* dAct,
                                         const void* preact, int64_t glu_rows, int H, int activation, void* gU,

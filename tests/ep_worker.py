@@ -139,6 +139,14 @@ def stacked_layers_case(rank, world, group, dev):
         for i, (a, b) in enumerate(zip(grads_a, grads_b)):
             assert torch.equal(a, b), f"gradient {i} changes when the ranks are kept in step (latent={latent})"
         if not latent:
+            # the host-sync-free path gives the same two-layer results, with and without the ranks kept in step
+            ffm.set_ep_static_forward(4096 + 256 * world)
+            out_c, grads_c = run(latent, full_grad, None)
+            out_d, grads_d = run(latent, full_grad, barrier_between)
+            ffm.set_ep_static_forward(None)
+            assert torch.equal(out_c, out_a) and torch.equal(out_d, out_a)
+            for i, (a, c, d) in enumerate(zip(grads_a, grads_c, grads_d)):
+                assert torch.equal(a, c) and torch.equal(a, d), f"static path: gradient {i} differs"
             ffm.set_ep_group(None)
             ws = [(gw.clone().requires_grad_(), wu.clone().requires_grad_(), wd.clone().requires_grad_())
                   for gw, wu, wd, _ in full]
@@ -279,6 +287,73 @@ def main():
 
     # ---- two layers back to back, skewed load: receive regions are reused across layers -------------------------
     stacked_layers_case(rank, world, group, dev)
+
+    # ---- host-sync-free training step: bit for bit the host-planned path, eager and replayed from a CUDA graph ---
+    if fm._EP_TRANSPORT == "p2p":
+        def train(tokens, grad_out, full):
+            ps = [t.clone().requires_grad_() for t in (tokens, g, wu_l, wd_l, sg, su, sd)]
+            out, m = ffm.fused_moe(ps[0], ps[1], ps[2], ps[3], top_k=k, ep_group=group, aux_loss_coeff=0.01,
+                                   z_loss_coeff=0.001, shared_expert_weights=tuple(ps[4:]), ep_full_input_grad=full,
+                                   return_metrics=True)
+            ((out.float() * grad_out.float()).sum() + m["aux_loss"] + m["z_loss"]).backward()
+            return [out.detach(), m["tokens_per_expert"]] + [p.grad for p in ps]
+
+        bound = 384 + 64 * world
+        for full in (False, True):
+            want = train(h, go, full)
+            ffm.set_ep_static_forward(bound)
+            got = [train(h, go, full) for _ in range(2)]
+            ffm.set_ep_static_forward(None)
+            ops.check_status()
+            for run in got:
+                for i, (a_, b_) in enumerate(zip(run, want)):
+                    assert torch.equal(a_, b_), f"static training differs from the host-planned path (tensor {i}, full={full})"
+        # one captured step, replayed on other tokens
+        ffm.set_ep_static_forward(bound)
+        statics = [t.clone().requires_grad_() for t in (h, g, wu_l, wd_l, sg, su, sd)]
+        go_static = go.clone()
+        cell = {}
+
+        def captured_step():
+            for p in statics:
+                p.grad = None
+            out, _ = ffm.fused_moe(statics[0], statics[1], statics[2], statics[3], top_k=k, ep_group=group,
+                                   shared_expert_weights=tuple(statics[4:]), ep_full_input_grad=True)
+            (out.float() * go_static.float()).sum().backward()
+            cell["out"] = out.detach()
+
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                captured_step()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        dist.barrier()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            captured_step()
+        torch.manual_seed(700 + rank)
+        h2 = torch.randn(N, D).bfloat16().to(dev)
+        go2 = torch.randn(N, D).bfloat16().to(dev)
+        for tok, gr in ((h, go), (h2, go2), (h, go)):
+            with torch.no_grad():
+                statics[0].copy_(tok)
+                go_static.copy_(gr)
+            graph.replay()
+            torch.cuda.synchronize()
+            ffm.set_ep_static_forward(None)
+            ps = [t.clone().requires_grad_() for t in (tok, g, wu_l, wd_l, sg, su, sd)]
+            out_e, _ = ffm.fused_moe(ps[0], ps[1], ps[2], ps[3], top_k=k, ep_group=group,
+                                     shared_expert_weights=tuple(ps[4:]), ep_full_input_grad=True)
+            (out_e.float() * gr.float()).sum().backward()
+            ffm.set_ep_static_forward(bound)
+            assert torch.equal(cell["out"], out_e), "replayed training step: output"
+            for a_, b_ in zip(statics, ps):
+                assert torch.equal(a_.grad, b_.grad), "replayed training step: gradient"
+        ops.check_status()
+        ffm.set_ep_static_forward(None)
+        del graph
 
     # ---- host-sync-free forward (inference), eager and replayed from a CUDA graph ---------------------------------
     if fm._EP_TRANSPORT == "p2p":

@@ -473,7 +473,8 @@ def test_push_rows_gathers_scatters_and_zeroes_locally():
                                              ([2048] * 8, 1024, 2048, 2048)])
 def test_wgrad_with_glu_backward_passenger(counts, M, Nout, H, activation):
     """The weight-gradient GEMM that carries the GLU backward on extra warps equals the two separate kernels bit for
-    bit, for both jobs (the passenger's rows are independent of the GEMM's groups)."""
+    bit, for both jobs. The passenger converts the rows below the end of the last group's tiles and leaves the rest
+    of a (possibly much larger, worst-case sized) buffer alone."""
     torch.manual_seed(M + H)
     A, ts, row_expert, rows_cap = _grouped_case(counts, M)
     E = len(counts)
@@ -486,4 +487,14 @@ def test_wgrad_with_glu_backward_passenger(counts, M, Nout, H, activation):
     dW, gU = ops.grouped_gemm_wgrad_glu_backward(A, Bx, E, ts, d_act, pre, activation, scale=0.5)
     ops.check_status()
     assert torch.equal(dW, dW_ref)
-    assert torch.equal(gU, gU_ref)
+    used = int(ts[-1]) * 128
+    assert used <= rows_cap and torch.equal(gU[:used], gU_ref[:used])
+    sentinel = torch.full_like(gU, 7.0)
+    lib = _lib.load()
+    rc = lib.ffm_grouped_gemm_wgrad_glu_backward(A.data_ptr(), Bx.data_ptr(), E, ts.data_ptr(), rows_cap, M, Nout, 0.5,
+                                                 dW.data_ptr(), d_act.data_ptr(), pre.data_ptr(), d_act.shape[0], H,
+                                                 _lib.ACTIVATION[activation], sentinel.data_ptr(),
+                                                 ops.status_tensor(A.device).data_ptr(), ops._stream())
+    assert rc == 0
+    ops.check_status()
+    assert torch.equal(sentinel[:used], gU_ref[:used]) and (sentinel[used:] == 7.0).all()
