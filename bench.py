@@ -563,6 +563,9 @@ def main():
         graph_note = "not capturable: the host-planned expert-parallel step reads the row counts on the host"
     run_step = graph.replay if graph is not None else step
     graph_used = graph is not None
+    # Capturing executes nothing, so ranks leave it at different times; a rank that replayed at once would sit in the
+    # exchange's bounded flag wait while its peer is still capturing. Nobody replays before everybody has captured.
+    fence()
 
     def timed_region(fn):
         fence()
@@ -581,8 +584,8 @@ def main():
 
     for _ in range(2):
         run_step()
+    fence()   # (every rank: the fence holds a collective)
     if sampler:
-        fence()
         sampler.begin()
     launches0 = ops.launch_count
     ms, step_series = timed_region(run_step)
@@ -685,6 +688,7 @@ def main():
             e2e_graph = None
             graph_note = f"end-to-end capture failed: {type(exc).__name__}: {str(exc)[:200]}"
             torch.cuda.synchronize()
+    fence()
 
     def e2e_run(steps):
         losses_read = []
@@ -737,7 +741,10 @@ def main():
     # ---- sustained: the same step for at least two seconds (the board settles at its power cap) -------------------
     sus_ms, sus_steps, sus_clocks = 0.0, 0, None
     if not args.no_extras:
-        sus_steps = max(K, int(2600.0 / max(step_ms[K // 2], 1e-3)) + 1)
+        med = torch.tensor([step_ms[K // 2]], device=device, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(med, op=dist.ReduceOp.MAX)   # every rank must run the same number of steps
+        sus_steps = max(K, int(2600.0 / max(float(med[0]), 1e-3)) + 1)
         sampler2 = ClockSampler(local_rank) if rank == 0 else None
         if sampler2:
             sampler2.start()

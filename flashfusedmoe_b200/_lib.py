@@ -49,6 +49,11 @@ SIGNATURES = {
     "ffm_grouped_gemm_wgrad_glu_backward": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int, c_int, c_float,
                                                     c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p,
                                                     c_void_p, c_void_p]),
+    "ffm_quantize_rows_e4m3": (c_int, [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p]),
+    "ffm_grouped_gemm_glu_fp8": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int, c_int,
+                                         c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
+    "ffm_grouped_gemm_fp8": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int, c_int,
+                                     c_void_p, c_int, c_void_p, c_void_p]),
     "ffm_combine_forward": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p,
                                     c_void_p]),
     "ffm_combine_backward": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p,

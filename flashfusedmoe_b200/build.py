@@ -12,7 +12,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libffmoe.so")
 PTXAS_LOG = os.path.join(HERE, "libffmoe.ptxas.txt")
-SOURCES = ["ffm_api.cu", "ffm_route.cu", "ffm_rows.cu", "ffm_route_bwd.cu", "ffm_gemm_sm100.cu", "ffm_p2p.cu"]
+SOURCES = ["ffm_api.cu", "ffm_route.cu", "ffm_rows.cu", "ffm_route_bwd.cu", "ffm_gemm_sm100.cu", "ffm_p2p.cu", "ffm_fp8.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "--use_fast_math", "-Xptxas", "-v",

@@ -120,6 +120,16 @@ struct GemmParams {
   int pz_h;
   int pz_act;
 };
+// FP8 = 1 (e4m3 operands, never with a passenger): the epilogue multiplies the fp32 accumulator by
+// a_scale[row] * b_scale[B row of the column]. The two pointers travel in the passenger's pointer fields: growing this
+// struct changes ptxas's register allocation of the bf16 GLU-epilogue instantiation (234 -> 185 registers, a much
+// slower kernel), so the struct keeps its size.
+__device__ __forceinline__ const float* fp8_a_scale(const GemmParams& p) {
+  return reinterpret_cast<const float*>(p.pz_dact);
+}
+__device__ __forceinline__ const float* fp8_b_scale(const GemmParams& p) {
+  return reinterpret_cast<const float*>(p.pz_pre);
+}
 
 struct Ctrl {
   unsigned long long full_bar[MAX_STAGES];
@@ -269,6 +279,36 @@ __device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t adesc, 
       : "memory");
 }
 
+// The same with 8-bit floating-point operands (e4m3 / e5m2 chosen by the instruction descriptor), 32 K elements per
+// instruction, fp32 accumulation.
+__device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                        uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_f8_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// Instruction descriptor for kind::f8f6f4 with e4m3 A and B (format code 0) and fp32 accumulation, K-major operands.
+__host__ __device__ constexpr uint32_t make_idesc_e4m3(int m, int n) {
+  return (1u << 4) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+}
+
 // Arrive (once the pair's MMAs issued so far have completed) on one mbarrier given by shared::cluster address.
 __device__ __forceinline__ void umma_commit_pair(uint32_t cluster_bar) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar)
@@ -329,7 +369,8 @@ __device__ __forceinline__ void passenger_glu_backward(const GemmParams& p, long
   }
 }
 
-template <int A_MN, int B_MN, int EPI, int GROUPK, int CTA2, int PASS = 0>
+// FP8 = 1: A and B hold e4m3 bytes, K-major only; a stage row is still 128 bytes, i.e. 128 K elements per block.
+template <int A_MN, int B_MN, int EPI, int GROUPK, int CTA2, int PASS = 0, int FP8 = 0>
 __global__ void __launch_bounds__(GEMM_THREADS + PASS * PASSENGER_THREADS, 1)
 ffm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB0,
                 const __grid_constant__ CUtensorMap tmB1, const __grid_constant__ CUtensorMap tmC,
@@ -427,7 +468,7 @@ ffm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           const uint32_t a_dst = smem_base + stage * STAGE_BYTES;
           const uint32_t b_dst = a_dst + A_STAGE_BYTES;
           if (leader) mbar_expect_tx(full_local, STAGE_BYTES * (CTA2 ? 2 : 1));
-          const int k0 = kb * BK;
+          const int k0 = kb * (FP8 ? 2 * BK : BK);
           // A tile: this CTA's 128 rows
           if (A_MN) {
             const int krow = t.k_row0 + k0;
@@ -479,7 +520,8 @@ ffm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   } else if (warp == 1) {
     // ================= MMA issuer (with CTA2: only in the even CTA of the pair) =================
     if (lane == 0 && leader) {
-      constexpr uint32_t idesc = make_idesc_bf16(CTA2 ? 256 : 128, BN, A_MN, B_MN);
+      constexpr uint32_t idesc = FP8 ? make_idesc_e4m3(CTA2 ? 256 : 128, BN)
+                                     : make_idesc_bf16(CTA2 ? 256 : 128, BN, A_MN, B_MN);
       TileWalker<GROUPK, CTA2> walker(p, ctrl->tile_start, rank);
       TileCoord t;
       int stage = 0;
@@ -507,10 +549,17 @@ ffm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                                         : make_smem_desc_sw128(a_src + kk * 32, 16, 1024);
             const uint64_t bdesc = B_MN ? make_smem_desc_sw128(b_src + kk * 2048, 8192, 1024)
                                         : make_smem_desc_sw128(b_src + kk * 32, 16, 1024);
-            if (CTA2) {
-              umma_bf16_pair(d_tmem, adesc, bdesc, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+            const uint32_t accumulate = (kb > 0 || kk > 0) ? 1u : 0u;
+            if (FP8) {
+              if (CTA2) {
+                umma_f8_pair(d_tmem, adesc, bdesc, idesc, accumulate);
+              } else {
+                umma_f8(d_tmem, adesc, bdesc, idesc, accumulate);
+              }
+            } else if (CTA2) {
+              umma_bf16_pair(d_tmem, adesc, bdesc, idesc, accumulate);
             } else {
-              umma_bf16(d_tmem, adesc, bdesc, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+              umma_bf16(d_tmem, adesc, bdesc, idesc, accumulate);
             }
           }
           // free the stage (in both CTAs) once these MMAs retire
@@ -598,8 +647,21 @@ ffm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
               uint32_t pg[16], pu[16], pa[16];
 #pragma unroll
               for (int i = 0; i < 16; ++i) {
-                pg[i] = pack_bf16x2(__uint_as_float(g[c & 1][2 * i]), __uint_as_float(g[c & 1][2 * i + 1]));
-                pu[i] = pack_bf16x2(__uint_as_float(u[c & 1][2 * i]), __uint_as_float(u[c & 1][2 * i + 1]));
+                float g0 = __uint_as_float(g[c & 1][2 * i]), g1 = __uint_as_float(g[c & 1][2 * i + 1]);
+                float u0 = __uint_as_float(u[c & 1][2 * i]), u1 = __uint_as_float(u[c & 1][2 * i + 1]);
+                if (FP8) {
+                  // de-quantise: row scale of A times the scale of the weight row that made this column
+                  const float* sg = fp8_b_scale(p) + t.group * p.b_group_rows + h0 + c * 32;
+                  const float2 wg = __ldg(reinterpret_cast<const float2*>(sg) + i);
+                  const float2 wu = __ldg(reinterpret_cast<const float2*>(sg + p.glu_h) + i);
+                  const float sa = __ldg(fp8_a_scale(p) + row0 + lane);
+                  g0 *= sa * wg.x;
+                  g1 *= sa * wg.y;
+                  u0 *= sa * wu.x;
+                  u1 *= sa * wu.y;
+                }
+                pg[i] = pack_bf16x2(g0, g1);
+                pu[i] = pack_bf16x2(u0, u1);
                 const float2 gf = unpack_bf16x2(pg[i]);
                 const float2 uf = unpack_bf16x2(pu[i]);
                 pa[i] = pack_bf16x2(glu_fwd(p.act, gf.x, uf.x), glu_fwd(p.act, gf.y, uf.y));
@@ -652,8 +714,16 @@ ffm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
               uint32_t o[16];
 #pragma unroll
               for (int i = 0; i < 16; ++i) {
-                o[i] = have_acc ? pack_bf16x2(__uint_as_float(v[c & 1][2 * i]) * scale,
-                                              __uint_as_float(v[c & 1][2 * i + 1]) * scale)
+                float s0 = scale, s1 = scale;
+                if (FP8) {
+                  const float* sb = fp8_b_scale(p) + t.group * p.b_group_rows + n0 + c * 32;
+                  const float2 w2 = __ldg(reinterpret_cast<const float2*>(sb) + i);
+                  const float sa = __ldg(fp8_a_scale(p) + row0 + lane);
+                  s0 *= sa * w2.x;
+                  s1 *= sa * w2.y;
+                }
+                o[i] = have_acc ? pack_bf16x2(__uint_as_float(v[c & 1][2 * i]) * s0,
+                                              __uint_as_float(v[c & 1][2 * i + 1]) * s1)
                                 : 0u;
               }
 #pragma unroll
@@ -731,17 +801,20 @@ EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
-// 2-D bf16 tensor map over a row-major [rows, cols] matrix, 128-byte swizzle, zero fill out of bounds.
-int make_map_2d(CUtensorMap* map, const void* base, long long rows, long long cols, int box_cols, int box_rows) {
+// 2-D tensor map over a row-major [rows, cols] matrix of bf16 (elt_bytes 2) or bytes (elt_bytes 1: e4m3 operands),
+// 128-byte swizzle, zero fill out of bounds.
+int make_map_2d(CUtensorMap* map, const void* base, long long rows, long long cols, int box_cols, int box_rows,
+                int elt_bytes = 2) {
   EncodeTiledFn fn = get_encode_fn();
   if (fn == nullptr) return FFM_ERR_NO_DRIVER;
   if (rows <= 0 || cols <= 0) return FFM_ERR_BAD_ARG;
-  if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0 || (cols * 2) % 16 != 0) return FFM_ERR_UNSUPPORTED;
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0 || (cols * elt_bytes) % 16 != 0) return FFM_ERR_UNSUPPORTED;
   cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
-  cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * 2};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * elt_bytes};
   cuuint32_t box[2] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows)};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+  CUresult r = fn(map, elt_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                  const_cast<void*>(base), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? FFM_OK : FFM_ERR_LAUNCH;
@@ -785,11 +858,11 @@ bool use_cta_pair() {
   return g_cta_pair != 0;
 }
 
-template <int A_MN, int B_MN, int EPI, int GROUPK, int CTA2, int PASS = 0>
+template <int A_MN, int B_MN, int EPI, int GROUPK, int CTA2, int PASS = 0, int FP8 = 0>
 int launch_gemm_shape(const CUtensorMap& tmA, const CUtensorMap& tmB0, const CUtensorMap& tmB1, const CUtensorMap& tmC,
                       const CUtensorMap& tmC2, const GemmParams& p, long long max_units, cudaStream_t stream) {
   static int max_ctas = 0;  // persistent grid size, found once per instantiation
-  auto kernel = ffm_gemm_kernel<A_MN, B_MN, EPI, GROUPK, CTA2, PASS>;
+  auto kernel = ffm_gemm_kernel<A_MN, B_MN, EPI, GROUPK, CTA2, PASS, FP8>;
   constexpr int threads = GEMM_THREADS + PASS * PASSENGER_THREADS;
   constexpr int smem_bytes = Shape<CTA2, EPI>::SMEM_BYTES;
   if (max_ctas == 0) {
@@ -844,17 +917,17 @@ int launch_gemm_shape(const CUtensorMap& tmA, const CUtensorMap& tmB0, const CUt
 
 // max_m_tiles: upper bound on the 128-row tiles of M the walker can see (per group for grouped-K);
 // multiplier: tiles per M tile (N blocks, times groups for grouped-K).
-template <int A_MN, int B_MN, int EPI, int GROUPK, int PASS = 0>
+template <int A_MN, int B_MN, int EPI, int GROUPK, int PASS = 0, int FP8 = 0>
 int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB0, const CUtensorMap& tmB1, const CUtensorMap& tmC,
                 const CUtensorMap& tmC2, const GemmParams& p, long long max_m_tiles, long long multiplier,
                 cudaStream_t stream, int tile_rows = 0) {
   const bool pair = tile_rows == 256 ? true : (tile_rows == 128 ? false : use_cta_pair());
   if (pair) {
-    return launch_gemm_shape<A_MN, B_MN, EPI, GROUPK, 1, PASS>(tmA, tmB0, tmB1, tmC, tmC2, p,
-                                                         ((max_m_tiles + 1) / 2) * multiplier, stream);
+    return launch_gemm_shape<A_MN, B_MN, EPI, GROUPK, 1, PASS, FP8>(tmA, tmB0, tmB1, tmC, tmC2, p,
+                                                                    ((max_m_tiles + 1) / 2) * multiplier, stream);
   }
-  return launch_gemm_shape<A_MN, B_MN, EPI, GROUPK, 0, PASS>(tmA, tmB0, tmB1, tmC, tmC2, p, max_m_tiles * multiplier,
-                                                              stream);
+  return launch_gemm_shape<A_MN, B_MN, EPI, GROUPK, 0, PASS, FP8>(tmA, tmB0, tmB1, tmC, tmC2, p,
+                                                                   max_m_tiles * multiplier, stream);
 }
 
 }  // namespace
@@ -1016,4 +1089,84 @@ extern "C" int ffm_grouped_gemm_wgrad_glu_backward(const void* A, const void* B,
   return launch_gemm<1, 1, EPI_PLAIN, 1, 1>(tmA, tmB, tmB, tmC, tmC, p, p.m_tiles_per_group,
                                          static_cast<long long>(groups) * p.n_tiles,
                                          static_cast<cudaStream_t>(stream));
+}
+
+// ---- FP8 (e4m3) forward projections: quantised operands, fp32 accumulation, scales applied in the epilogue ----
+
+extern "C" int ffm_grouped_gemm_glu_fp8(const void* Aq, const float* a_scale, const void* Wq, const float* w_scale,
+                                        int groups, const int32_t* tile_start, int64_t rows, int K, int H,
+                                        int activation, void* act, void* preact, int tile_rows, int32_t* status,
+                                        ffm_stream_t stream) {
+  if (!Aq || !a_scale || !Wq || !w_scale || !act || !status) return FFM_ERR_BAD_ARG;
+  if (groups < 1 || groups > MAX_GROUPS || rows < 0 || K <= 0 || H <= 0) return FFM_ERR_BAD_ARG;
+  if (activation < 0 || activation > 3) return FFM_ERR_BAD_ARG;
+  if (tile_start == nullptr && groups != 1) return FFM_ERR_BAD_ARG;
+  if (tile_rows != 0 && tile_rows != 128 && tile_rows != 256) return FFM_ERR_BAD_ARG;
+  if (K % 128 != 0 || H % 64 != 0) return FFM_ERR_UNSUPPORTED;
+  if (rows == 0) return FFM_OK;
+  CUtensorMap tmA, tmB0, tmB1, tmC, tmC2;
+  int rc;
+  if ((rc = make_map_2d(&tmA, Aq, rows, K, 128, 128, 1)) != FFM_OK) return rc;
+  const long long wrows = static_cast<long long>(groups) * 2 * H;
+  const uint8_t* w = static_cast<const uint8_t*>(Wq);
+  // gate rows of every group through one map, up rows (H rows further down) through a second one
+  if ((rc = make_map_2d(&tmB0, w, wrows - H, K, 128, 128, 1)) != FFM_OK) return rc;
+  if ((rc = make_map_2d(&tmB1, w + static_cast<long long>(H) * K, wrows - H, K, 128, 128, 1)) != FFM_OK) return rc;
+  if ((rc = make_out_map(&tmC, act, 1, rows, H)) != FFM_OK) return rc;
+  if (preact != nullptr) {
+    if ((rc = make_out_map(&tmC2, preact, 1, rows, 2LL * H)) != FFM_OK) return rc;
+  } else {
+    tmC2 = tmC;
+  }
+  GemmParams p = {};
+  p.tile_start = tile_start;
+  p.groups = groups;
+  p.dense_m_tiles = static_cast<int>((rows + BM - 1) / BM);
+  p.n_cols = H;
+  p.k_blocks = K / 128;
+  p.b_group_rows = 2LL * H;
+  p.b1_row_offset = 0;
+  p.has_c2 = preact != nullptr ? 1 : 0;
+  p.glu_h = H;
+  p.scale = 1.0f;
+  p.act = activation;
+  p.n_tiles = (H + 127) / 128;
+  p.status = status;
+  p.wait_cycles = g_wait_cycles;
+  p.pz_dact = reinterpret_cast<const bf16*>(a_scale);   // see fp8_a_scale / fp8_b_scale
+  p.pz_pre = reinterpret_cast<const bf16*>(w_scale);
+  return launch_gemm<0, 0, EPI_GLU, 0, 0, 1>(tmA, tmB0, tmB1, tmC, tmC2, p, (rows + BM - 1) / BM, p.n_tiles,
+                                             static_cast<cudaStream_t>(stream), tile_rows);
+}
+
+extern "C" int ffm_grouped_gemm_fp8(const void* Aq, const float* a_scale, const void* Bq, const float* b_scale,
+                                    int groups, const int32_t* tile_start, int64_t rows, int K, int Nout, void* out,
+                                    int tile_rows, int32_t* status, ffm_stream_t stream) {
+  if (!Aq || !a_scale || !Bq || !b_scale || !out || !status) return FFM_ERR_BAD_ARG;
+  if (groups < 1 || groups > MAX_GROUPS || rows < 0 || K <= 0 || Nout <= 0) return FFM_ERR_BAD_ARG;
+  if (tile_start == nullptr && groups != 1) return FFM_ERR_BAD_ARG;
+  if (tile_rows != 0 && tile_rows != 128 && tile_rows != 256) return FFM_ERR_BAD_ARG;
+  if (K % 128 != 0 || Nout % 32 != 0) return FFM_ERR_UNSUPPORTED;
+  if (rows == 0) return FFM_OK;
+  CUtensorMap tmA, tmB, tmC;
+  int rc;
+  if ((rc = make_map_2d(&tmA, Aq, rows, K, 128, 128, 1)) != FFM_OK) return rc;
+  if ((rc = make_map_2d(&tmB, Bq, static_cast<long long>(groups) * Nout, K, 128, 128, 1)) != FFM_OK) return rc;
+  if ((rc = make_out_map(&tmC, out, 1, rows, Nout)) != FFM_OK) return rc;
+  GemmParams p = {};
+  p.tile_start = tile_start;
+  p.groups = groups;
+  p.dense_m_tiles = static_cast<int>((rows + BM - 1) / BM);
+  p.n_cols = Nout;
+  p.k_blocks = K / 128;
+  p.scale = 1.0f;
+  p.n_tiles = (Nout + BN - 1) / BN;
+  p.status = status;
+  p.wait_cycles = g_wait_cycles;
+  p.b_group_rows = Nout;
+  p.b1_row_offset = 128;
+  p.pz_dact = reinterpret_cast<const bf16*>(a_scale);   // see fp8_a_scale / fp8_b_scale
+  p.pz_pre = reinterpret_cast<const bf16*>(b_scale);
+  return launch_gemm<0, 0, EPI_PLAIN, 0, 0, 1>(tmA, tmB, tmB, tmC, tmC, p, (rows + BM - 1) / BM, p.n_tiles,
+                                               static_cast<cudaStream_t>(stream), tile_rows);
 }

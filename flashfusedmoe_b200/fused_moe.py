@@ -56,6 +56,53 @@ _OVERLAP = os.environ.get("FFM_OVERLAP", "1") != "0"
 _EP_DIRECT = os.environ.get("FFM_EP_DIRECT", "1") != "0"
 
 
+# Expert GEMM precision of the single-GPU forward pass: "bf16", or "fp8" = e4m3 operands (activations quantised per
+# row, weights per output channel, fp32 accumulation, bf16 outputs) for the up- and down-projection. Opt-in; the
+# backward pass always runs in bf16 on the saved bf16 tensors.
+_EXPERT_GEMM = "bf16"
+_fp8_weight_cache = {}
+
+
+def set_expert_gemm_precision(mode):
+    """"bf16" (default) or "fp8": run the routed experts' forward projections on e4m3 operands (single-GPU path,
+    d_model and ffn_dim / 2 multiples of 128). Returns the previous mode."""
+    global _EXPERT_GEMM
+    if mode not in ("bf16", "fp8"):
+        raise ValueError(f"unknown expert GEMM precision: {mode}")
+    old, _EXPERT_GEMM = _EXPERT_GEMM, mode
+    return old
+
+
+def _quantized_weight(w):
+    """e4m3 copy of a weight tensor [E, N, K] with one scale per (expert, output channel); cached until the tensor is
+    modified in place (its version counter moves) or replaced."""
+    key = (w.data_ptr(), tuple(w.shape))
+    hit = _fp8_weight_cache.get(key)
+    if hit is not None and hit[0] == w._version:
+        return hit[1], hit[2]
+    q, sc = ops.quantize_rows_e4m3(w.reshape(-1, w.shape[-1]))
+    if len(_fp8_weight_cache) > 64:
+        _fp8_weight_cache.clear()
+    _fp8_weight_cache[key] = (w._version, q, sc)
+    return q, sc
+
+
+def _expert_ffn_forward(Xg, wu, wd, E, tile_start, D, H, activation, keep, small):
+    """Up-projection + GLU and down-projection of the routed experts over grouped rows: (act, pre, Y)."""
+    if _EXPERT_GEMM == "fp8" and D % 128 == 0 and H % 128 == 0 and not small:
+        xq, xs = ops.quantize_rows_e4m3(Xg)
+        wuq, wus = _quantized_weight(wu)
+        act, pre = ops.grouped_gemm_glu_fp8(xq, xs, wuq, wus, E, tile_start, D, H, activation, want_preact=keep)
+        aq, as_ = ops.quantize_rows_e4m3(act)
+        wdq, wds = _quantized_weight(wd)
+        Y = ops.grouped_gemm_fp8(aq, as_, wdq, wds, E, tile_start, H, D)
+        return act, pre, Y
+    act, pre = ops.grouped_gemm_glu(Xg, wu, wu.view(-1, D)[H:], 2 * H, E, tile_start, D, H, activation,
+                                    want_preact=keep, **small)
+    Y = ops.grouped_gemm(act, wd, _lib.B_KMAJOR, E, tile_start, H, D, **small)
+    return act, pre, Y
+
+
 def set_ep_dry_exchange(enable):
     """Benchmark switch: skip the payload of the expert-parallel exchanges (results are then meaningless)."""
     global _EP_DRY_EXCHANGE
@@ -315,9 +362,7 @@ class _FusedMoEFunction(torch.autograd.Function):
         keep = need_grad and not cfg.recompute
         # inference with few rows per expert (decode): one CTA per 128-row tile and no work on tiles without rows
         small = _small_m_kwargs(not need_grad and cfg.capacity is None and N * k < 128 * E, routing.counts)
-        act, pre = ops.grouped_gemm_glu(Xg, wu, wu.view(-1, D)[H:], 2 * H, E, routing.tile_start, D, H,
-                                        cfg.activation, want_preact=keep, **small)
-        Y = ops.grouped_gemm(act, wd, _lib.B_KMAJOR, E, routing.tile_start, H, D, **small)
+        act, pre, Y = _expert_ffn_forward(Xg, wu, wd, E, routing.tile_start, D, H, cfg.activation, keep, small)
         if add is not None and cfg.addend_ready is not None:
             torch.cuda.current_stream().wait_event(cfg.addend_ready)
             add.record_stream(torch.cuda.current_stream())

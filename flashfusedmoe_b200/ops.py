@@ -351,6 +351,47 @@ def grouped_gemm_wgrad_glu_backward(A, B, groups, tile_start, d_act, preact, act
     return out, gU
 
 
+def quantize_rows_e4m3(x):
+    """(q uint8 [rows, K], scale f32 [rows padded to 128]): row-wise e4m3 quantisation, x = q * scale[row]."""
+    lib = _lib.load()
+    _req(x, torch.bfloat16, "x")
+    rows, K = x.shape
+    q = torch.empty(rows, K, dtype=torch.uint8, device=x.device)
+    scale = torch.ones((rows + 127) // 128 * 128, dtype=torch.float32, device=x.device)
+    with _Launch("quantize_rows", 1):
+        _lib.check(lib.ffm_quantize_rows_e4m3(_ptr(x), rows, K, _ptr(q), _ptr(scale), _stream()),
+                   "ffm_quantize_rows_e4m3")
+    return q, scale
+
+
+def grouped_gemm_glu_fp8(Aq, a_scale, Wq, w_scale, groups, tile_start, K, H, activation, want_preact=True,
+                         tile_rows=0):
+    """grouped_gemm_glu on e4m3 operands: Aq uint8 [rows, K], Wq uint8 [groups, 2H, K], scales as quantize_rows_e4m3
+    returns them. Outputs bf16."""
+    lib = _lib.load()
+    rows = Aq.shape[0]
+    act = torch.empty(rows, H, dtype=torch.bfloat16, device=Aq.device)
+    pre = torch.empty(rows, 2 * H, dtype=torch.bfloat16, device=Aq.device) if want_preact else None
+    with _Launch("gemm_up_glu", 1):
+        rc = lib.ffm_grouped_gemm_glu_fp8(_ptr(Aq), _ptr(a_scale), _ptr(Wq), _ptr(w_scale), groups, _ptr(tile_start),
+                                          rows, K, H, _lib.ACTIVATION[activation], _ptr(act), _ptr(pre),
+                                          int(tile_rows), _ptr(status_tensor(Aq.device)), _stream())
+    _lib.check(rc, "ffm_grouped_gemm_glu_fp8")
+    return act, pre
+
+
+def grouped_gemm_fp8(Aq, a_scale, Bq, b_scale, groups, tile_start, K, n_out, tile_rows=0):
+    """grouped_gemm (K-major B) on e4m3 operands: Bq uint8 [groups, n_out, K]. Output bf16 [rows, n_out]."""
+    lib = _lib.load()
+    rows = Aq.shape[0]
+    out = torch.empty(rows, n_out, dtype=torch.bfloat16, device=Aq.device)
+    with _Launch("gemm", 1):
+        rc = lib.ffm_grouped_gemm_fp8(_ptr(Aq), _ptr(a_scale), _ptr(Bq), _ptr(b_scale), groups, _ptr(tile_start), rows,
+                                      K, n_out, _ptr(out), int(tile_rows), _ptr(status_tensor(Aq.device)), _stream())
+    _lib.check(rc, "ffm_grouped_gemm_fp8")
+    return out
+
+
 def combine_forward(Y, pos, w, N, top_k, addend=None):
     lib = _lib.load()
     _req(Y, torch.bfloat16, "Y")

@@ -291,6 +291,12 @@ def get_exchange(group, device, region_bytes):
     key = (id(group), torch.device(device).index)
     px = _exchanges.get(key)
     if px is None or px.region_bytes < region_bytes:
-        px = PeerExchange(group, device, region_bytes)
+        old = px
+        px = PeerExchange(group, device, region_bytes)   # (its constructor ends with a group barrier)
         _exchanges[key] = px
+        if old is not None:
+            # Let go of the smaller buffer: every rank has left its last exchange on it (it took part in the new
+            # buffer's rendezvous and barrier after it), and tensors that still view it keep its storage alive.
+            old.buf = old.hdl = None
+            old.ptrs = []
     return px

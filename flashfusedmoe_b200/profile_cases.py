@@ -4,6 +4,7 @@
 
 Cases: route_forward permute combine_forward combine_backward glu_backward route_backward
        gemm_up_glu gemm_down gemm_dact gemm_dx gemm_wgrad_down gemm_wgrad_up
+       quantize_rows gemm_up_glu_fp8 gemm_down_fp8
 Shape: D = 1024, H = 2048, top_k = 2 (E * rows_per_expert routed rows). Every case touches far more than the
 126 MB L2 and holds about 1 GB on the device. Prints the CUDA-event time per launch.
 """
@@ -56,6 +57,17 @@ def main():
         "gemm_wgrad_down": (lambda: ops.grouped_gemm_wgrad(X, act, E, ts), 2.0 * T * D * H),
         "gemm_wgrad_up": (lambda: ops.grouped_gemm_wgrad(gU, X, E, ts), 4.0 * T * D * H),
     }
+    if a.case in ("quantize_rows", "gemm_up_glu_fp8", "gemm_down_fp8"):
+        xq, xs = ops.quantize_rows_e4m3(X)
+        wuq, wus = ops.quantize_rows_e4m3(Wu.view(-1, D))
+        aq, as_ = ops.quantize_rows_e4m3(act)
+        wdq, wds = ops.quantize_rows_e4m3(Wd.view(-1, H))
+        cases.update({
+            "quantize_rows": (lambda: ops.quantize_rows_e4m3(act), 3.0 * rows * H),
+            "gemm_up_glu_fp8": (lambda: ops.grouped_gemm_glu_fp8(xq, xs, wuq, wus, E, ts, D, H, "swiglu"),
+                                4.0 * T * D * H),
+            "gemm_down_fp8": (lambda: ops.grouped_gemm_fp8(aq, as_, wdq, wds, E, ts, H, D), 2.0 * T * D * H),
+        })
     fn, work = cases[a.case]
     fn()
     torch.cuda.synchronize()

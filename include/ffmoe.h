@@ -260,6 +260,27 @@ int ffm_compact_positions(const int32_t* pos, const int32_t* topk_idx, const int
                           ffm_stream_t stream);
 
 /* -------------------------------------------------------------------------------------------------
+ * FP8 (e4m3) forward projections, opt-in. The reference has FP8 only for the dense nn.Linear layers of its training
+ * benchmark (benchmarks/train_multigpu.py:283-336, torch._scaled_mm); this is the same idea for the routed experts'
+ * up- and down-projection.
+ * ffm_quantize_rows_e4m3: q[r, :] = e4m3(x[r, :] / scale[r]), scale[r] = max |x[r, :]| / 448 (1 for an all-zero row);
+ *   x bf16 [rows, K], K % 16 == 0; q uint8 [rows, K]; scale f32 [rows]. Used for activations (a scale per row) and for
+ *   weights viewed as [groups * N, K] (a scale per output channel).
+ * ffm_grouped_gemm_glu_fp8 / ffm_grouped_gemm_fp8: ffm_grouped_gemm_glu / ffm_grouped_gemm (K-major B) on quantised
+ *   operands with tcgen05.mma.kind::f8f6f4, fp32 accumulation, out[r, n] = acc * a_scale[r] * b_scale[row of B];
+ *   K % 128 == 0. Wq is [groups, 2H, K] (gate rows, then up rows) with w_scale [groups * 2H]; Bq is [groups, Nout, K]
+ *   with b_scale [groups * Nout]. a_scale must hold an entry for every row up to the next multiple of 128.
+ *   Outputs are bf16 as in the bf16 entry points.
+ * ------------------------------------------------------------------------------------------------- */
+int ffm_quantize_rows_e4m3(const void* x, int64_t rows, int K, void* q, float* scale, ffm_stream_t stream);
+int ffm_grouped_gemm_glu_fp8(const void* Aq, const float* a_scale, const void* Wq, const float* w_scale, int groups,
+                             const int32_t* tile_start, int64_t rows, int K, int H, int activation, void* act,
+                             void* preact, int tile_rows, int32_t* status, ffm_stream_t stream);
+int ffm_grouped_gemm_fp8(const void* Aq, const float* a_scale, const void* Bq, const float* b_scale, int groups,
+                         const int32_t* tile_start, int64_t rows, int K, int Nout, void* out, int tile_rows,
+                         int32_t* status, ffm_stream_t stream);
+
+/* -------------------------------------------------------------------------------------------------
  * Expert-parallel exchange over NVLink with plain peer stores. Replaces the c10d all_to_all_single calls of the
  * reference's dispatcher (expert_parallel.py:253-258, :290-292; fused_moe.py:901-910).
  * The caller owns the receive buffers and the flag arrays, which must be mapped on every GPU of the group

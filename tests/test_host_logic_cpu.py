@@ -255,3 +255,25 @@ def test_small_helpers_without_a_gpu():
     assert fm._EP_STATIC_TOKENS == 128
     fm.set_ep_static_forward(None)
     assert fm._EP_STATIC_TOKENS is None
+
+
+def test_backward_exchanges_alternate_receive_regions():
+    """Consecutive backward exchanges of a group must not share a receive region (rows are read in place after the
+    barrier while a faster peer may already push the next layer's rows): regions 2 and 3 in turn, per group."""
+    import sys
+    fm = sys.modules["flashfusedmoe_b200.fused_moe"]
+    from flashfusedmoe_b200 import p2p
+    assert p2p.NUM_REGIONS == 4
+    g1, g2 = object(), object()
+    seq1 = [fm._backward_region(g1) for _ in range(5)]
+    seq2 = [fm._backward_region(g2) for _ in range(2)]
+    assert seq1 == [2, 3, 2, 3, 2] and seq2 == [2, 3]
+    assert all(r < p2p.NUM_REGIONS for r in seq1)
+
+
+def test_expert_gemm_precision_switch():
+    import flashfusedmoe_b200 as ffm
+    assert ffm.set_expert_gemm_precision("fp8") == "bf16"
+    assert ffm.set_expert_gemm_precision("bf16") == "fp8"
+    with pytest.raises(ValueError):
+        ffm.set_expert_gemm_precision("fp4")
