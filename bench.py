@@ -776,6 +776,9 @@ def main():
     if not args.no_extras:
         del layer, step, x, go, x_bufs, x_in, graph, e2e_graph, run_step
         loss_cell[0] = None
+        if ep_static:
+            _ffm.set_ep_static_forward(None)   # the other configurations choose their own mode (worst-case buffers
+                                               # declared for 16,384 tokens would be far too large for them)
         torch.cuda.empty_cache()
         other = other_configs(group, rank, world, device)
 

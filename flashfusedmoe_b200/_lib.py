@@ -49,7 +49,10 @@ SIGNATURES = {
     "ffm_grouped_gemm_wgrad_glu_backward": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int, c_int, c_float,
                                                     c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p,
                                                     c_void_p, c_void_p]),
+    "ffm_grouped_gemm_dact_glu_backward": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int, c_int, c_int,
+                                                   c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
     "ffm_quantize_rows_e4m3": (c_int, [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p]),
+    "ffm_quantize_rows_given_scale_e4m3": (c_int, [c_void_p, c_int64, c_int, c_int64, c_void_p, c_void_p, c_void_p]),
     "ffm_grouped_gemm_glu_fp8": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int, c_int,
                                          c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
     "ffm_grouped_gemm_fp8": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int, c_int,

@@ -58,7 +58,7 @@ constexpr int SMEM_CTRL_BYTES = 2048;
 constexpr int MAX_STAGES = 6;
 constexpr int SMEM_LIMIT = 232448;  // 227 KiB of dynamic shared memory per CTA
 
-enum { EPI_PLAIN = 0, EPI_GLU = 1 };
+enum { EPI_PLAIN = 0, EPI_GLU = 1, EPI_GLUBWD = 2 };
 
 // Ring depth against staging depth for CTA pairs. Measured at 8 x 4096 rows, D 1024, H 2048: every split from 4 to
 // 6 stages runs within 3 % of the others alone (the GEMMs sit at the board's power limit, not at a pipeline limit).
@@ -78,14 +78,18 @@ enum { EPI_PLAIN = 0, EPI_GLU = 1 };
 // Shared-memory budget per tile shape and epilogue: ring stages against staging boxes per epilogue warp.
 //   CTA pair, plain: 6 stages x 32 KiB + 2 boxes    CTA pair, GLU: 5 stages x 32 KiB + 3 boxes
 //   one CTA,  plain: 4 stages x 48 KiB + 2 boxes    one CTA,  GLU: 3 stages x 48 KiB + 3 boxes
-// A GLU step stores three boxes (activation, gate, up) as one bulk group; a plain step stores one box.
+//   GLU backward epilogue (EPI_GLUBWD): 5 (one CTA: 3) stages + 2 x 2 boxes
+// A GLU step stores three boxes (activation, gate, up) as one bulk group; a plain step stores one box; a GLU backward
+// step stores two (gate gradient, up gradient).
 template <int CTA2, int EPI>
 struct Shape {
-  static constexpr int STAGES = EPI == EPI_GLU ? (CTA2 ? FFM_TUNE_PG_STAGES : 3) : (CTA2 ? FFM_TUNE_PP_STAGES : 4);
+  static constexpr int STAGES = EPI == EPI_GLU      ? (CTA2 ? FFM_TUNE_PG_STAGES : 3)
+                                : EPI == EPI_GLUBWD ? (CTA2 ? 5 : 3)
+                                                    : (CTA2 ? FFM_TUNE_PP_STAGES : 4);
   static constexpr int B_STAGE_BYTES = (CTA2 ? 128 : 256) * BK * 2;
   static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
   static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
-  static constexpr int BOXES_PER_STEP = EPI == EPI_GLU ? 3 : 1;
+  static constexpr int BOXES_PER_STEP = EPI == EPI_GLU ? 3 : (EPI == EPI_GLUBWD ? 2 : 1);
   static constexpr int STEPS_BUFFERED = EPI == EPI_GLU ? (CTA2 ? FFM_TUNE_PG_STEPS : 1) : (CTA2 ? FFM_TUNE_PP_STEPS : 2);
   static constexpr int STG_WARP_BYTES = BOXES_PER_STEP * STEPS_BUFFERED * BOX_BYTES;
   static constexpr int STG_BYTES = EPI_WARPS * STG_WARP_BYTES;
@@ -121,7 +125,7 @@ struct GemmParams {
   int pz_act;
 };
 // FP8 = 1 (e4m3 operands, never with a passenger): the epilogue multiplies the fp32 accumulator by
-// a_scale[row] * b_scale[B row of the column]. The two pointers travel in the passenger's pointer fields: growing this
+// a_scale[row] * b_scale[group]. The two pointers travel in the passenger's pointer fields: growing this
 // struct changes ptxas's register allocation of the bf16 GLU-epilogue instantiation (234 -> 185 registers, a much
 // slower kernel), so the struct keeps its size.
 __device__ __forceinline__ const float* fp8_a_scale(const GemmParams& p) {
@@ -246,6 +250,11 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const void* map, 
 __device__ __forceinline__ void tma_store_3d(const void* map, uint32_t src, int c0, int c1, int c2) {
   asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(map), "r"(src),
                "r"(c0), "r"(c1), "r"(c2)
+               : "memory");
+}
+// Ask the TMA unit to bring one box of a tensor into L2 (nothing lands in shared memory, nothing to wait for).
+__device__ __forceinline__ void tma_prefetch_l2_2d(const void* map, int c0, int c1) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map), "r"(c0), "r"(c1)
                : "memory");
 }
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
@@ -459,6 +468,12 @@ ffm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       bool ok = true;
       while (ok && walker.next(t)) {
         const int m0 = t.m_tile * BM;
+        if (EPI == EPI_GLUBWD) {
+          // the epilogue of this tile reads the matching pre-activations (gate and up columns) straight from global
+          // memory: pull them into L2 now, a whole main loop ahead (tmC2 maps them with a 256 x 128 box)
+          tma_prefetch_l2_2d(&tmC2, t.n_block * BN, m0);
+          tma_prefetch_l2_2d(&tmC2, p.pz_h + t.n_block * BN, m0);
+        }
         for (int kb = 0; kb < t.k_blocks && ok; ++kb) {
           ok = mbar_wait_bounded(smem_u32(&ctrl->empty_bar[stage]), phase ^ 1u, abort_flag, p.status,
                                  FFM_STATUS_WAIT_PRODUCER, p.wait_cycles);
@@ -620,6 +635,9 @@ ffm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         tc_fence_after();
       }
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+      // FP8: de-quantisation factor of this lane's row in this tile = scale of the row of A x scale of the group's B
+      float fp8_scale = 1.0f;
+      if (FP8) fp8_scale = __ldg(fp8_a_scale(p) + row0 + lane) * __ldg(fp8_b_scale(p) + t.group);
 
       if (EPI == EPI_GLU) {
         // two steps of 64 GLU columns, each two 32-column chunks of gate and up; the TMEM loads of chunk c + 1 fly
@@ -650,15 +668,10 @@ ffm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 float g0 = __uint_as_float(g[c & 1][2 * i]), g1 = __uint_as_float(g[c & 1][2 * i + 1]);
                 float u0 = __uint_as_float(u[c & 1][2 * i]), u1 = __uint_as_float(u[c & 1][2 * i + 1]);
                 if (FP8) {
-                  // de-quantise: row scale of A times the scale of the weight row that made this column
-                  const float* sg = fp8_b_scale(p) + t.group * p.b_group_rows + h0 + c * 32;
-                  const float2 wg = __ldg(reinterpret_cast<const float2*>(sg) + i);
-                  const float2 wu = __ldg(reinterpret_cast<const float2*>(sg + p.glu_h) + i);
-                  const float sa = __ldg(fp8_a_scale(p) + row0 + lane);
-                  g0 *= sa * wg.x;
-                  g1 *= sa * wg.y;
-                  u0 *= sa * wu.x;
-                  u1 *= sa * wu.y;
+                  g0 *= fp8_scale;
+                  g1 *= fp8_scale;
+                  u0 *= fp8_scale;
+                  u1 *= fp8_scale;
                 }
                 pg[i] = pack_bf16x2(g0, g1);
                 pu[i] = pack_bf16x2(u0, u1);
@@ -691,10 +704,91 @@ ffm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             }
           }
         }
+      } else if (EPI == EPI_GLUBWD) {
+        // The accumulator is dAct (gradient of the GLU output). Rounded to bf16 as the stand-alone dAct GEMM would
+        // store it, it goes through the GLU backward with the saved pre-activations of the same rows and columns, and
+        // the gate and up gradients leave as two boxes per 64-column step: dAct itself never touches memory.
+        // Each lane owns a row; its 32 gate and 32 up pre-activations of a chunk are four 16-byte loads each, issued
+        // one chunk ahead beside the TMEM load. They hit L2: the producer warp prefetched the tile's pre-activations
+        // when its main loop started.
+        const int n0 = t.n_block * BN;
+        const int Hh = p.pz_h;
+        const float scale = p.scale;
+        const long long r = static_cast<long long>(row0) + lane;
+        const bool row_ok = r < p.pz_rows;
+        const bf16* prow = p.pz_pre + r * 2 * Hh;
+        uint32_t v[2][32];
+        uint4 qg[2][4], qu[2][4];
+        tmem_ld_32x32(taddr, v[0]);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const bool okc = row_ok && n0 < p.n_cols;
+          qg[0][q] = okc ? __ldg(reinterpret_cast<const uint4*>(prow + n0) + q) : make_uint4(0, 0, 0, 0);
+          qu[0][q] = okc ? __ldg(reinterpret_cast<const uint4*>(prow + Hh + n0) + q) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int c = 0; c < BN / 32; ++c) {
+          tmem_ld_wait();
+          if (c + 1 < BN / 32) {
+            tmem_ld_32x32(taddr + (c + 1) * 32, v[(c + 1) & 1]);
+            const int cn = n0 + (c + 1) * 32;
+            const bool okc = row_ok && cn < p.n_cols;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              qg[(c + 1) & 1][q] = okc ? __ldg(reinterpret_cast<const uint4*>(prow + cn) + q) : make_uint4(0, 0, 0, 0);
+              qu[(c + 1) & 1][q] =
+                  okc ? __ldg(reinterpret_cast<const uint4*>(prow + Hh + cn) + q) : make_uint4(0, 0, 0, 0);
+            }
+          }
+          const int col = n0 + (c >> 1) * 64;  // first column of this step's boxes
+          if (col < p.n_cols) {
+            const uint32_t buf = stg + step_slot * STEP_BYTES;
+            if ((c & 1) == 0) {
+              if (lane == 0) bulk_wait_read<S::STEPS_BUFFERED - 1>();
+              __syncwarp();
+            }
+            if (n0 + c * 32 < p.n_cols) {
+              uint32_t og[16], ou[16];
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const uint32_t gw4[4] = {qg[c & 1][q].x, qg[c & 1][q].y, qg[c & 1][q].z, qg[c & 1][q].w};
+                const uint32_t uw4[4] = {qu[c & 1][q].x, qu[c & 1][q].y, qu[c & 1][q].z, qu[c & 1][q].w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const int i = q * 4 + j;
+                  const float2 da = unpack_bf16x2(pack_bf16x2(__uint_as_float(v[c & 1][2 * i]) * scale,
+                                                              __uint_as_float(v[c & 1][2 * i + 1]) * scale));
+                  const float2 gf = unpack_bf16x2(gw4[j]);
+                  const float2 uf = unpack_bf16x2(uw4[j]);
+                  const float2 r0 = glu_bwd(p.pz_act, da.x, gf.x, uf.x);
+                  const float2 r1 = glu_bwd(p.pz_act, da.y, gf.y, uf.y);
+                  og[i] = pack_bf16x2(r0.x, r1.x);
+                  ou[i] = pack_bf16x2(r0.y, r1.y);
+                }
+              }
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const uint32_t o = box_offset(lane, (c & 1) * 4 + q);
+                st_shared_v4(buf + o, og[4 * q], og[4 * q + 1], og[4 * q + 2], og[4 * q + 3]);
+                st_shared_v4(buf + BOX_BYTES + o, ou[4 * q], ou[4 * q + 1], ou[4 * q + 2], ou[4 * q + 3]);
+              }
+            }
+            if (c & 1) {
+              fence_proxy_async();
+              __syncwarp();
+              if (lane == 0) {
+                tma_store_3d(&tmC, buf, col, row0, 0);
+                tma_store_3d(&tmC, buf + BOX_BYTES, Hh + col, row0, 0);
+                bulk_commit();
+              }
+              if (++step_slot == S::STEPS_BUFFERED) step_slot = 0;
+            }
+          }
+        }
       } else {
         // four steps of 64 columns (one box each), two 32-column chunks per step, TMEM loads one chunk ahead
         const int n0 = t.n_block * BN;
-        const float scale = p.scale;
+        const float scale = FP8 ? p.scale * fp8_scale : p.scale;
         uint32_t v[2][32];
         if (have_acc) tmem_ld_32x32(taddr, v[0]);
 #pragma unroll
@@ -714,16 +808,8 @@ ffm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
               uint32_t o[16];
 #pragma unroll
               for (int i = 0; i < 16; ++i) {
-                float s0 = scale, s1 = scale;
-                if (FP8) {
-                  const float* sb = fp8_b_scale(p) + t.group * p.b_group_rows + n0 + c * 32;
-                  const float2 w2 = __ldg(reinterpret_cast<const float2*>(sb) + i);
-                  const float sa = __ldg(fp8_a_scale(p) + row0 + lane);
-                  s0 *= sa * w2.x;
-                  s1 *= sa * w2.y;
-                }
-                o[i] = have_acc ? pack_bf16x2(__uint_as_float(v[c & 1][2 * i]) * s0,
-                                              __uint_as_float(v[c & 1][2 * i + 1]) * s1)
+                o[i] = have_acc ? pack_bf16x2(__uint_as_float(v[c & 1][2 * i]) * scale,
+                                              __uint_as_float(v[c & 1][2 * i + 1]) * scale)
                                 : 0u;
               }
 #pragma unroll
@@ -816,6 +902,22 @@ int make_map_2d(CUtensorMap* map, const void* base, long long rows, long long co
   CUresult r = fn(map, elt_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
                   const_cast<void*>(base), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? FFM_OK : FFM_ERR_LAUNCH;
+}
+
+// 2-D bf16 map used only for L2 prefetches (cp.async.bulk.prefetch.tensor): box {256 columns, 128 rows}, no swizzle.
+int make_prefetch_map(CUtensorMap* map, const void* base, long long rows, long long cols) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return FFM_ERR_NO_DRIVER;
+  if (rows <= 0 || cols <= 0) return FFM_ERR_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0 || (cols * 2) % 16 != 0) return FFM_ERR_UNSUPPORTED;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * 2};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(cols < 256 ? cols : 256), static_cast<cuuint32_t>(rows < 128 ? rows : 128)};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? FFM_OK : FFM_ERR_LAUNCH;
 }
@@ -1169,4 +1271,41 @@ extern "C" int ffm_grouped_gemm_fp8(const void* Aq, const float* a_scale, const 
   p.pz_pre = reinterpret_cast<const bf16*>(b_scale);
   return launch_gemm<0, 0, EPI_PLAIN, 0, 0, 1>(tmA, tmB, tmB, tmC, tmC, p, (rows + BM - 1) / BM, p.n_tiles,
                                                static_cast<cudaStream_t>(stream), tile_rows);
+}
+
+// ---- dAct GEMM with the GLU backward in its epilogue ----
+
+extern "C" int ffm_grouped_gemm_dact_glu_backward(const void* gY, const void* Wd, int groups, const int32_t* tile_start,
+                                                  int64_t rows, int K, int H, int activation, const void* preact,
+                                                  void* gU, int tile_rows, int32_t* status, ffm_stream_t stream) {
+  if (!gY || !Wd || !preact || !gU || !status) return FFM_ERR_BAD_ARG;
+  if (groups < 1 || groups > MAX_GROUPS || rows < 0 || K <= 0 || H <= 0) return FFM_ERR_BAD_ARG;
+  if (activation < 0 || activation > 3) return FFM_ERR_BAD_ARG;
+  if (tile_start == nullptr && groups != 1) return FFM_ERR_BAD_ARG;
+  if (tile_rows != 0 && tile_rows != 128 && tile_rows != 256) return FFM_ERR_BAD_ARG;
+  if (K % 64 != 0 || H % 64 != 0) return FFM_ERR_UNSUPPORTED;
+  if (rows == 0) return FFM_OK;
+  CUtensorMap tmA, tmB, tmC, tmP;
+  int rc;
+  if ((rc = make_map_2d(&tmA, gY, rows, K, 64, 128)) != FFM_OK) return rc;
+  if ((rc = make_map_2d(&tmB, Wd, static_cast<long long>(groups) * K, H, 64, 64)) != FFM_OK) return rc;
+  if ((rc = make_out_map(&tmC, gU, 1, rows, 2LL * H)) != FFM_OK) return rc;
+  if ((rc = make_prefetch_map(&tmP, preact, rows, 2LL * H)) != FFM_OK) return rc;
+  GemmParams p = {};
+  p.tile_start = tile_start;
+  p.groups = groups;
+  p.dense_m_tiles = static_cast<int>((rows + BM - 1) / BM);
+  p.n_cols = H;
+  p.k_blocks = K / BK;
+  p.scale = 1.0f;
+  p.n_tiles = (H + BN - 1) / BN;
+  p.status = status;
+  p.wait_cycles = g_wait_cycles;
+  p.b_group_rows = K;
+  p.pz_pre = static_cast<const bf16*>(preact);
+  p.pz_rows = rows;
+  p.pz_h = H;
+  p.pz_act = activation;
+  return launch_gemm<0, 1, EPI_GLUBWD, 0>(tmA, tmB, tmB, tmC, tmP, p, (rows + BM - 1) / BM, p.n_tiles,
+                                          static_cast<cudaStream_t>(stream), tile_rows);
 }

@@ -51,13 +51,17 @@ _EP_DRY_EXCHANGE = False
 # (they fill the gaps and tails between GEMMs), the GLU backward as a passenger inside the dW_down GEMM's CTAs.
 # FFM_OVERLAP=0 keeps one stream and separate kernels.
 _OVERLAP = os.environ.get("FFM_OVERLAP", "1") != "0"
+# FFM_FUSED_GLU_BACKWARD=1: GLU backward inside the dAct GEMM's epilogue (one launch, dAct never written, bit-identical)
+# instead of riding as a passenger in the dW_down GEMM. Off by default: measured slower (the epilogue's row-per-lane
+# loads of the pre-activations touch 32 cache lines per instruction); it saves the dAct buffer where memory is tight.
+_FUSED_GLU_BWD = os.environ.get("FFM_FUSED_GLU_BACKWARD", "0") != "0"
 # Peer-store transport only: move rows straight into the receivers' grouped layout (FFM_EP_DIRECT=0 keeps the
 # contiguous-range exchange with a permute on either side, the layout the NCCL transport also uses).
 _EP_DIRECT = os.environ.get("FFM_EP_DIRECT", "1") != "0"
 
 
 # Expert GEMM precision of the single-GPU forward pass: "bf16", or "fp8" = e4m3 operands (activations quantised per
-# row, weights per output channel, fp32 accumulation, bf16 outputs) for the up- and down-projection. Opt-in; the
+# row, weights per expert, fp32 accumulation, bf16 outputs) for the up- and down-projection. Opt-in; the
 # backward pass always runs in bf16 on the saved bf16 tensors.
 _EXPERT_GEMM = "bf16"
 _fp8_weight_cache = {}
@@ -74,13 +78,13 @@ def set_expert_gemm_precision(mode):
 
 
 def _quantized_weight(w):
-    """e4m3 copy of a weight tensor [E, N, K] with one scale per (expert, output channel); cached until the tensor is
-    modified in place (its version counter moves) or replaced."""
+    """e4m3 copy of a weight tensor [E, N, K] with one scale per expert; cached until the tensor is modified in place
+    (its version counter moves) or replaced."""
     key = (w.data_ptr(), tuple(w.shape))
     hit = _fp8_weight_cache.get(key)
     if hit is not None and hit[0] == w._version:
         return hit[1], hit[2]
-    q, sc = ops.quantize_rows_e4m3(w.reshape(-1, w.shape[-1]))
+    q, sc = ops.quantize_weight_e4m3(w)
     if len(_fp8_weight_cache) > 64:
         _fp8_weight_cache.clear()
     _fp8_weight_cache[key] = (w._version, q, sc)
@@ -253,14 +257,20 @@ def _glu_ffn_forward(x, w_gate, w_up, w_down, activation, want_preact):
 
 def _glu_ffn_backward(go, x, act, pre, w_gate, w_up, w_down, activation):
     Hs, D = w_gate.shape
-    d_act = ops.grouped_gemm(go, w_down, _lib.B_NMAJOR, 1, None, D, Hs)
+    fused = _FUSED_GLU_BWD and Hs % 64 == 0 and D % 64 == 0
+    if fused:
+        gU = ops.grouped_gemm_dact_glu_backward(go, w_down, 1, None, D, Hs, pre, activation)
+    else:
+        d_act = ops.grouped_gemm(go, w_down, _lib.B_NMAJOR, 1, None, D, Hs)
     ts = _dense_ts(x.shape[0], x.device)
     # [D, Hs] has few output tiles (32 CTA-pair tiles at D = 1024, Hs = 2048 for 74 pairs): split the token
     # dimension in two halves, each accumulated in fp32, and add the two bf16 results
     tiles = (x.shape[0] + 127) // 128
     split = 2 if tiles >= 64 and (D // 256) * ((Hs + 255) // 256) <= 40 else 1
     ts_down = _dense_ts(x.shape[0], x.device, split=2) if split == 2 else ts
-    if _OVERLAP:
+    if fused:
+        d_wdown = ops.grouped_gemm_wgrad(go, act, split, ts_down)
+    elif _OVERLAP:
         # the GLU backward rides on extra warps of the dW_down GEMM, which does not depend on it
         d_wdown, gU = ops.grouped_gemm_wgrad_glu_backward(go, act, split, ts_down, d_act, pre, activation)
     else:
@@ -421,9 +431,14 @@ class _FusedMoEFunction(torch.autograd.Function):
                 dH_route, d_gate = ops.route_backward(gw, routing, gaux, gz, h, g, cfg.gating, dH=None)
                 route_done = torch.cuda.Event()
                 route_done.record(route)
-            d_act = ops.grouped_gemm(gYw, wd, _lib.B_NMAJOR, E, tile_start, D, H)
-            # the GLU backward rides on extra warps of the dW_down GEMM (one launch)
-            d_wd, gU = ops.grouped_gemm_wgrad_glu_backward(gYw, act, E, tile_start, d_act, pre, cfg.activation)
+            if _FUSED_GLU_BWD and H % 64 == 0 and D % 64 == 0:
+                # dAct GEMM with the GLU backward in its epilogue, then the plain dW_down GEMM
+                gU = ops.grouped_gemm_dact_glu_backward(gYw, wd, E, tile_start, D, H, pre, cfg.activation)
+                d_wd = ops.grouped_gemm_wgrad(gYw, act, E, tile_start)
+            else:
+                d_act = ops.grouped_gemm(gYw, wd, _lib.B_NMAJOR, E, tile_start, D, H)
+                # the GLU backward rides on extra warps of the dW_down GEMM (one launch)
+                d_wd, gU = ops.grouped_gemm_wgrad_glu_backward(gYw, act, E, tile_start, d_act, pre, cfg.activation)
             dXg = ops.grouped_gemm(gU, wu, _lib.B_NMAJOR, E, tile_start, 2 * H, D)
             dx_done = torch.cuda.Event()
             dx_done.record(main)
@@ -712,12 +727,17 @@ class _FusedMoEEPStaticFunction(torch.autograd.Function):
 
         torch.cuda.current_stream().wait_event(a2a_done)
         ts_l = t["ts_l"]
-        d_act = ops.grouped_gemm(gYg, wd, _lib.B_NMAJOR, El, ts_l, D, H)
-        if _OVERLAP:
-            d_wd, gU = _grouped_wgrad(gYg, t["act"], El, ts_l, scale=inv_ep, passenger=(d_act, t["pre"], cfg.activation))
-        else:
-            gU = ops.glu_backward(d_act, t["pre"], ts_l, El, cfg.activation)
+        if _FUSED_GLU_BWD and H % 64 == 0 and D % 64 == 0:
+            gU = ops.grouped_gemm_dact_glu_backward(gYg, wd, El, ts_l, D, H, t["pre"], cfg.activation)
             d_wd = _grouped_wgrad(gYg, t["act"], El, ts_l, scale=inv_ep)
+        else:
+            d_act = ops.grouped_gemm(gYg, wd, _lib.B_NMAJOR, El, ts_l, D, H)
+            if _OVERLAP:
+                d_wd, gU = _grouped_wgrad(gYg, t["act"], El, ts_l, scale=inv_ep,
+                                          passenger=(d_act, t["pre"], cfg.activation))
+            else:
+                gU = ops.glu_backward(d_act, t["pre"], ts_l, El, cfg.activation)
+                d_wd = _grouped_wgrad(gYg, t["act"], El, ts_l, scale=inv_ep)
         d_wu = _grouped_wgrad(gU, t["Xg"], El, ts_l, scale=inv_ep)
         if cfg.ep_full_input_grad:
             dXg = ops.grouped_gemm(gU, wu, _lib.B_NMAJOR, El, ts_l, 2 * H, D)
@@ -1002,7 +1022,10 @@ class _FusedMoEEPFunction(torch.autograd.Function):
                          if M > 0 else recv_grad.new_empty(0, D))
         if M > 0:
             gYg = recv_grad if direct else ops.permute_rows(recv_grad, t["src_l"], rows_l, 1)
-            if _OVERLAP:
+            if _FUSED_GLU_BWD and H % 64 == 0 and D % 64 == 0:
+                gU = ops.grouped_gemm_dact_glu_backward(gYg, wd, El, t["ts_l"], D, H, t["pre"], cfg.activation)
+                d_wd = _grouped_wgrad(gYg, t["act"], El, t["ts_l"], scale=inv_ep)
+            elif _OVERLAP:
                 # the down-projection weight gradient does not need the GLU backward: it carries it as a passenger
                 d_act = ops.grouped_gemm(gYg, wd, _lib.B_NMAJOR, El, t["ts_l"], D, H)
                 d_wd, gU = _grouped_wgrad(gYg, t["act"], El, t["ts_l"], scale=inv_ep,

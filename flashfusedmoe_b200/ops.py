@@ -351,6 +351,23 @@ def grouped_gemm_wgrad_glu_backward(A, B, groups, tile_start, d_act, preact, act
     return out, gU
 
 
+def grouped_gemm_dact_glu_backward(gY, Wd, groups, tile_start, K, H, preact, activation):
+    """gU [rows, 2H]: the dAct GEMM (gY Wd, N-major B) with the GLU backward in its epilogue; equals
+    glu_backward(grouped_gemm(gY, Wd, B_NMAJOR, ...), preact) bit for bit without writing dAct."""
+    lib = _lib.load()
+    _req(gY, torch.bfloat16, "gY")
+    _req(Wd, torch.bfloat16, "Wd")
+    _req(preact, torch.bfloat16, "preact")
+    rows = gY.shape[0]
+    gU = torch.empty(rows, 2 * H, dtype=torch.bfloat16, device=gY.device)
+    with _Launch("gemm", 1):
+        rc = lib.ffm_grouped_gemm_dact_glu_backward(_ptr(gY), _ptr(Wd), groups, _ptr(tile_start), rows, K, H,
+                                                    _lib.ACTIVATION[activation], _ptr(preact), _ptr(gU), 0,
+                                                    _ptr(status_tensor(gY.device)), _stream())
+    _lib.check(rc, "ffm_grouped_gemm_dact_glu_backward")
+    return gU
+
+
 def quantize_rows_e4m3(x):
     """(q uint8 [rows, K], scale f32 [rows padded to 128]): row-wise e4m3 quantisation, x = q * scale[row]."""
     lib = _lib.load()
@@ -364,10 +381,26 @@ def quantize_rows_e4m3(x):
     return q, scale
 
 
+def quantize_weight_e4m3(w):
+    """(q uint8 [E, N, K], scale f32 [E]): e4m3 copy of a weight tensor with one scale per expert,
+    w[e] = q[e] * scale[e]. Two launches: per-row maxima, then the conversion with the per-expert scale."""
+    lib = _lib.load()
+    _req(w, torch.bfloat16, "w")
+    E, N, K = w.shape
+    flat = w.reshape(E * N, K)
+    _, row_scale = quantize_rows_e4m3(flat)
+    scale = row_scale[:E * N].view(E, N).amax(dim=1).contiguous()
+    q = torch.empty(E, N, K, dtype=torch.uint8, device=w.device)
+    with _Launch("quantize_rows", 1):
+        _lib.check(lib.ffm_quantize_rows_given_scale_e4m3(_ptr(flat), E * N, K, N, _ptr(scale), _ptr(q), _stream()),
+                   "ffm_quantize_rows_given_scale_e4m3")
+    return q, scale
+
+
 def grouped_gemm_glu_fp8(Aq, a_scale, Wq, w_scale, groups, tile_start, K, H, activation, want_preact=True,
                          tile_rows=0):
-    """grouped_gemm_glu on e4m3 operands: Aq uint8 [rows, K], Wq uint8 [groups, 2H, K], scales as quantize_rows_e4m3
-    returns them. Outputs bf16."""
+    """grouped_gemm_glu on e4m3 operands: Aq uint8 [rows, K] with a scale per row (quantize_rows_e4m3), Wq uint8
+    [groups, 2H, K] with a scale per group (quantize_weight_e4m3). Outputs bf16."""
     lib = _lib.load()
     rows = Aq.shape[0]
     act = torch.empty(rows, H, dtype=torch.bfloat16, device=Aq.device)

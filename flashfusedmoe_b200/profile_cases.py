@@ -59,9 +59,9 @@ def main():
     }
     if a.case in ("quantize_rows", "gemm_up_glu_fp8", "gemm_down_fp8"):
         xq, xs = ops.quantize_rows_e4m3(X)
-        wuq, wus = ops.quantize_rows_e4m3(Wu.view(-1, D))
+        wuq, wus = ops.quantize_weight_e4m3(Wu)
         aq, as_ = ops.quantize_rows_e4m3(act)
-        wdq, wds = ops.quantize_rows_e4m3(Wd.view(-1, H))
+        wdq, wds = ops.quantize_weight_e4m3(Wd)
         cases.update({
             "quantize_rows": (lambda: ops.quantize_rows_e4m3(act), 3.0 * rows * H),
             "gemm_up_glu_fp8": (lambda: ops.grouped_gemm_glu_fp8(xq, xs, wuq, wus, E, ts, D, H, "swiglu"),

@@ -194,6 +194,14 @@ int ffm_grouped_gemm(const void* A, const void* B, int b_major, int groups, cons
                      int tile_rows, int32_t* status, ffm_stream_t stream);
 int ffm_grouped_gemm_wgrad(const void* A, const void* B, int groups, const int32_t* tile_start, int64_t rows_cap,
                            int M, int Nout, float scale, void* dW, int32_t* status, ffm_stream_t stream);
+/* dAct GEMM with the GLU backward fused into its epilogue: gU [rows, 2H] = GLU backward of (gY Wd (N-major B, as
+ * ffm_grouped_gemm with FFM_B_NMAJOR) rounded to bf16, preact [rows, 2H]), bit-identical to ffm_grouped_gemm followed by
+ * ffm_glu_backward (reference: the bmm + activation_backward pair, fused_moe.py:520-531); dAct is never written. The
+ * tile's pre-activations are prefetched into L2 when its main loop starts and read by the epilogue warps directly.
+ * gY [rows, K], Wd [groups, K, H], K % 64 == 0, H % 64 == 0. */
+int ffm_grouped_gemm_dact_glu_backward(const void* gY, const void* Wd, int groups, const int32_t* tile_start,
+                                       int64_t rows, int K, int H, int activation, const void* preact, void* gU,
+                                       int tile_rows, int32_t* status, ffm_stream_t stream);
 /* ffm_grouped_gemm_wgrad with a passenger: the same launch also computes gU = GLU backward of (dAct [glu_rows, H],
  * preact [glu_rows, 2H]) exactly as ffm_glu_backward does, on eight extra warps per CTA that stream through HBM while
  * the tensor pipe works on the weight gradient. The two jobs are independent (in the layer: dW_down needs the output
@@ -264,15 +272,18 @@ int ffm_compact_positions(const int32_t* pos, const int32_t* topk_idx, const int
  * benchmark (benchmarks/train_multigpu.py:283-336, torch._scaled_mm); this is the same idea for the routed experts'
  * up- and down-projection.
  * ffm_quantize_rows_e4m3: q[r, :] = e4m3(x[r, :] / scale[r]), scale[r] = max |x[r, :]| / 448 (1 for an all-zero row);
- *   x bf16 [rows, K], K % 16 == 0; q uint8 [rows, K]; scale f32 [rows]. Used for activations (a scale per row) and for
- *   weights viewed as [groups * N, K] (a scale per output channel).
+ *   x bf16 [rows, K], K % 16 == 0; q uint8 [rows, K]; scale f32 [rows]. Used for activations (a scale per row).
+ * ffm_quantize_rows_given_scale_e4m3: the same conversion with the caller's scales, row r uses
+ *   scale_in[r / rows_per_scale]: weights viewed as [groups * N, K] with one scale per group (per expert).
  * ffm_grouped_gemm_glu_fp8 / ffm_grouped_gemm_fp8: ffm_grouped_gemm_glu / ffm_grouped_gemm (K-major B) on quantised
- *   operands with tcgen05.mma.kind::f8f6f4, fp32 accumulation, out[r, n] = acc * a_scale[r] * b_scale[row of B];
- *   K % 128 == 0. Wq is [groups, 2H, K] (gate rows, then up rows) with w_scale [groups * 2H]; Bq is [groups, Nout, K]
- *   with b_scale [groups * Nout]. a_scale must hold an entry for every row up to the next multiple of 128.
+ *   operands with tcgen05.mma.kind::f8f6f4, fp32 accumulation, out[r, n] = acc * a_scale[r] * b_scale[group];
+ *   K % 128 == 0. Wq is [groups, 2H, K] (gate rows, then up rows), Bq is [groups, Nout, K], w_scale / b_scale f32
+ *   [groups]. a_scale must hold an entry for every row up to the next multiple of 128.
  *   Outputs are bf16 as in the bf16 entry points.
  * ------------------------------------------------------------------------------------------------- */
 int ffm_quantize_rows_e4m3(const void* x, int64_t rows, int K, void* q, float* scale, ffm_stream_t stream);
+int ffm_quantize_rows_given_scale_e4m3(const void* x, int64_t rows, int K, int64_t rows_per_scale,
+                                       const float* scale_in, void* q, ffm_stream_t stream);
 int ffm_grouped_gemm_glu_fp8(const void* Aq, const float* a_scale, const void* Wq, const float* w_scale, int groups,
                              const int32_t* tile_start, int64_t rows, int K, int H, int activation, void* act,
                              void* preact, int tile_rows, int32_t* status, ffm_stream_t stream);

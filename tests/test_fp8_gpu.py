@@ -4,7 +4,7 @@ Two levels. (1) The kernels against exact arithmetic on the quantised values: th
 e4m3 numbers in fp32, so out = (q_a * s_a) (q_b * s_b)^T computed in fp32 by torch from the same quantised tensors
 is the reference, and only the bf16 rounding of the output separates the two (bound 1e-2). (2) The layer with FP8
 forward projections against the bf16 layer: e4m3 keeps 3 mantissa bits (relative rounding error up to 2^-4 per
-element), so the stated tolerance is max |a - b| / max |b| <= 0.12 and a relative Frobenius error <= 0.06; the
+element), so the stated tolerance is max |a - b| / max |b| <= 0.12 and a relative Frobenius error <= 0.08; the
 routing decisions, which do not go through FP8, stay bit-identical.
 """
 
@@ -55,14 +55,16 @@ def test_fp8_grouped_gemms_match_exact_arithmetic_on_quantised_values(counts, K,
     Wu = (torch.randn(E, 2 * H, K, device=DEV) * 0.05).bfloat16()
     Wd = (torch.randn(E, K, H, device=DEV) * 0.05).bfloat16()
     xq, xs = ops.quantize_rows_e4m3(X)
-    wuq, wus = ops.quantize_rows_e4m3(Wu.view(-1, K))
+    wuq, wus = ops.quantize_weight_e4m3(Wu)
     act, pre = ops.grouped_gemm_glu_fp8(xq, xs, wuq, wus, E, ts, K, H, "swiglu")
     aq, as_ = ops.quantize_rows_e4m3(act)
-    wdq, wds = ops.quantize_rows_e4m3(Wd.view(-1, H))
+    wdq, wds = ops.quantize_weight_e4m3(Wd)
     Y = ops.grouped_gemm_fp8(aq, as_, wdq, wds, E, ts, H, K)
     ops.check_status()
-    Xd, Wud = dequant(xq, xs), dequant(wuq, wus).view(E, 2 * H, K)
-    Ad, Wdd = dequant(aq, as_), dequant(wdq, wds).view(E, K, H)
+    Xd, Ad = dequant(xq, xs), dequant(aq, as_)
+    Wud = wuq.view(torch.float8_e4m3fn).float() * wus.view(E, 1, 1)
+    Wdd = wdq.view(torch.float8_e4m3fn).float() * wds.view(E, 1, 1)
+    assert torch.allclose(wus, Wu.float().abs().amax(dim=(1, 2)) / 448.0, rtol=1e-6)
     for e in range(E):
         lo = int(ts[e]) * 128
         n = counts[e]
@@ -105,7 +107,7 @@ def test_layer_with_fp8_forward_against_bf16_layer():
     fro = ((got.float() - want.float()).norm() / want.float().norm()).item()
     print(f"[fp8 layer] out: max-norm {rel(got, want):.3e}, Frobenius {fro:.3e}; "
           + ", ".join(f"grad{i} {rel(a, b):.3e}" for i, (a, b) in enumerate(zip(grads8, grads))))
-    assert rel(got, want) <= 0.12 and fro <= 0.06
+    assert rel(got, want) <= 0.12 and fro <= 0.08
     # the backward pass runs in bf16 from the saved tensors (pre-activations come from the FP8 up-projection)
     for a, b in zip(grads8, grads):
         assert torch.isfinite(a).all() and rel(a, b) <= 0.15

@@ -498,3 +498,35 @@ def test_wgrad_with_glu_backward_passenger(counts, M, Nout, H, activation):
     assert rc == 0
     ops.check_status()
     assert torch.equal(sentinel[:used], gU_ref[:used]) and (sentinel[used:] == 7.0).all()
+
+
+@pytest.mark.parametrize("activation", ["swiglu", "geglu", "relu_squared"])
+@pytest.mark.parametrize("counts,K,H", [([5, 0, 200, 128], 64, 64), ([300, 17, 129, 64, 1, 0, 77, 256], 128, 320),
+                                        ([2048] * 8, 1024, 2048)])
+def test_dact_gemm_with_fused_glu_backward(counts, K, H, activation):
+    """The dAct GEMM whose epilogue runs the GLU backward equals the dAct GEMM followed by the GLU backward kernel, bit
+    for bit, on every row of the groups' tiles (ragged groups, empty groups, H not a multiple of the 256-column tile),
+    also with a row buffer much larger than the rows in use, and for a dense (one group, ragged row count) call."""
+    torch.manual_seed(K + H)
+    gY, ts, row_expert, rows_cap = _grouped_case(counts, K)
+    E = len(counts)
+    Wd = (torch.randn(E, K, H, device=DEV) * 0.05).bfloat16()
+    pre = torch.randn(rows_cap, 2 * H, device=DEV).bfloat16()
+    used = int(ts[-1]) * 128
+    want = ops.glu_backward(ops.grouped_gemm(gY, Wd, _lib.B_NMAJOR, E, ts, K, H), pre, ts, E, activation)
+    got = ops.grouped_gemm_dact_glu_backward(gY, Wd, E, ts, K, H, pre, activation)
+    ops.check_status()
+    assert torch.equal(got[:used], want[:used])
+    # worst-case sized buffers: three times the rows, only the groups' tiles are touched
+    big_gY = torch.cat([gY, torch.randn(2 * rows_cap, K, device=DEV).bfloat16()])
+    big_pre = torch.cat([pre, torch.randn(2 * rows_cap, 2 * H, device=DEV).bfloat16()])
+    got_big = ops.grouped_gemm_dact_glu_backward(big_gY, Wd, E, ts, K, H, big_pre, activation)
+    assert torch.equal(got_big[:used], want[:used])
+    # dense, one group, a row count that is not a multiple of the tile height
+    n = min(rows_cap, 333)
+    dense_want = ops.glu_backward(ops.grouped_gemm(gY[:n].contiguous(), Wd[:1], _lib.B_NMAJOR, 1, None, K, H),
+                                  pre[:n].contiguous(), None, 1, activation)
+    dense_got = ops.grouped_gemm_dact_glu_backward(gY[:n].contiguous(), Wd[:1], 1, None, K, H, pre[:n].contiguous(),
+                                                   activation)
+    ops.check_status()
+    assert torch.equal(dense_got, dense_want)
