@@ -45,20 +45,17 @@ __device__ __forceinline__ uint4 pack8(const float (&a)[8]) {
   return make_uint4(pack_bf16x2(a[0], a[1]), pack_bf16x2(a[2], a[3]), pack_bf16x2(a[4], a[5]), pack_bf16x2(a[6], a[7]));
 }
 
-// One warp per token and per block of 1024 columns: every lane owns up to four 16-byte chunks (c, c + 32, c + 64,
-// c + 96) and, for each of the k slots in turn, issues its four loads before it uses any of them, so that k x 4
-// independent loads per lane are in flight instead of one. The sum over the slots keeps its order (slot 0 first).
 __global__ void __launch_bounds__(ROW_THREADS)
 combine_forward_kernel(const bf16* __restrict__ Y, const int32_t* __restrict__ pos, const float* __restrict__ w,
                        const bf16* __restrict__ addend, long long N, int top_k, int D, bf16* __restrict__ out) {
   const int lane = threadIdx.x & 31;
   const int chunks = D >> 3;
-  const int cblocks = (chunks + 127) >> 7;  // a warp handles one token and one block of 128 chunks (1024 columns)
+  const int cblocks = (chunks + 31) >> 5;  // a warp handles one token and one block of 32 chunks (256 columns)
   const long long items = N * cblocks;
   for (long long item = static_cast<long long>(blockIdx.x) * ROW_WARPS + (threadIdx.x >> 5); item < items;
        item += static_cast<long long>(gridDim.x) * ROW_WARPS) {
     const long long n = item / cblocks;
-    const int c0 = (static_cast<int>(item % cblocks) << 7) + lane;
+    const int c0 = static_cast<int>(item % cblocks) << 5;
     // lane j < k holds slot j's row and weight
     int my_pos = 0;
     float my_w = 0.0f;
@@ -66,40 +63,30 @@ combine_forward_kernel(const bf16* __restrict__ Y, const int32_t* __restrict__ p
       my_pos = pos[n * top_k + lane];
       my_w = (w != nullptr) ? bf16_round(w[n * top_k + lane]) : 1.0f;
     }
-    float acc[4][8];
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-#pragma unroll
-      for (int i = 0; i < 8; ++i) acc[u][i] = 0.0f;
-    }
     // every lane takes part in the shuffles, lanes past the row end only skip memory
-    for (int j = 0; j < top_k; ++j) {
-      const int pj = __shfl_sync(0xffffffffu, my_pos, j);
-      const float wj = __shfl_sync(0xffffffffu, my_w, j);
-      const uint4* row = reinterpret_cast<const uint4*>(Y + static_cast<long long>(pj) * D);
-      uint4 v[4];
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int c = c0 + 32 * u;
-        v[u] = c < chunks ? __ldg(row + c) : make_uint4(0, 0, 0, 0);
+    {
+      const int c = c0 + lane;
+      const bool active = c < chunks;
+      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      for (int j = 0; j < top_k; ++j) {
+        const int pj = __shfl_sync(0xffffffffu, my_pos, j);
+        const float wj = __shfl_sync(0xffffffffu, my_w, j);
+        if (active) {
+          const uint4 v = __ldg(reinterpret_cast<const uint4*>(Y + static_cast<long long>(pj) * D) + c);
+          fma8(acc, v, wj);
+        }
       }
-#pragma unroll
-      for (int u = 0; u < 4; ++u) fma8(acc[u], v[u], wj);
-    }
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int c = c0 + 32 * u;
-      if (c >= chunks) continue;
+      if (!active) continue;
       if (addend != nullptr) {
         // the reference adds the shared expert to the already rounded routed output
-        const uint4 r = pack8(acc[u]);
+        const uint4 r = pack8(acc);
         const uint4 a = __ldg(reinterpret_cast<const uint4*>(addend + n * D) + c);
         float s[8] = {0, 0, 0, 0, 0, 0, 0, 0};
         fma8(s, r, 1.0f);
         fma8(s, a, 1.0f);
         reinterpret_cast<uint4*>(out + n * D)[c] = pack8(s);
       } else {
-        reinterpret_cast<uint4*>(out + n * D)[c] = pack8(acc[u]);
+        reinterpret_cast<uint4*>(out + n * D)[c] = pack8(acc);
       }
     }
   }
@@ -124,36 +111,23 @@ combine_backward_kernel(const bf16* __restrict__ go, const bf16* __restrict__ Y,
     const uint4* g = reinterpret_cast<const uint4*>(go + n * D);
     const uint4* y = (Y != nullptr) ? reinterpret_cast<const uint4*>(Y + r * D) : nullptr;
     float dot = 0.0f;
-    // four chunks per lane and trip: all eight loads are issued before the first one is used; the dot product keeps
-    // its order (chunk by chunk, element by element)
-    for (int cb = lane; cb < chunks; cb += 128) {
-      uint4 gv[4], yv[4];
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int c = cb + 32 * u;
-        gv[u] = c < chunks ? __ldg(g + c) : make_uint4(0, 0, 0, 0);
-        yv[u] = (y != nullptr && c < chunks) ? __ldg(y + c) : make_uint4(0, 0, 0, 0);
-      }
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int c = cb + 32 * u;
-        if (c >= chunks) continue;
-        float o[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        fma8(o, gv[u], wi);
-        dst[c] = pack8(o);
-        if (y != nullptr) {
-          const uint4 g4 = gv[u], y4 = yv[u];
-          const float2 g0 = unpack_bf16x2(g4.x), g1 = unpack_bf16x2(g4.y), g2 = unpack_bf16x2(g4.z), g3 = unpack_bf16x2(g4.w);
-          const float2 y0 = unpack_bf16x2(y4.x), y1 = unpack_bf16x2(y4.y), y2 = unpack_bf16x2(y4.z), y3 = unpack_bf16x2(y4.w);
-          dot = fmaf(g0.x, y0.x, dot);
-          dot = fmaf(g0.y, y0.y, dot);
-          dot = fmaf(g1.x, y1.x, dot);
-          dot = fmaf(g1.y, y1.y, dot);
-          dot = fmaf(g2.x, y2.x, dot);
-          dot = fmaf(g2.y, y2.y, dot);
-          dot = fmaf(g3.x, y3.x, dot);
-          dot = fmaf(g3.y, y3.y, dot);
-        }
+    for (int c = lane; c < chunks; c += 32) {
+      const uint4 gv = __ldg(g + c);
+      float o[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      fma8(o, gv, wi);
+      dst[c] = pack8(o);
+      if (y != nullptr) {
+        const uint4 yv = __ldg(y + c);
+        const float2 g0 = unpack_bf16x2(gv.x), g1 = unpack_bf16x2(gv.y), g2 = unpack_bf16x2(gv.z), g3 = unpack_bf16x2(gv.w);
+        const float2 y0 = unpack_bf16x2(yv.x), y1 = unpack_bf16x2(yv.y), y2 = unpack_bf16x2(yv.z), y3 = unpack_bf16x2(yv.w);
+        dot = fmaf(g0.x, y0.x, dot);
+        dot = fmaf(g0.y, y0.y, dot);
+        dot = fmaf(g1.x, y1.x, dot);
+        dot = fmaf(g1.y, y1.y, dot);
+        dot = fmaf(g2.x, y2.x, dot);
+        dot = fmaf(g2.y, y2.y, dot);
+        dot = fmaf(g3.x, y3.x, dot);
+        dot = fmaf(g3.y, y3.y, dot);
       }
     }
     if (y != nullptr && gw != nullptr) {
@@ -230,7 +204,7 @@ extern "C" int ffm_combine_forward(const void* Y, const int32_t* pos, const floa
   if (D % 8 != 0 || top_k > 32) return FFM_ERR_UNSUPPORTED;
   if (N == 0) return FFM_OK;
   FFM_PREFER_MAX_SHARED(combine_forward_kernel);
-  combine_forward_kernel<<<grid_for_rows(N * ((D / 8 + 127) / 128)), ROW_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
+  combine_forward_kernel<<<grid_for_rows(N * ((D / 8 + 31) / 32)), ROW_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const bf16*>(Y), pos, w, static_cast<const bf16*>(addend), N, top_k, D, static_cast<bf16*>(out));
   return cudaGetLastError() == cudaSuccess ? FFM_OK : FFM_ERR_LAUNCH;
 }
