@@ -30,3 +30,36 @@ def test_reference_arm_is_silent_on_other_ranks():
                         "1", "--warmup", "1"], capture_output=True, text=True, timeout=120, cwd=ROOT, env=env)
     assert p.returncode == 0, p.stderr[-2000:]
     assert not [ln for ln in p.stdout.splitlines() if ln.startswith("{")]
+
+
+def test_routing_only_input_gradient_restatement_against_the_oracle():
+    """bench.py's fp32 restatement of the expert-parallel input gradient (routing-weight path + shared expert, the
+    experts' own input held constant: reference fused_moe.py:1001-1005), which `ep_parity` compares the sharded
+    layer with, agrees with the oracle's backward on a small case (the oracle rounds to bf16 where the reference
+    does, the restatement does not: bf16 bound)."""
+    import importlib.util
+    import torch
+    from oracle import moe_oracle as orc
+    spec = importlib.util.spec_from_file_location("bench_module", os.path.join(ROOT, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    torch.manual_seed(0)
+    N, D, E, F, k = 96, 64, 8, 128, 2
+    bf = torch.bfloat16
+    h = torch.randn(N, D).to(bf)
+    g = (torch.randn(E, D) * 0.1).to(bf)
+    wu = (torch.randn(E, F, D) * 0.1).to(bf)
+    wd = (torch.randn(E, D, F // 2) * 0.1).to(bf)
+    shared = [(torch.randn(F // 2, D) * 0.1).to(bf), (torch.randn(F // 2, D) * 0.1).to(bf),
+              (torch.randn(D, F // 2) * 0.1).to(bf)]
+    go = torch.randn(N, D).to(bf)
+    fw = orc.fused_moe_forward(h, g, wu, wd, k, dtype=bf)
+    bw = orc.fused_moe_backward(fw, go)
+    route_only = orc.mm(bw["gl"], g, bf).float()
+    xs = h.float().requires_grad_()
+    ws = [t.float() for t in shared]
+    ((torch.nn.functional.silu(xs @ ws[0].T) * (xs @ ws[1].T)) @ ws[2].T * go.float()).sum().backward()
+    want = route_only + xs.grad
+    got = bench.routing_only_input_grad(h, go, g, wu, wd, shared, fw["topk_idx"])
+    err = ((got - want).abs().max() / want.abs().max()).item()
+    assert err <= 2e-2, err
