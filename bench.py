@@ -446,7 +446,7 @@ def other_configs(group, rank, world, device):
     if rank != 0:
         return None
     keep = ("value", "unit", "ms_per_step", "gemm_tflops_per_gpu_whole_step", "p50", "p99", "min", "mode",
-            "weight_stream_bound_ms", "tokens_per_gpu", "iters", "steps", "config", "skipped")
+            "weight_stream_bound_ms", "tokens_per_gpu", "iters", "steps", "config", "skipped", "grad_sync")
     return {n: ({k: v for k, v in d.items() if k in keep} if isinstance(d, dict) else d) for n, d in out.items()}
 
 
@@ -651,14 +651,15 @@ def main():
     # ---- end to end: pinned host input in, loss scalar out, every step ------------------------
     # The loop a training script would run around the public API: the next step's input is uploaded on a copy
     # stream while the current step computes (two device buffers), and each step's loss is copied to pinned
-    # host memory and read one step later, so neither transfer stalls the compute stream. Every step still
+    # host memory and read two steps later, so neither transfer stalls the compute stream. Every step still
     # moves its own input host -> device and its own loss device -> host inside the timed region.
     copy_stream = torch.cuda.Stream(device=device)
     x_bufs = [torch.empty_like(x_host, device=device) for _ in range(2)]
-    loss_host = torch.zeros(2, dtype=torch.float32).pin_memory()
+    LAG = 2   # a step's loss is read two steps later: the host stays two replays ahead of the GPU
+    loss_host = torch.zeros(LAG + 1, dtype=torch.float32).pin_memory()
     uploaded = [torch.cuda.Event(), torch.cuda.Event()]
     consumed = [torch.cuda.Event(), torch.cuda.Event()]
-    loss_ready = [torch.cuda.Event(), torch.cuda.Event()]
+    loss_ready = [torch.cuda.Event() for _ in range(LAG + 1)]
 
     def upload(i):
         with torch.cuda.stream(copy_stream):
@@ -716,13 +717,17 @@ def main():
                 loss.backward()
                 consumed[i % 2].record(main)
                 loss = loss.detach().reshape(1)
-            loss_host[i % 2:i % 2 + 1].copy_(loss, non_blocking=True)
-            loss_ready[i % 2].record(main)
-            if i >= 1:
-                loss_ready[(i - 1) % 2].synchronize()
-                losses_read.append(float(loss_host[(i - 1) % 2]))
-        loss_ready[(steps - 1) % 2].synchronize()
-        losses_read.append(float(loss_host[(steps - 1) % 2]))
+            slot = i % (LAG + 1)
+            loss_host[slot:slot + 1].copy_(loss, non_blocking=True)
+            loss_ready[slot].record(main)
+            if i >= LAG:
+                back = (i - LAG) % (LAG + 1)
+                loss_ready[back].synchronize()
+                losses_read.append(float(loss_host[back]))
+        for i in range(max(steps - LAG, 0), steps):
+            back = i % (LAG + 1)
+            loss_ready[back].synchronize()
+            losses_read.append(float(loss_host[back]))
         return losses_read
 
     time.sleep(0.5)   # the same power headroom as the device-resident region started with

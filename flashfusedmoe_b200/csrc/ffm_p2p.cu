@@ -5,8 +5,8 @@
 //   p2p_push_kernel     copies up to FFM_P2P_MAX_PEERS contiguous segments of the local send buffer to
 //                       (peer base + offset); blockIdx.y selects the segment.
 //   p2p_rows_kernel     the same copy at row granularity, driven by a table of segments in device memory
-//                       {first source row, first destination row, rows, destination buffer}: one warp per row finds
-//                       its segment by binary search on the running row count. The source row may be looked up
+//                       {first source row, first destination row, rows, destination buffer}: a warp takes four
+//                       consecutive rows, four of its lanes find their segments by binary search on the running row count. The source row may be looked up
 //                       through an index (gather from the token matrix), or be absent (the rows are zeroed).
 //   p2p_plan_kernel     builds those tables on the device from the [ep, E] matrix of row counts, so that a forward
 //                       pass needs no host read of the counts (and can be captured in a CUDA graph).
@@ -48,6 +48,13 @@ struct RowBases {
   uint8_t* base[FFM_P2P_MAX_PEERS];
 };
 
+// Four consecutive rows per warp and trip. Lanes 0..3 each find the segment of one row (binary search on the running
+// row count), its source row (through the index, if any) and its destination address, and hand them to the warp by
+// shuffle; then every lane moves one 16-byte chunk of each of the four rows per step, four loads in flight before the
+// four stores. Consecutive rows mostly share a segment, so the four stores of a step land in one contiguous stretch
+// of the destination.
+constexpr int ROWS_PER_WARP = 4;
+
 __global__ void __launch_bounds__(256) p2p_rows_kernel(const uint8_t* __restrict__ src, const int32_t* __restrict__ src_index,
                                                        int index_div, long long row_bytes,
                                                        const long long* __restrict__ segments,
@@ -59,36 +66,55 @@ __global__ void __launch_bounds__(256) p2p_rows_kernel(const uint8_t* __restrict
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int chunks = static_cast<int>(row_bytes >> 4);
-  for (long long row = static_cast<long long>(blockIdx.x) * warps + warp; row < total_rows;
-       row += static_cast<long long>(gridDim.x) * warps) {
-    int lo = 0, hi = n_segments - 1;  // smallest segment whose running end lies beyond this row
-    while (lo < hi) {
-      const int mid = (lo + hi) >> 1;
-      if (__ldg(seg_end + mid) > row) {
-        hi = mid;
-      } else {
-        lo = mid + 1;
+  for (long long row0 = (static_cast<long long>(blockIdx.x) * warps + warp) * ROWS_PER_WARP; row0 < total_rows;
+       row0 += static_cast<long long>(gridDim.x) * warps * ROWS_PER_WARP) {
+    // lanes 0..3: where row0 + lane comes from and where it goes
+    unsigned long long my_src = 0ull, my_dst = 0ull;
+    const long long row = row0 + lane;
+    if (lane < ROWS_PER_WARP && row < total_rows) {
+      int lo = 0, hi = n_segments - 1;  // smallest segment whose running end lies beyond this row
+      while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if (__ldg(seg_end + mid) > row) {
+          hi = mid;
+        } else {
+          lo = mid + 1;
+        }
       }
+      const long long j = row - (lo > 0 ? __ldg(seg_end + lo - 1) : 0LL);
+      const long long* seg = segments + 4LL * lo;
+      long long src_row = __ldg(seg) + j;
+      if (src_index != nullptr) src_row = __ldg(src_index + src_row) / index_div;
+      my_dst = reinterpret_cast<unsigned long long>(bases.base[__ldg(seg + 3)] + (__ldg(seg + 1) + j) * row_bytes);
+      my_src = src != nullptr ? reinterpret_cast<unsigned long long>(src + src_row * row_bytes) : 0ull;
     }
-    const long long j = row - (lo > 0 ? __ldg(seg_end + lo - 1) : 0LL);
-    const long long* seg = segments + 4LL * lo;
-    long long src_row = __ldg(seg) + j;
-    if (src_index != nullptr) src_row = __ldg(src_index + src_row) / index_div;
-    uint4* __restrict__ d = reinterpret_cast<uint4*>(bases.base[__ldg(seg + 3)] + (__ldg(seg + 1) + j) * row_bytes);
+    const uint4* s[ROWS_PER_WARP];
+    uint4* d[ROWS_PER_WARP];
+#pragma unroll
+    for (int q = 0; q < ROWS_PER_WARP; ++q) {
+      s[q] = reinterpret_cast<const uint4*>(__shfl_sync(0xffffffffu, my_src, q));
+      d[q] = reinterpret_cast<uint4*>(__shfl_sync(0xffffffffu, my_dst, q));  // null: no such row
+    }
     if (src != nullptr) {
-      const uint4* __restrict__ s = reinterpret_cast<const uint4*>(src + src_row * row_bytes);
-      int c = lane;
-      for (; c + 96 < chunks; c += 128) {  // four independent 16-byte copies in flight per lane
-        const uint4 v0 = s[c], v1 = s[c + 32], v2 = s[c + 64], v3 = s[c + 96];
-        d[c] = v0;
-        d[c + 32] = v1;
-        d[c + 64] = v2;
-        d[c + 96] = v3;
+      for (int c = lane; c < chunks; c += 32) {
+        uint4 v[ROWS_PER_WARP];
+#pragma unroll
+        for (int q = 0; q < ROWS_PER_WARP; ++q) {
+          if (d[q] != nullptr) v[q] = s[q][c];
+        }
+#pragma unroll
+        for (int q = 0; q < ROWS_PER_WARP; ++q) {
+          if (d[q] != nullptr) d[q][c] = v[q];
+        }
       }
-      for (; c < chunks; c += 32) d[c] = s[c];
     } else {
       const uint4 z = make_uint4(0u, 0u, 0u, 0u);
-      for (int c = lane; c < chunks; c += 32) d[c] = z;
+      for (int c = lane; c < chunks; c += 32) {
+#pragma unroll
+        for (int q = 0; q < ROWS_PER_WARP; ++q) {
+          if (d[q] != nullptr) d[q][c] = z;
+        }
+      }
     }
   }
 }
@@ -273,7 +299,7 @@ extern "C" int ffm_p2p_push_rows(const void* src, const int32_t* src_index, int 
     if (!dst_bases[i] || (reinterpret_cast<uintptr_t>(dst_bases[i]) & 15u) != 0) return FFM_ERR_BAD_ARG;
     b.base[i] = static_cast<uint8_t*>(dst_bases[i]);
   }
-  long long blocks = (total_rows + 7) / 8;
+  long long blocks = (total_rows + 8 * ROWS_PER_WARP - 1) / (8 * ROWS_PER_WARP);
   if (blocks > 148LL * 8) blocks = 148LL * 8;
   p2p_rows_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint8_t*>(src), src_index, index_div, row_bytes, reinterpret_cast<const long long*>(segments),
@@ -297,7 +323,7 @@ extern "C" int ffm_p2p_push_rows_dev(const void* src, const int32_t* src_index, 
     if (!dst_bases[i] || (reinterpret_cast<uintptr_t>(dst_bases[i]) & 15u) != 0) return FFM_ERR_BAD_ARG;
     b.base[i] = static_cast<uint8_t*>(dst_bases[i]);
   }
-  long long blocks = (max_rows + 7) / 8;
+  long long blocks = (max_rows + 8 * ROWS_PER_WARP - 1) / (8 * ROWS_PER_WARP);
   if (blocks > 148LL * 8) blocks = 148LL * 8;
   p2p_rows_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint8_t*>(src), src_index, index_div, row_bytes, reinterpret_cast<const long long*>(segments),

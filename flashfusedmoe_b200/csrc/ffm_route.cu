@@ -280,7 +280,7 @@ route_gate_topk(const bf16* __restrict__ hidden, const bf16* __restrict__ gate_w
                 long long N, int D, int E, int top_k, RouteOpts opts, int tokens_per_block,
                 bf16* __restrict__ logits_out, float* __restrict__ topk_w, int32_t* __restrict__ topk_idx,
                 float* __restrict__ lse_out, int32_t* __restrict__ block_hist, float* __restrict__ block_mass,
-                float* __restrict__ block_z) {
+                float* __restrict__ block_z, int gate_in_smem) {
   // sized for the experts this instantiation can see, so that the few-expert variants fit beside a resident GEMM
   __shared__ float s_mass[ROUTE_WARPS][GW * NG];
   __shared__ int s_cnt[ROUTE_WARPS][GW * NG];
@@ -292,6 +292,17 @@ route_gate_topk(const bf16* __restrict__ hidden, const bf16* __restrict__ gate_w
   long long tok_end = tok_begin + tokens_per_block;
   if (tok_end > N) tok_end = N;
   const int chunks = D >> 3;  // 16-byte chunks per row
+
+  // Few experts (a warp owns them all): the block copies the gate matrix into shared memory once and every token's
+  // dot products read it from there. Read from global memory instead, each lane re-loads E 16-byte chunks per chunk
+  // of the token, far more loads than the 64 registers of this occupancy can keep in flight, and the kernel ran at
+  // an eighth of HBM speed.
+  extern __shared__ uint4 s_gate[];
+  if (NG == 1 && gate_in_smem) {
+    const uint4* gsrc = reinterpret_cast<const uint4*>(gate_w);
+    for (int i = threadIdx.x; i < E * chunks; i += ROUTE_THREADS) s_gate[i] = __ldg(gsrc + i);
+    __syncthreads();
+  }
 
   float mass[NG];
   int cnt[NG];
@@ -375,7 +386,9 @@ route_gate_topk(const bf16* __restrict__ hidden, const bf16* __restrict__ gate_w
           for (int e = 0; e < GW; ++e) {
             const int ee = g * GW + e;
             if (ee < E) {
-              const uint4 w = __ldg(reinterpret_cast<const uint4*>(gate_w + static_cast<long long>(ee) * D) + c);
+              const uint4 w = gate_in_smem
+                                  ? s_gate[ee * chunks + c]
+                                  : __ldg(reinterpret_cast<const uint4*>(gate_w + static_cast<long long>(ee) * D) + c);
               acc0[e] = dot8(a0, w, acc0[e]);
               acc1[e] = dot8(a1, w, acc1[e]);
             }
@@ -669,9 +682,20 @@ void launch_route(int blocks, cudaStream_t s, const bf16* hidden, const bf16* ga
                   int32_t* topk_idx, float* lse, const RouteWorkspace& w) {
   auto kernel = route_gate_topk<GW, NG>;
   FFM_PREFER_MAX_SHARED(kernel);
-  route_gate_topk<GW, NG><<<blocks, ROUTE_THREADS, 0, s>>>(hidden, gate_w, bias, N, D, E, top_k, opts, tpb, logits,
-                                                           topk_w, topk_idx, lse, w.block_hist, w.block_mass,
-                                                           w.block_z);
+  // gate matrix in shared memory when a warp owns all experts and E x D bf16 fits in 64 KiB
+  constexpr size_t kGateSmemMax = 64 * 1024;
+  const size_t gate_bytes = static_cast<size_t>(E) * D * sizeof(bf16);
+  static bool smem_ok = false, smem_tried = false;
+  if (NG == 1 && !smem_tried) {
+    smem_tried = true;
+    smem_ok = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   static_cast<int>(kGateSmemMax)) == cudaSuccess;
+    if (!smem_ok) cudaGetLastError();
+  }
+  const bool in_smem = NG == 1 && gate_bytes <= kGateSmemMax && (gate_bytes <= 48 * 1024 || smem_ok) && D % 8 == 0;
+  route_gate_topk<GW, NG><<<blocks, ROUTE_THREADS, in_smem ? gate_bytes : 0, s>>>(
+      hidden, gate_w, bias, N, D, E, top_k, opts, tpb, logits, topk_w, topk_idx, lse, w.block_hist, w.block_mass,
+      w.block_z, in_smem ? 1 : 0);
 }
 
 // Expert capacity: a routed slot whose rank inside its expert segment is >= capacity is dropped. One thread
@@ -783,7 +807,8 @@ extern "C" int ffm_route_forward(const void* hidden, const void* gate_w, const f
   bf16* lg = static_cast<bf16*>(logits);
   // Many experts: gate GEMM on the tensor cores (dense tcgen05 GEMM, fp32 accumulate, bf16 logits), then one
   // scoring kernel. Few experts: everything in one warp-level kernel.
-  const bool tensor_gate = E > 32 && D % 64 == 0 && E % 32 == 0 && logits != nullptr;
+  // (E = 32 included: one warp owning 32 experts keeps 64 accumulators per lane and ran at 0.12 TB/s)
+  const bool tensor_gate = E >= 32 && D % 64 == 0 && E % 32 == 0 && logits != nullptr;
   if (tensor_gate) {
     const int rc = ffm_grouped_gemm(hidden, gate_w, FFM_B_KMAJOR, 1, nullptr, N, D, E, 1.0f, logits, nullptr, 0, status,
                                     stream);

@@ -51,7 +51,7 @@ def make_groups(counts, device=DEV):
 
 @pytest.mark.parametrize("gating", ["softmax", "sigmoid"])
 @pytest.mark.parametrize("N,D,E,k", [(1, 64, 4, 1), (37, 64, 8, 2), (512, 256, 8, 2), (300, 128, 16, 4),
-                                     (129, 256, 64, 6), (128, 512, 256, 8), (1000, 128, 24, 3)])
+                                     (129, 256, 64, 6), (128, 512, 256, 8), (1000, 128, 24, 3), (700, 256, 32, 4)])
 def test_route_forward(N, D, E, k, gating):
     torch.manual_seed(N + E)
     hidden = torch.randn(N, D, device=DEV).bfloat16()
