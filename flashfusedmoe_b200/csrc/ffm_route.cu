@@ -10,6 +10,8 @@
 //
 // Tokens are assigned to blocks in contiguous chunks, so "block order, then warp order, then slot order"
 // equals the (token, slot) order of a stable sort by expert id.
+#include <atomic>
+
 #include "ffm_common.cuh"
 
 namespace ffm {
@@ -737,21 +739,21 @@ static __device__ __align__(256) unsigned char g_static_scratch[FFM_STATIC_SCRAT
 // stand-in for the symbol, not a pointer a kernel could use, so the address is asked for once per device
 // (with that device current) and remembered.
 int static_scratch_address(void** out) {
-  static void* cached[64] = {};
+  static std::atomic<void*> cached[64];  // (zero-initialised; host threads may race here: same value either way)
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
     cudaGetLastError();
     return FFM_ERR_LAUNCH;
   }
-  if (cached[dev] == nullptr) {
-    void* p = nullptr;
+  void* p = cached[dev].load(std::memory_order_acquire);
+  if (p == nullptr) {
     if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || p == nullptr) {
       cudaGetLastError();
       return FFM_ERR_LAUNCH;
     }
-    cached[dev] = p;
+    cached[dev].store(p, std::memory_order_release);
   }
-  *out = cached[dev];
+  *out = p;
   return FFM_OK;
 }
 

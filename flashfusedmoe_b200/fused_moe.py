@@ -77,28 +77,34 @@ def set_expert_gemm_precision(mode):
     return old
 
 
-def _quantized_weight(w):
-    """e4m3 copy of a weight tensor [E, N, K] with one scale per expert; cached until the tensor is modified in place
-    (its version counter moves) or replaced."""
-    key = (w.data_ptr(), tuple(w.shape))
+def _quantized_weight(owner, w):
+    """e4m3 copy of the weight tensor `w` [E, N, K] (bf16, possibly a cast copy of `owner`) with one scale per expert.
+    Cached per owner, the caller's own weight tensor (normally an nn.Parameter): the entry is reused while that very
+    object is alive, unmodified (same version counter) and still where it was; a weak reference drops the entry
+    when the owner dies, so an address reused by another tensor can never hit a stale entry."""
+    import weakref
+    key = id(owner)
     hit = _fp8_weight_cache.get(key)
-    if hit is not None and hit[0] == w._version:
-        return hit[1], hit[2]
+    if hit is not None and hit[0]() is owner and hit[1] == (owner._version, owner.data_ptr(), tuple(owner.shape)):
+        return hit[2], hit[3]
     q, sc = ops.quantize_weight_e4m3(w)
-    if len(_fp8_weight_cache) > 64:
-        _fp8_weight_cache.clear()
-    _fp8_weight_cache[key] = (w._version, q, sc)
+    try:
+        ref = weakref.ref(owner, lambda _r, k=key: _fp8_weight_cache.pop(k, None))
+    except TypeError:
+        return q, sc
+    _fp8_weight_cache[key] = (ref, (owner._version, owner.data_ptr(), tuple(owner.shape)), q, sc)
     return q, sc
 
 
-def _expert_ffn_forward(Xg, wu, wd, E, tile_start, D, H, activation, keep, small):
+def _expert_ffn_forward(Xg, wu, wd, E, tile_start, D, H, activation, keep, small, owners=None):
     """Up-projection + GLU and down-projection of the routed experts over grouped rows: (act, pre, Y)."""
     if _EXPERT_GEMM == "fp8" and D % 128 == 0 and H % 128 == 0 and not small:
         xq, xs = ops.quantize_rows_e4m3(Xg)
-        wuq, wus = _quantized_weight(wu)
+        own_u, own_d = owners if owners is not None else (wu, wd)
+        wuq, wus = _quantized_weight(own_u, wu)
         act, pre = ops.grouped_gemm_glu_fp8(xq, xs, wuq, wus, E, tile_start, D, H, activation, want_preact=keep)
         aq, as_ = ops.quantize_rows_e4m3(act)
-        wdq, wds = _quantized_weight(wd)
+        wdq, wds = _quantized_weight(own_d, wd)
         Y = ops.grouped_gemm_fp8(aq, as_, wdq, wds, E, tile_start, H, D)
         return act, pre, Y
     act, pre = ops.grouped_gemm_glu(Xg, wu, wu.view(-1, D)[H:], 2 * H, E, tile_start, D, H, activation,
@@ -372,7 +378,8 @@ class _FusedMoEFunction(torch.autograd.Function):
         keep = need_grad and not cfg.recompute
         # inference with few rows per expert (decode): one CTA per 128-row tile and no work on tiles without rows
         small = _small_m_kwargs(not need_grad and cfg.capacity is None and N * k < 128 * E, routing.counts)
-        act, pre, Y = _expert_ffn_forward(Xg, wu, wd, E, routing.tile_start, D, H, cfg.activation, keep, small)
+        act, pre, Y = _expert_ffn_forward(Xg, wu, wd, E, routing.tile_start, D, H, cfg.activation, keep, small,
+                                          owners=(w_up, w_down))
         if add is not None and cfg.addend_ready is not None:
             torch.cuda.current_stream().wait_event(cfg.addend_ready)
             add.record_stream(torch.cuda.current_stream())
