@@ -630,21 +630,28 @@ def main():
     # ---- expert parallel only: K steps whose row exchanges move nothing (everything else runs) -----------------
     # step time minus this = the exchange time that compute did not hide
     dry_ms = None
+    dry_mode = None
     if world > 1:
         fm = sys.modules["flashfusedmoe_b200.fused_moe"]
         fm.set_ep_dry_exchange(True)
+        dry_fn = step
+        if graph is not None:
+            # compared like with like: the dry step is captured and replayed as the measured one is
+            try:
+                dry_graph, _ = capture_step(step)
+                dry_fn, dry_mode = dry_graph.replay, "replayed"
+            except Exception:
+                torch.cuda.synchronize()
+        fence()
         for _ in range(2):
-            step()
-        fence()
-        d0 = torch.cuda.Event(enable_timing=True)
-        d1 = torch.cuda.Event(enable_timing=True)
-        d0.record()
-        for _ in range(K):
-            step()
-        d1.record()
-        fence()
+            dry_fn()
+        dry_ms, _ = timed_region(dry_fn)
         fm.set_ep_dry_exchange(False)
-        dry_ms = d0.elapsed_time(d1)
+        if dry_mode is None:
+            dry_mode = "eager"
+        else:
+            del dry_graph
+        dry_fn = None
         step()   # one real step: the receive buffers hold real rows again
         fence()
 
@@ -864,7 +871,8 @@ def main():
             # Time is from CUDA events around each call on its issuing stream, so it includes waiting for peers;
             # the NVLink fraction is against the per-direction peer copy measured by this run (measure_peer_copy).
             n_a2a, a2a_ms = kt["all_to_all"]
-            ref_ms = eager["ms_per_step"] * K if eager is not None else ms
+            # the step the dry one is compared with: the replayed one if the dry step was replayed too
+            ref_ms = ms if (dry_mode == "replayed" or eager is None) else eager["ms_per_step"] * K
             gbs = a2a_bytes / (a2a_ms * 1e-3) / 1e9 if a2a_ms > 0 else None
             link = (nvlink or {}).get("copy_engine_gbs")
             line["expert_parallel"] = {"all_to_all_calls_per_step": n_a2a / K, "all_to_all_ms_per_step": a2a_ms / K,
@@ -878,7 +886,7 @@ def main():
                                        # exposed = step time minus the time of the same step with exchanges that move
                                        # nothing; hidden = 1 - exposed / (event time of the exchanges)
                                        "ms_per_step_without_exchange_payload": dry_ms / K,
-                                       # (both eager: a replayed graph is compared with nothing here)
+                                       "dry_step_launch": dry_mode,
                                        "exposed_exchange_ms_per_step": max(0.0, (ref_ms - dry_ms) / K),
                                        "hidden_frac": (min(1.0, max(0.0, 1.0 - (ref_ms - dry_ms) / a2a_ms))
                                                        if a2a_ms > 0 else None),
