@@ -446,7 +446,7 @@ def other_configs(group, rank, world, device):
     if rank != 0:
         return None
     keep = ("value", "unit", "ms_per_step", "gemm_tflops_per_gpu_whole_step", "p50", "p99", "min", "mode",
-            "weight_stream_bound_ms", "tokens_per_gpu", "iters", "steps", "config", "skipped", "grad_sync")
+            "weight_stream_bound_ms", "tokens_per_gpu", "iters", "steps", "config", "skipped", "grad_sync", "all_to_all_ms_per_iter")
     return {n: ({k: v for k, v in d.items() if k in keep} if isinstance(d, dict) else d) for n, d in out.items()}
 
 

@@ -70,7 +70,7 @@ SIGNATURES = {
     "ffm_p2p_push_rows_dev": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_int64,
                                       c_void_p, c_int, c_void_p]),
     "ffm_p2p_plan": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                             c_void_p, c_void_p, c_void_p]),
+                             c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
     "ffm_p2p_signal_wait_dev": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, ctypes.c_longlong, c_void_p]),
     "ffm_p2p_signal_wait": (c_int, [c_void_p, c_int, c_int, ctypes.c_uint32, c_void_p, ctypes.c_longlong, c_void_p]),
     "ffm_route_backward_workspace_bytes": (c_size_t, [c_int64, c_int, c_int]),

@@ -18,6 +18,7 @@ extern "C" const char* ffm_error_string(int code) {
     case FFM_STATUS_WAIT_EPILOGUE: return "device: epilogue wait ran out";
     case FFM_STATUS_BAD_INDEX: return "device: expert index or row position out of range";
     case FFM_STATUS_WAIT_PEER: return "device: a peer GPU did not signal within the wait budget";
+    case FFM_STATUS_EP_OVERFLOW: return "device: a rank would receive more rows than the declared bound; nothing was moved";
     default: return "unknown code";
   }
 }

@@ -129,13 +129,16 @@ __global__ void __launch_bounds__(256) p2p_plan_kernel(const int32_t* __restrict
                                                        long long* __restrict__ dispatch, long long* __restrict__ dispatch_end,
                                                        long long* __restrict__ combine, long long* __restrict__ combine_end,
                                                        long long* __restrict__ padding, long long* __restrict__ padding_end,
-                                                       int32_t* __restrict__ tile_start, long long* __restrict__ totals) {
+                                                       int32_t* __restrict__ tile_start, long long* __restrict__ totals,
+                                                       long long max_grouped_rows, int32_t* __restrict__ status) {
   __shared__ long long s_R[PLAN_MAX_E];      // rows per expert over all sources
+  __shared__ int s_overflow;
   __shared__ long long s_seg0[PLAN_MAX_E];   // first grouped row of expert e at its owner
   __shared__ long long s_send0[FFM_P2P_MAX_PEERS][PLAN_MAX_E];  // first sender-order row of expert e at rank s
   __shared__ long long s_rows_grouped;
   const int E = ep * e_local;
   const int t = threadIdx.x;
+  if (t == 0) s_overflow = 0;
   for (int e = t; e < E; e += blockDim.x) {
     long long r = 0;
     for (int s = 0; s < ep; ++s) r += C[s * E + e];
@@ -161,8 +164,36 @@ __global__ void __launch_bounds__(256) p2p_plan_kernel(const int32_t* __restrict
       tile_start[e_local] = static_cast<int32_t>(tiles);
       s_rows_grouped = tiles * 128;
     }
+    // the grouped layout of owner t must fit its receive buffer; every rank evaluates every owner on the same counts
+    if (max_grouped_rows > 0 && tiles * 128 > max_grouped_rows) s_overflow = 1;
   }
   __syncthreads();
+  if (s_overflow) {
+    // nothing may be stored past a buffer: tables that move nothing, and the status word says why
+    for (int e = t; e < E; e += blockDim.x) {
+      dispatch[4 * e + 0] = dispatch[4 * e + 1] = dispatch[4 * e + 2] = 0;
+      dispatch[4 * e + 3] = e / e_local;
+      dispatch_end[e] = 0;
+    }
+    for (int i = t; i < e_local * ep; i += blockDim.x) {
+      combine[4 * i + 0] = combine[4 * i + 1] = combine[4 * i + 2] = 0;
+      combine[4 * i + 3] = i % ep;
+      combine_end[i] = 0;
+    }
+    for (int el = t; el <= e_local; el += blockDim.x) {
+      tile_start[el] = 0;
+      if (el < e_local) {
+        padding[4 * el + 0] = padding[4 * el + 1] = padding[4 * el + 2] = 0;
+        padding[4 * el + 3] = rank;
+        padding_end[el] = 0;
+      }
+    }
+    if (t == 0) {
+      totals[0] = totals[1] = totals[2] = totals[3] = 0;
+      if (status != nullptr) atomicCAS(status, 0, FFM_STATUS_EP_OVERFLOW);
+    }
+    return;
+  }
   const int lo = rank * e_local;
   // dispatch: one run per expert, sender order -> owner's grouped layout
   for (int e = t; e < E; e += blockDim.x) {
@@ -333,18 +364,20 @@ extern "C" int ffm_p2p_push_rows_dev(const void* src, const int32_t* src_index, 
 
 extern "C" int ffm_p2p_plan(const int32_t* counts, int ep, int e_local, int rank, int64_t* dispatch,
                             int64_t* dispatch_end, int64_t* combine, int64_t* combine_end, int64_t* padding,
-                            int64_t* padding_end, int32_t* tile_start, int64_t* totals, ffm_stream_t stream) {
+                            int64_t* padding_end, int32_t* tile_start, int64_t* totals, int64_t max_grouped_rows,
+                            int32_t* status, ffm_stream_t stream) {
   if (!counts || !dispatch || !dispatch_end || !combine || !combine_end || !padding || !padding_end || !tile_start ||
       !totals) {
     return FFM_ERR_BAD_ARG;
   }
   if (ep < 1 || ep > FFM_P2P_MAX_PEERS || e_local < 1 || rank < 0 || rank >= ep) return FFM_ERR_BAD_ARG;
   if (ep * e_local > PLAN_MAX_E) return FFM_ERR_UNSUPPORTED;
+  if (max_grouped_rows < 0 || (max_grouped_rows > 0 && status == nullptr)) return FFM_ERR_BAD_ARG;
   p2p_plan_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       counts, ep, e_local, rank, reinterpret_cast<long long*>(dispatch), reinterpret_cast<long long*>(dispatch_end),
       reinterpret_cast<long long*>(combine), reinterpret_cast<long long*>(combine_end),
       reinterpret_cast<long long*>(padding), reinterpret_cast<long long*>(padding_end), tile_start,
-      reinterpret_cast<long long*>(totals));
+      reinterpret_cast<long long*>(totals), max_grouped_rows, status);
   return cudaGetLastError() == cudaSuccess ? FFM_OK : FFM_ERR_LAUNCH;
 }
 

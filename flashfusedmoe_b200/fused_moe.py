@@ -574,13 +574,21 @@ class _EPPlan:
 # sequence that a CUDA graph can capture and replay. Kernels only touch the rows in use (the persistent GEMM stops at
 # the last real tile), so the worst-case sizes cost address space and memory, not time.
 _EP_STATIC_TOKENS = None
+_EP_STATIC_ROWS = None
 
 
-def set_ep_static_forward(max_tokens_per_rank):
+def set_ep_static_forward(max_tokens_per_rank, max_recv_rows=None):
     """Enable (int, identical on every rank) or disable (None) host-sync-free expert parallelism: inference and
-    training calls without latent projection then run without reading the routing counts on the host."""
-    global _EP_STATIC_TOKENS
+    training calls without latent projection then run without reading the routing counts on the host.
+
+    max_recv_rows (optional, identical on every rank) bounds the routed rows a rank's experts may receive in one
+    call, and with it the size of every buffer (default: the worst case, every routed row of every rank; the
+    reference's own bound is twice the balanced load, fused_moe.py:100-113). If the routing of a call would exceed
+    it on any rank, that call moves and computes nothing and sets device status 106 (raised by a later fused_moe()
+    call or ops.check_status()): rows are never dropped silently and never stored past a buffer."""
+    global _EP_STATIC_TOKENS, _EP_STATIC_ROWS
     _EP_STATIC_TOKENS = None if max_tokens_per_rank is None else int(max_tokens_per_rank)
+    _EP_STATIC_ROWS = None if (max_recv_rows is None or max_tokens_per_rank is None) else int(max_recv_rows)
 
 
 class _FusedMoEEPStaticFunction(torch.autograd.Function):
@@ -620,10 +628,12 @@ class _FusedMoEEPStaticFunction(torch.autograd.Function):
             shared_done.record(side)
             shared = (s_out, s_act, s_pre, swg, swu, swd)
         rb = D * h.element_size()
-        cap_rows = (ep * _EP_STATIC_TOKENS * k + 256 * El + 255) // 256 * 256   # every row of every rank lands here
-        px = p2p.get_exchange(group, h.device, cap_rows * rb)
+        worst = ep * _EP_STATIC_TOKENS * k                       # every routed row of every rank lands on one rank
+        bounded = _EP_STATIC_ROWS is not None and _EP_STATIC_ROWS < worst
+        cap_rows = ((_EP_STATIC_ROWS if bounded else worst) + 256 * El + 255) // 256 * 256
+        px = p2p.get_exchange(group, h.device, max(cap_rows, _EP_STATIC_TOKENS * k) * rb)
         C = px.share_counts(routing.counts)
-        t = px.plan_dev(C, El)
+        t = px.plan_dev(C, El, max_grouped_rows=cap_rows if bounded else 0)
         cpos, src_c = _compact_send_map(routing, T)
         tot = t["totals"]
         dry = _EP_DRY_EXCHANGE   # measurement aid: the row exchanges move nothing and their barriers are skipped

@@ -228,8 +228,10 @@ class PeerExchange:
         self.barrier_dev()
         return self.buf[COUNTS_OFFSET:COUNTS_OFFSET + n * E * 4].view(torch.int32).view(n, E)
 
-    def plan_dev(self, count_matrix, e_local):
-        """Device-built tables of one call (ffm_p2p_plan) from the shared count matrix."""
+    def plan_dev(self, count_matrix, e_local, max_grouped_rows=0):
+        """Device-built tables of one call (ffm_p2p_plan) from the shared count matrix. max_grouped_rows > 0: the
+        rows every rank's receive buffer holds; if any rank's grouped layout would exceed it the tables move nothing
+        and the status word gets FFM_STATUS_EP_OVERFLOW."""
         lib = _lib.load()
         ep = self.world
         E = ep * e_local
@@ -244,7 +246,8 @@ class PeerExchange:
                                         t["dispatch_end"].data_ptr(), t["combine"].data_ptr(),
                                         t["combine_end"].data_ptr(), t["padding"].data_ptr(),
                                         t["padding_end"].data_ptr(), t["tile_start"].data_ptr(),
-                                        t["totals"].data_ptr(), ops._stream()), "ffm_p2p_plan")
+                                        t["totals"].data_ptr(), int(max_grouped_rows),
+                                        ops.status_tensor(dev).data_ptr(), ops._stream()), "ffm_p2p_plan")
         return t
 
     def push_rows_dev(self, src, src_index, index_div, row_bytes, seg, seg_end, total_dev, max_rows, region,

@@ -49,6 +49,7 @@ extern "C" {
 #define FFM_STATUS_WAIT_EPILOGUE 103 /* epilogue gave up waiting for an accumulator */
 #define FFM_STATUS_BAD_INDEX 104     /* an expert index or row position was out of range */
 #define FFM_STATUS_WAIT_PEER 105     /* a peer GPU's flag did not arrive within the wait budget */
+#define FFM_STATUS_EP_OVERFLOW 106   /* a rank would receive more rows than its declared bound: the call moved nothing */
 
 /* Gating */
 #define FFM_GATING_SOFTMAX 0
@@ -315,7 +316,10 @@ int ffm_grouped_gemm_fp8(const void* Aq, const float* a_scale, const void* Bq, c
  *   int64 [e_local * ep][4] + combine_end (this rank's grouped layout -> the origins' sender order), padding
  *   int64 [e_local][4] + padding_end (rows of its own layout to zero), tile_start int32 [e_local + 1] for the grouped
  *   GEMM, totals int64 [4] = {rows sent, rows received, padding rows, grouped rows}. With it a forward pass needs no
- *   host read of the counts and can be captured in a CUDA graph.
+ *   host read of the counts and can be captured in a CUDA graph. max_grouped_rows (0 = no bound) is the size of every
+ *   rank's receive buffer in rows: if ANY rank's grouped layout would exceed it, every rank (they all see the same
+ *   counts) writes tables that move nothing (all run lengths, totals and tile_start zero) and sets
+ *   FFM_STATUS_EP_OVERFLOW in *status, so no row is ever stored past a buffer.
  * ffm_p2p_signal_wait: all ranks call it with the same, growing epoch after their pushes: stores epoch into
  *   slot [my_rank] of every rank's flag array (release), then waits (bounded by wait_cycles, 0 = default) until its
  *   own array holds epoch in every slot (acquire). Kernels enqueued after it may read what the peers pushed.
@@ -336,7 +340,7 @@ int ffm_p2p_push_rows_dev(const void* src, const int32_t* src_index, int index_d
                           ffm_stream_t stream);
 int ffm_p2p_plan(const int32_t* counts, int ep, int e_local, int rank, int64_t* dispatch, int64_t* dispatch_end,
                  int64_t* combine, int64_t* combine_end, int64_t* padding, int64_t* padding_end, int32_t* tile_start,
-                 int64_t* totals, ffm_stream_t stream);
+                 int64_t* totals, int64_t max_grouped_rows, int32_t* status, ffm_stream_t stream);
 int ffm_p2p_signal_wait_dev(void* const* flag_arrays, int my_rank, int world, uint32_t* epoch_counter,
                             int32_t* status, long long wait_cycles, ffm_stream_t stream);
 int ffm_p2p_signal_wait(void* const* flag_arrays, int my_rank, int world, uint32_t epoch, int32_t* status,

@@ -308,6 +308,28 @@ def main():
             for run in got:
                 for i, (a_, b_) in enumerate(zip(run, want)):
                     assert torch.equal(a_, b_), f"static training differs from the host-planned path (tensor {i}, full={full})"
+        # a declared bound on the rows a rank may receive: generous -> same results; too small -> the call moves
+        # nothing, status 106 on every rank, nothing stored out of bounds, and the next call works again
+        want = train(h, go, True)
+        ffm.set_ep_static_forward(bound, max_recv_rows=2 * k * bound)
+        got = train(h, go, True)
+        ops.check_status()
+        for i, (a_, b_) in enumerate(zip(got, want)):
+            assert torch.equal(a_, b_), f"bounded static mode differs (tensor {i})"
+        ffm.set_ep_static_forward(bound, max_recv_rows=64)
+        with torch.no_grad():
+            ffm.fused_moe(h, g, wu_l, wd_l, top_k=k, ep_group=group)
+        torch.cuda.synchronize()
+        try:
+            ops.check_status()
+            raise AssertionError("an overflow of the declared bound must set the status word")
+        except RuntimeError as exc:
+            assert "106" in str(exc), str(exc)
+        ffm.set_ep_static_forward(bound)
+        got = train(h, go, True)
+        ops.check_status()
+        for i, (a_, b_) in enumerate(zip(got, want)):
+            assert torch.equal(a_, b_), f"static mode after an overflow differs (tensor {i})"
         # one captured step, replayed on other tokens
         ffm.set_ep_static_forward(bound)
         statics = [t.clone().requires_grad_() for t in (h, g, wu_l, wd_l, sg, su, sd)]
