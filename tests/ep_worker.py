@@ -311,7 +311,7 @@ def main():
         # a declared bound on the rows a rank may receive: generous -> same results; too small -> the call moves
         # nothing, status 106 on every rank, nothing stored out of bounds, and the next call works again
         want = train(h, go, True)
-        ffm.set_ep_static_forward(bound, max_recv_rows=2 * k * bound)
+        ffm.set_ep_static_forward(bound, max_recv_rows=(3 * k * bound) // 2)
         got = train(h, go, True)
         ops.check_status()
         for i, (a_, b_) in enumerate(zip(got, want)):
