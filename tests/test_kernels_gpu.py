@@ -413,11 +413,30 @@ def test_device_exchange_plan_matches_host_plan(ep, e_local):
         p, pe = torch.empty(e_local, 4, **i64), torch.empty(e_local, **i64)
         ts = torch.empty(e_local + 1, dtype=torch.int32, device=DEV)
         tot = torch.empty(4, **i64)
-        rc = lib.ffm_p2p_plan(Cd.data_ptr(), ep, e_local, rank, d.data_ptr(), de.data_ptr(), c.data_ptr(),
-                              ce.data_ptr(), p.data_ptr(), pe.data_ptr(), ts.data_ptr(), tot.data_ptr(),
-                              torch.cuda.current_stream().cuda_stream)
-        assert rc == 0
+        st = ops.status_tensor(torch.device("cuda", torch.cuda.current_device()))
+        stream = torch.cuda.current_stream().cuda_stream
+        largest = int(host.rows_grouped.max())
+
+        def plan(bound):
+            return lib.ffm_p2p_plan(Cd.data_ptr(), ep, e_local, rank, d.data_ptr(), de.data_ptr(), c.data_ptr(),
+                                    ce.data_ptr(), p.data_ptr(), pe.data_ptr(), ts.data_ptr(), tot.data_ptr(), bound,
+                                    st.data_ptr(), stream)
+
+        # a bound below the largest grouped layout of ANY rank: tables that move nothing, status 106
+        assert plan(largest - 256) == 0
         torch.cuda.synchronize()
+        assert int(d[:, 2].sum()) == 0 and int(c[:, 2].sum()) == 0 and int(p[:, 2].sum()) == 0
+        assert tot.cpu().tolist() == [0, 0, 0, 0] and ts.cpu().tolist() == [0] * (e_local + 1)
+        with pytest.raises(RuntimeError, match="106"):
+            ops.check_status()
+        # a bound that fits (and no bound): the full plan
+        assert plan(largest) == 0
+        torch.cuda.synchronize()
+        ops.check_status()
+        full = [x.clone() for x in (d, de, c, ce, p, pe, ts, tot)]
+        assert plan(0) == 0
+        torch.cuda.synchronize()
+        assert all(torch.equal(a, b) for a, b in zip(full, (d, de, c, ce, p, pe, ts, tot)))
 
         def nonempty(seg, end):
             seg, end = seg.cpu().numpy(), end.cpu().numpy()
