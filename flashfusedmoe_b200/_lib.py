@@ -65,6 +65,7 @@ SIGNATURES = {
     "ffm_compact_positions": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p, c_void_p,
                                       c_void_p]),
     "ffm_p2p_push": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "ffm_p2p_set_local_only": (c_int, [c_int]),
     "ffm_p2p_push_rows": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_void_p, c_void_p, c_int, c_int64, c_void_p, c_int,
                                   c_void_p]),
     "ffm_p2p_push_rows_dev": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_int64,

@@ -60,7 +60,8 @@ __global__ void __launch_bounds__(256) p2p_rows_kernel(const uint8_t* __restrict
                                                        const long long* __restrict__ segments,
                                                        const long long* __restrict__ seg_end, int n_segments,
                                                        long long total_rows,
-                                                       const long long* __restrict__ total_rows_dev, RowBases bases) {
+                                                       const long long* __restrict__ total_rows_dev, RowBases bases,
+                                                       int only_dst) {
   if (total_rows_dev != nullptr) total_rows = *total_rows_dev;
   const int warps = blockDim.x >> 5;
   const int warp = threadIdx.x >> 5;
@@ -85,8 +86,12 @@ __global__ void __launch_bounds__(256) p2p_rows_kernel(const uint8_t* __restrict
       const long long* seg = segments + 4LL * lo;
       long long src_row = __ldg(seg) + j;
       if (src_index != nullptr) src_row = __ldg(src_index + src_row) / index_div;
-      my_dst = reinterpret_cast<unsigned long long>(bases.base[__ldg(seg + 3)] + (__ldg(seg + 1) + j) * row_bytes);
-      my_src = src != nullptr ? reinterpret_cast<unsigned long long>(src + src_row * row_bytes) : 0ull;
+      const long long dst_rank = __ldg(seg + 3);
+      // (measurement aid, see ffm_p2p_set_local_only: rows bound for another buffer are left where they are)
+      if (only_dst < 0 || dst_rank == only_dst) {
+        my_dst = reinterpret_cast<unsigned long long>(bases.base[dst_rank] + (__ldg(seg + 1) + j) * row_bytes);
+        my_src = src != nullptr ? reinterpret_cast<unsigned long long>(src + src_row * row_bytes) : 0ull;
+      }
     }
     const uint4* s[ROWS_PER_WARP];
     uint4* d[ROWS_PER_WARP];
@@ -249,6 +254,11 @@ __global__ void __launch_bounds__(256) p2p_plan_kernel(const int32_t* __restrict
   }
 }
 
+// Measurement aid: >= 0 makes the row kernels skip every row whose destination buffer index differs from it (with
+// the caller's own rank: local rows still move, nothing crosses NVLink), so that a step can be timed without the
+// payload of its exchanges while every kernel, barrier and local copy still runs. Results are then meaningless.
+int g_only_dst = -1;
+
 struct SignalArgs {
   uint32_t* flags[FFM_P2P_MAX_PEERS];  // flag array of every rank (index = rank); [my_rank] is local memory
 };
@@ -285,6 +295,12 @@ __global__ void p2p_signal_kernel(SignalArgs a, int my_rank, int world, uint32_t
 }  // namespace ffm
 
 using namespace ffm;
+
+extern "C" int ffm_p2p_set_local_only(int buffer_index) {
+  const int old = g_only_dst;
+  g_only_dst = buffer_index < 0 ? -1 : buffer_index;
+  return old;
+}
 
 extern "C" int ffm_p2p_push(int n_segments, const void* const* src, void* const* dst, const int64_t* bytes,
                             ffm_stream_t stream) {
@@ -334,7 +350,7 @@ extern "C" int ffm_p2p_push_rows(const void* src, const int32_t* src_index, int 
   if (blocks > 148LL * 8) blocks = 148LL * 8;
   p2p_rows_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint8_t*>(src), src_index, index_div, row_bytes, reinterpret_cast<const long long*>(segments),
-      reinterpret_cast<const long long*>(seg_end), n_segments, total_rows, nullptr, b);
+      reinterpret_cast<const long long*>(seg_end), n_segments, total_rows, nullptr, b, g_only_dst);
   return cudaGetLastError() == cudaSuccess ? FFM_OK : FFM_ERR_LAUNCH;
 }
 
@@ -358,7 +374,8 @@ extern "C" int ffm_p2p_push_rows_dev(const void* src, const int32_t* src_index, 
   if (blocks > 148LL * 8) blocks = 148LL * 8;
   p2p_rows_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint8_t*>(src), src_index, index_div, row_bytes, reinterpret_cast<const long long*>(segments),
-      reinterpret_cast<const long long*>(seg_end), n_segments, 0, reinterpret_cast<const long long*>(total_rows_dev), b);
+      reinterpret_cast<const long long*>(seg_end), n_segments, 0, reinterpret_cast<const long long*>(total_rows_dev), b,
+      g_only_dst);
   return cudaGetLastError() == cudaSuccess ? FFM_OK : FFM_ERR_LAUNCH;
 }
 

@@ -114,9 +114,13 @@ def _expert_ffn_forward(Xg, wu, wd, E, tile_start, D, H, activation, keep, small
 
 
 def set_ep_dry_exchange(enable):
-    """Benchmark switch: skip the payload of the expert-parallel exchanges (results are then meaningless)."""
+    """Benchmark switch: skip the payload of the expert-parallel exchanges (results are then meaningless). In
+    host-sync-free mode the row kernels then move local rows only and every barrier still runs; the host-planned
+    path skips its exchange kernels altogether."""
     global _EP_DRY_EXCHANGE
     _EP_DRY_EXCHANGE = bool(enable)
+    if not enable:
+        _lib.load().ffm_p2p_set_local_only(-1)
 
 _side_streams = {}
 _dense_tile_start = {}
@@ -636,16 +640,16 @@ class _FusedMoEEPStaticFunction(torch.autograd.Function):
         t = px.plan_dev(C, El, max_grouped_rows=cap_rows if bounded else 0)
         cpos, src_c = _compact_send_map(routing, T)
         tot = t["totals"]
-        dry = _EP_DRY_EXCHANGE   # measurement aid: the row exchanges move nothing and their barriers are skipped
-        if not dry:
-            px.push_rows_dev(h, src_c, k, rb, t["dispatch"], t["dispatch_end"], tot[0:1], T, 0)
+        # measurement aid: with the dry switch on, the row kernels leave out every row bound for another GPU (local rows,
+        # barriers and everything else still run)
+        _lib.load().ffm_p2p_set_local_only(px.rank if _EP_DRY_EXCHANGE else -1)
+        px.push_rows_dev(h, src_c, k, rb, t["dispatch"], t["dispatch_end"], tot[0:1], T, 0)
         if need_grad:
             # the weight-gradient GEMMs sum over whole 64-row blocks: the padding rows of the grouped layout are zeroed
             # (without a backward pass nothing sums over them, and a GEMM row only depends on its own input row)
             px.push_rows_dev(None, None, 1, rb, t["padding"], t["padding_end"], tot[2:3], 256 * El, 0,
                              name="zero_padding")
-        if not dry:
-            px.barrier_dev()
+        px.barrier_dev()
         Xg = px.region_view(0, cap_rows, D, h.dtype)
         if need_grad:
             Xg = px.keep_rows_dev(Xg, tot[3:4], cap_rows)   # saved for backward; the region is overwritten by the next call
@@ -655,9 +659,8 @@ class _FusedMoEEPStaticFunction(torch.autograd.Function):
         act, pre = ops.grouped_gemm_glu(Xg, wu, wu.view(-1, D)[H:], 2 * H, El, t["tile_start"], D, H, cfg.activation,
                                         want_preact=need_grad, **small)
         Y = ops.grouped_gemm(act, wd, _lib.B_KMAJOR, El, t["tile_start"], H, D, **small)
-        if not dry:
-            px.push_rows_dev(Y, None, 1, rb, t["combine"], t["combine_end"], tot[1:2], cap_rows, 1)
-            px.barrier_dev()
+        px.push_rows_dev(Y, None, 1, rb, t["combine"], t["combine_end"], tot[1:2], cap_rows, 1)
+        px.barrier_dev()
         returned = px.region_view(1, T, D, h.dtype)
         if need_grad:
             returned = returned.clone()
@@ -723,15 +726,13 @@ class _FusedMoEEPStaticFunction(torch.autograd.Function):
         ready2 = torch.cuda.Event()
         ready2.record()
         region = _backward_region(group)
-        dry = _EP_DRY_EXCHANGE
+        _lib.load().ffm_p2p_set_local_only(px.rank if _EP_DRY_EXCHANGE else -1)
         with torch.cuda.stream(a2a):
             a2a.wait_event(ready2)
-            if not dry:
-                px.push_rows_dev(gYw, None, 1, rb, t["dispatch"], t["dispatch_end"], tot[0:1], T, region)
+            px.push_rows_dev(gYw, None, 1, rb, t["dispatch"], t["dispatch_end"], tot[0:1], T, region)
             px.push_rows_dev(None, None, 1, rb, t["padding"], t["padding_end"], tot[2:3], 256 * El, region,
                              name="zero_padding")
-            if not dry:
-                px.barrier_dev()
+            px.barrier_dev()
         a2a_done = torch.cuda.Event()
         a2a_done.record(a2a)
         gYw.record_stream(a2a)
@@ -758,9 +759,8 @@ class _FusedMoEEPStaticFunction(torch.autograd.Function):
         d_wu = _grouped_wgrad(gU, t["Xg"], El, ts_l, scale=inv_ep)
         if cfg.ep_full_input_grad:
             dXg = ops.grouped_gemm(gU, wu, _lib.B_NMAJOR, El, ts_l, 2 * H, D)
-            if not dry:
-                px.push_rows_dev(dXg, None, 1, rb, t["combine"], t["combine_end"], tot[1:2], cap_rows, 1)
-                px.barrier_dev()
+            px.push_rows_dev(dXg, None, 1, rb, t["combine"], t["combine_end"], tot[1:2], cap_rows, 1)
+            px.barrier_dev()
             d_send = px.region_view(1, T, D, h.dtype)
             dH = dH + ops.combine_forward(d_send, t["cpos"], None, N, k)
         s_grads = (None, None, None)

@@ -331,6 +331,10 @@ int ffm_grouped_gemm_fp8(const void* Aq, const float* a_scale, const void* Bq, c
 #define FFM_P2P_MAX_PEERS 16
 int ffm_p2p_push(int n_segments, const void* const* src, void* const* dst, const int64_t* bytes,
                  ffm_stream_t stream);
+/* Measurement aid: buffer_index >= 0 makes ffm_p2p_push_rows(_dev) skip rows bound for any other destination buffer
+ * (pass the caller's rank: local rows move, nothing crosses NVLink); -1 restores normal operation. Returns the old
+ * value. The difference between a step timed this way and a normal one is the exposed exchange time. */
+int ffm_p2p_set_local_only(int buffer_index);
 int ffm_p2p_push_rows(const void* src, const int32_t* src_index, int index_div, int64_t row_bytes,
                       const int64_t* segments, const int64_t* seg_end, int n_segments, int64_t total_rows,
                       void* const* dst_bases, int n_bases, ffm_stream_t stream);

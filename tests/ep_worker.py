@@ -316,9 +316,10 @@ def main():
         ops.check_status()
         for i, (a_, b_) in enumerate(zip(got, want)):
             assert torch.equal(a_, b_), f"bounded static mode differs (tensor {i})"
-        ffm.set_ep_static_forward(bound, max_recv_rows=64)
+        # (four times the tokens: every expert then needs several 256-row segments, far beyond 64 rows + one segment each)
+        ffm.set_ep_static_forward(4 * bound, max_recv_rows=64)
         with torch.no_grad():
-            ffm.fused_moe(h, g, wu_l, wd_l, top_k=k, ep_group=group)
+            ffm.fused_moe(torch.cat([h] * 4), g, wu_l, wd_l, top_k=k, ep_group=group)
         torch.cuda.synchronize()
         try:
             ops.check_status()
