@@ -100,6 +100,14 @@ def check_status(device=None):
     dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
     st = status_tensor(dev)
     code = int(st.item())
+    # an asynchronous copy of the word queued by poll_status() carries the same information: drop it, so that a failure
+    # reported here is not reported a second time by a later fused_moe() call
+    key = dev.index if dev.index is not None else torch.cuda.current_device()
+    entry = _status_host.get(key)
+    if entry is not None and entry["pending"]:
+        entry["done"].synchronize()
+        entry["pending"] = False
+        entry["host"][0] = 0
     if code != 0:
         st.zero_()
         raise RuntimeError(f"libffmoe device status {code}: {_lib.error_string(code)}")
