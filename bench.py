@@ -852,7 +852,7 @@ def main():
                 "gemm_launches": gemm_launches, "gemm_ms_per_step": gemm_ms / K,
                 "algorithmic_tflop_per_step": fl["gemm"] / 1e12,
                 "other_kernels_ms_per_step": {n: v[1] / K for n, v in kt.items()
-                                              if n not in gemm_names and n != "all_to_all"},
+                                              if n not in gemm_names and n not in ("all_to_all", "exchange_rows")},
             },
         }
         if eager is not None:
@@ -875,8 +875,15 @@ def main():
             ref_ms = ms if (dry_mode == "replayed" or eager is None) else eager["ms_per_step"] * K
             gbs = a2a_bytes / (a2a_ms * 1e-3) / 1e9 if a2a_ms > 0 else None
             link = (nvlink or {}).get("copy_engine_gbs")
+            # the row kernels alone (no barriers, no waiting for peers): what the stores achieve over NVLink; their
+            # launches also move this rank's local rows, which the byte count leaves out
+            rows_ms = kt["exchange_rows"][1] if "exchange_rows" in kt else None
+            rows_gbs = a2a_bytes / (rows_ms * 1e-3) / 1e9 if rows_ms else None
             line["expert_parallel"] = {"all_to_all_calls_per_step": n_a2a / K, "all_to_all_ms_per_step": a2a_ms / K,
                                        "bytes_sent_per_step": a2a_bytes / K, "achieved_gbs_per_direction": gbs,
+                                       "row_kernels_ms_per_step": (rows_ms / K) if rows_ms else None,
+                                       "row_kernels_gbs_per_direction": rows_gbs,
+                                       "row_kernels_frac_of_measured_peer_copy": (rows_gbs / link) if rows_gbs and link else None,
                                        "nvlink_peer_copy": nvlink,
                                        "nvlink_frac_of_measured_peer_copy": (gbs / link) if gbs and link else None,
                                        "nvlink_frac_of_nominal_900": (gbs / 900.0) if gbs else None,

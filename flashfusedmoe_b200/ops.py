@@ -40,9 +40,10 @@ def set_timer(timer):
 class _Launch:
     """Counts `kernels` launches under `name`; with a timer installed also brackets them with events."""
 
-    def __init__(self, name, kernels=1):
+    def __init__(self, name, kernels=1, also=None):
         self.name = name
         self.kernels = kernels
+        self.also = also   # second timer bucket for the same event pair (a finer breakdown of `name`)
 
     def __enter__(self):
         global launch_count
@@ -57,6 +58,8 @@ class _Launch:
             end = torch.cuda.Event(enable_timing=True)
             end.record()
             _timer.events.setdefault(self.name, []).append((self.start, end))
+            if self.also is not None:
+                _timer.events.setdefault(self.also, []).append((self.start, end))
         return False
 
 

@@ -184,7 +184,7 @@ class PeerExchange:
         n = self.world
         bases = (ctypes.c_void_p * n)(*[self.region_ptr(d, region) for d in range(n)])
         ops.a2a_bytes_sent += remote_rows * row_bytes
-        with ops._Launch(name, 1):
+        with ops._Launch(name, 1, also="exchange_rows" if name == "all_to_all" else None):
             _lib.check(lib.ffm_p2p_push_rows(0 if src is None else src.data_ptr(),
                                              0 if src_index is None else src_index.data_ptr(), int(index_div),
                                              int(row_bytes), seg_dev.data_ptr(), end_dev.data_ptr(), int(n_segments),
@@ -256,7 +256,7 @@ class PeerExchange:
         lib = _lib.load()
         n = self.world
         bases = (ctypes.c_void_p * n)(*[self.region_ptr(d, region) for d in range(n)])
-        with ops._Launch(name, 1):
+        with ops._Launch(name, 1, also="exchange_rows" if name == "all_to_all" else None):
             _lib.check(lib.ffm_p2p_push_rows_dev(0 if src is None else src.data_ptr(),
                                                  0 if src_index is None else src_index.data_ptr(), int(index_div),
                                                  int(row_bytes), seg.data_ptr(), seg_end.data_ptr(), int(seg.shape[0]),
