@@ -802,6 +802,12 @@ def main():
         gemm_ms = sum(kt[n][1] for n in gemm_names if n in kt)
         gemm_launches = sum(kt[n][0] for n in gemm_names if n in kt)
         achieved = fl["gemm"] * K / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else None
+        # the same without the dW_down launches that carry the GLU backward as a passenger (their event time is the
+        # whole launch, their FLOPs are dW_down's alone): the rate of the GEMM kernel when it runs by itself
+        pass_ms = kt["gemm_wgrad_passenger"][1] if "gemm_wgrad_passenger" in kt else 0.0
+        pass_flops = 2.0 * tokens * CFG["d_model"] * (CFG["top_k"] * CFG["ffn_dim"] // 2 + CFG["shared_ffn_dim"] // 2)
+        alone = ((fl["gemm"] - pass_flops) * K / ((gemm_ms - pass_ms) * 1e-3) / 1e12
+                 if pass_ms > 0 and gemm_ms > pass_ms else None)
         value = tokens * world * K / (ms * 1e-3)
         sm_mhz = (clocks or {}).get("sm_mhz")
         sm_max = (clocks or {}).get("sm_max_mhz")
@@ -849,10 +855,13 @@ def main():
                 "frac_of_nominal_2250": (achieved / 2250.0) if achieved else None,
                 "frac_of_hw_rate_at_sampled_clock": (achieved / hw_rate) if achieved and hw_rate else None,
                 "whole_step_tflops": fl["gemm"] * K / (ms * 1e-3) / 1e12,
+                "achieved_without_passenger_launches": alone,
+                "frac_without_passenger_launches": (alone / peaks["tflops_burst"]) if alone else None,
+                "passenger_launch_ms_per_step": pass_ms / K,
                 "gemm_launches": gemm_launches, "gemm_ms_per_step": gemm_ms / K,
                 "algorithmic_tflop_per_step": fl["gemm"] / 1e12,
                 "other_kernels_ms_per_step": {n: v[1] / K for n, v in kt.items()
-                                              if n not in gemm_names and n not in ("all_to_all", "exchange_rows")},
+                                              if n not in gemm_names and n not in ("all_to_all", "exchange_rows", "gemm_wgrad_passenger")},
             },
         }
         if eager is not None:

@@ -353,7 +353,7 @@ def grouped_gemm_wgrad_glu_backward(A, B, groups, tile_start, d_act, preact, act
     rows, H = d_act.shape
     out = torch.empty(groups, M, n_out, dtype=torch.bfloat16, device=A.device)
     gU = torch.empty(rows, 2 * H, dtype=torch.bfloat16, device=A.device)
-    with _Launch("gemm_wgrad", 1):
+    with _Launch("gemm_wgrad", 1, also="gemm_wgrad_passenger"):
         rc = lib.ffm_grouped_gemm_wgrad_glu_backward(_ptr(A), _ptr(B), groups, _ptr(tile_start), rows_cap, M, n_out,
                                                      float(scale), _ptr(out), _ptr(d_act), _ptr(preact), rows, H,
                                                      _lib.ACTIVATION[activation], _ptr(gU),
