@@ -59,6 +59,13 @@ constexpr int MAX_STAGES = 6;
 constexpr int SMEM_LIMIT = 232448;  // 227 KiB of dynamic shared memory per CTA
 
 enum { EPI_PLAIN = 0, EPI_GLU = 1, EPI_GLUBWD = 2 };
+// The GLU-backward epilogue does about 16 instructions and two MUFU operations per accumulator element, too much for
+// one warp per scheduler inside a tile's main loop: four helper warps (one more per TMEM lane quarter) take the upper
+// 32 columns of every 64-column step.
+constexpr int GLUBWD_HELPER_THREADS = 128;
+__host__ __device__ constexpr int gemm_threads(int epi, int pass) {
+  return GEMM_THREADS + pass * PASSENGER_THREADS + (epi == EPI_GLUBWD ? GLUBWD_HELPER_THREADS : 0);
+}
 
 // Ring depth against staging depth for CTA pairs. Measured at 8 x 4096 rows, D 1024, H 2048: every split from 4 to
 // 6 stages runs within 3 % of the others alone (the GEMMs sit at the board's power limit, not at a pipeline limit).
@@ -78,19 +85,21 @@ enum { EPI_PLAIN = 0, EPI_GLU = 1, EPI_GLUBWD = 2 };
 // Shared-memory budget per tile shape and epilogue: ring stages against staging boxes per epilogue warp.
 //   CTA pair, plain: 6 stages x 32 KiB + 2 boxes    CTA pair, GLU: 5 stages x 32 KiB + 3 boxes
 //   one CTA,  plain: 4 stages x 48 KiB + 2 boxes    one CTA,  GLU: 3 stages x 48 KiB + 3 boxes
-//   GLU backward epilogue (EPI_GLUBWD): 5 (one CTA: 3) stages + 2 x 2 boxes
+//   GLU backward epilogue (EPI_GLUBWD): 4 stages + 3 x 2 boxes (one CTA: 3 stages + 2 x 2 boxes)
 // A GLU step stores three boxes (activation, gate, up) as one bulk group; a plain step stores one box; a GLU backward
 // step stores two (gate gradient, up gradient).
 template <int CTA2, int EPI>
 struct Shape {
   static constexpr int STAGES = EPI == EPI_GLU      ? (CTA2 ? FFM_TUNE_PG_STAGES : 3)
-                                : EPI == EPI_GLUBWD ? (CTA2 ? 5 : 3)
+                                : EPI == EPI_GLUBWD ? (CTA2 ? 4 : 3)
                                                     : (CTA2 ? FFM_TUNE_PP_STAGES : 4);
   static constexpr int B_STAGE_BYTES = (CTA2 ? 128 : 256) * BK * 2;
   static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
   static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
   static constexpr int BOXES_PER_STEP = EPI == EPI_GLU ? 3 : (EPI == EPI_GLUBWD ? 2 : 1);
-  static constexpr int STEPS_BUFFERED = EPI == EPI_GLU ? (CTA2 ? FFM_TUNE_PG_STEPS : 1) : (CTA2 ? FFM_TUNE_PP_STEPS : 2);
+  static constexpr int STEPS_BUFFERED = EPI == EPI_GLU      ? (CTA2 ? FFM_TUNE_PG_STEPS : 1)
+                                        : EPI == EPI_GLUBWD ? (CTA2 ? 3 : 2)
+                                                            : (CTA2 ? FFM_TUNE_PP_STEPS : 2);
   static constexpr int STG_WARP_BYTES = BOXES_PER_STEP * STEPS_BUFFERED * BOX_BYTES;
   static constexpr int STG_BYTES = EPI_WARPS * STG_WARP_BYTES;
   static constexpr int SMEM_BYTES = RING_BYTES + STG_BYTES + SMEM_CTRL_BYTES + 1024;  // + 1 KiB alignment slack
@@ -142,6 +151,8 @@ struct Ctrl {
   unsigned long long acc_empty_bar[NUM_ACC];
   uint32_t tmem_base;
   int abort_flag;
+  unsigned long long pre_bar[EPI_WARPS][3];  // GLU-backward epilogue: "pre-activation boxes have landed", per warp and buffer
+  unsigned long long help_bar[EPI_WARPS][3];  // ... and "the helper warp has written its half of the step"
   int tile_start[MAX_GROUPS + 1];
 };
 static_assert(sizeof(Ctrl) <= SMEM_CTRL_BYTES, "control block too large");
@@ -245,6 +256,18 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const void* map, 
       "[%2];" ::"r"(dst),
       "l"(map), "r"(bar), "r"(c0), "r"(c1)
       : "memory");
+}
+
+// 3-D TMA load into this CTA's shared memory (no cluster broadcast), completing on one of its own mbarriers.
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* map, uint32_t bar, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+
+__device__ __forceinline__ void ld_shared_v4(uint32_t addr, uint4& v) {
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
 }
 
 __device__ __forceinline__ void tma_store_3d(const void* map, uint32_t src, int c0, int c1, int c2) {
@@ -378,9 +401,53 @@ __device__ __forceinline__ void passenger_glu_backward(const GemmParams& p, long
   }
 }
 
+// Eight columns of the GLU backward in the dAct epilogue: 16 bytes of this lane's row in the staged gate and up
+// pre-activation boxes (128-byte swizzle) are read, combined with the bf16-rounded accumulator values v, and
+// overwritten with the gate and up gradients.
+template <int ACT>
+__device__ __forceinline__ void glu_backward_8(const uint32_t (&v)[8], float scale, uint32_t buf, uint32_t o) {
+  uint4 g4, u4;
+  ld_shared_v4(buf + o, g4);
+  ld_shared_v4(buf + BOX_BYTES + o, u4);
+  const uint32_t gw4[4] = {g4.x, g4.y, g4.z, g4.w};
+  const uint32_t uw4[4] = {u4.x, u4.y, u4.z, u4.w};
+  uint32_t og[4], ou[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 da = unpack_bf16x2(
+        pack_bf16x2(__uint_as_float(v[2 * j]) * scale, __uint_as_float(v[2 * j + 1]) * scale));
+    const float2 gf = unpack_bf16x2(gw4[j]);
+    const float2 uf = unpack_bf16x2(uw4[j]);
+    const float2 r0 = glu_bwd(ACT, da.x, gf.x, uf.x);
+    const float2 r1 = glu_bwd(ACT, da.y, gf.y, uf.y);
+    og[j] = pack_bf16x2(r0.x, r1.x);
+    ou[j] = pack_bf16x2(r0.y, r1.y);
+  }
+  st_shared_v4(buf + o, og[0], og[1], og[2], og[3]);
+  st_shared_v4(buf + BOX_BYTES + o, ou[0], ou[1], ou[2], ou[3]);
+}
+
+// Half of a 64-column step (four 16-byte column groups from q_begin): the accumulator comes out of TMEM eight columns
+// at a time, one load ahead of the math, in a loop that stays rolled (two loads per trip) so that its body stays
+// resident in the instruction cache.
+template <int ACT>
+__device__ __forceinline__ void glu_backward_step(uint32_t tcol, float scale, uint32_t buf, int lane, int q_begin) {
+  uint32_t a[8], b[8];
+  tmem_ld_32x8(tcol + q_begin * 8, a);
+#pragma unroll 1
+  for (int q = q_begin; q < q_begin + 4; q += 2) {
+    tmem_ld_wait();
+    tmem_ld_32x8(tcol + (q + 1) * 8, b);
+    glu_backward_8<ACT>(a, scale, buf, box_offset(lane, q));
+    tmem_ld_wait();
+    if (q + 2 < q_begin + 4) tmem_ld_32x8(tcol + (q + 2) * 8, a);
+    glu_backward_8<ACT>(b, scale, buf, box_offset(lane, q + 1));
+  }
+}
+
 // FP8 = 1: A and B hold e4m3 bytes, K-major only; a stage row is still 128 bytes, i.e. 128 K elements per block.
 template <int A_MN, int B_MN, int EPI, int GROUPK, int CTA2, int PASS = 0, int FP8 = 0>
-__global__ void __launch_bounds__(GEMM_THREADS + PASS * PASSENGER_THREADS, 1)
+__global__ void __launch_bounds__(gemm_threads(EPI, PASS), 1)
 ffm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB0,
                 const __grid_constant__ CUtensorMap tmB1, const __grid_constant__ CUtensorMap tmC,
                 const __grid_constant__ CUtensorMap tmC2, const GemmParams p) {
@@ -409,7 +476,16 @@ ffm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     }
     for (int a = 0; a < NUM_ACC; ++a) {
       mbar_init(smem_u32(&ctrl->acc_full_bar[a]), 1);
-      mbar_init(smem_u32(&ctrl->acc_empty_bar[a]), EPI_WARPS * (CTA2 ? 2 : 1));  // one arrival per epilogue warp
+      // one arrival per epilogue warp (helpers included)
+      mbar_init(smem_u32(&ctrl->acc_empty_bar[a]), (EPI == EPI_GLUBWD ? 2 : 1) * EPI_WARPS * (CTA2 ? 2 : 1));
+    }
+    if (EPI == EPI_GLUBWD) {
+      for (int w = 0; w < EPI_WARPS; ++w) {
+        for (int b = 0; b < 3; ++b) {
+          mbar_init(smem_u32(&ctrl->pre_bar[w][b]), 1);
+          mbar_init(smem_u32(&ctrl->help_bar[w][b]), 1);
+        }
+      }
     }
     ctrl->abort_flag = 0;
     fence_barrier_init();
@@ -468,12 +544,13 @@ ffm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       bool ok = true;
       while (ok && walker.next(t)) {
         const int m0 = t.m_tile * BM;
+#ifdef FFM_TUNE_GLUBWD_L2_PREFETCH
         if (EPI == EPI_GLUBWD) {
-          // the epilogue of this tile reads the matching pre-activations (gate and up columns) straight from global
-          // memory: pull them into L2 now, a whole main loop ahead (tmC2 maps them with a 256 x 128 box)
+          // pull the tile's pre-activations into L2 a whole main loop ahead (tmC2 maps them with a 256 x 128 box)
           tma_prefetch_l2_2d(&tmC2, t.n_block * BN, m0);
           tma_prefetch_l2_2d(&tmC2, p.pz_h + t.n_block * BN, m0);
         }
+#endif
         for (int kb = 0; kb < t.k_blocks && ok; ++kb) {
           ok = mbar_wait_bounded(smem_u32(&ctrl->empty_bar[stage]), phase ^ 1u, abort_flag, p.status,
                                  FFM_STATUS_WAIT_PRODUCER, p.wait_cycles);
@@ -613,11 +690,15 @@ ffm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                            static_cast<long long>(blockIdx.x) * PASSENGER_THREADS + (threadIdx.x - GEMM_THREADS),
                            static_cast<long long>(gridDim.x) * PASSENGER_THREADS);
   } else {
-    // ================= epilogue (warps 2..5) =================
+    // ================= epilogue (warps 2..5; with the GLU backward also helper warps 6..9) =================
     const int quarter = warp & 3;  // TMEM lanes [32 * quarter, 32 * quarter + 32) belong to this warp
-    const uint32_t stg = stg_base + (warp - 2) * S::STG_WARP_BYTES;
+    const int wi = (warp - 2) & 3;  // staging area and barriers; a helper shares those of the warp of its quarter
+    const bool helper = EPI == EPI_GLUBWD && warp >= 2 + EPI_WARPS;
+    const uint32_t stg = stg_base + wi * S::STG_WARP_BYTES;
     constexpr int STEP_BYTES = S::BOXES_PER_STEP * BOX_BYTES;
     int step_slot = 0;  // staging slot of the next store step; advances per step actually stored
+    uint32_t pre_phase = 0u;  // GLU-backward epilogue: bit b = parity to wait for on buffer b's load barrier
+    uint32_t help_phase = 0u;  // the same for the helper's "half written" barriers (waited for by warps 2..5)
     TileWalker<GROUPK, CTA2> walker(p, ctrl->tile_start, rank);
     TileCoord t;
     int acc = 0;
@@ -627,6 +708,19 @@ ffm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       const int row0 = t.m_tile * BM + quarter * 32;  // first row of this warp's 32-row slab
       const int zdim = GROUPK ? t.group : 0;
       const bool have_acc = t.k_blocks > 0;
+      if (EPI == EPI_GLUBWD) {
+        // pre-activation boxes of this tile's first step, requested before the accumulator is waited for (the MMAs of
+        // this tile may still be running): wait until the store that last read this buffer has drained, then load
+        if (!helper && lane == 0) {
+          bulk_wait_read<S::STEPS_BUFFERED - 1>();  // the store that last read this buffer is STEPS_BUFFERED groups back
+          const uint32_t bar = smem_u32(&ctrl->pre_bar[wi][step_slot]);
+          const uint32_t buf = stg + step_slot * STEP_BYTES;
+          mbar_expect_tx(bar, STEP_BYTES);
+          tma_load_3d(buf, &tmB1, bar, t.n_block * BN, row0, 0);
+          tma_load_3d(buf + BOX_BYTES, &tmB1, bar, p.pz_h + t.n_block * BN, row0, 0);
+        }
+        __syncwarp();
+      }
       if (have_acc) {
         ok = mbar_wait_bounded(smem_u32(&ctrl->acc_full_bar[acc]), acc_phase, abort_flag, p.status,
                                FFM_STATUS_WAIT_EPILOGUE, p.wait_cycles);
@@ -708,83 +802,63 @@ ffm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         // The accumulator is dAct (gradient of the GLU output). Rounded to bf16 as the stand-alone dAct GEMM would
         // store it, it goes through the GLU backward with the saved pre-activations of the same rows and columns, and
         // the gate and up gradients leave as two boxes per 64-column step: dAct itself never touches memory.
-        // Each lane owns a row; its 32 gate and 32 up pre-activations of a chunk are four 16-byte loads each, issued
-        // one chunk ahead beside the TMEM load. They hit L2: the producer warp prefetched the tile's pre-activations
-        // when its main loop started.
+        // The pre-activations come in by TMA, one step (a gate box and an up box of 32 rows x 64 columns) ahead, into
+        // the boxes that the step's results are then written over and stored from (tmB1 maps them).
+        // The step loop is deliberately not unrolled and the activation is a template argument of the step's math:
+        // unrolled with the activation switch inlined at every element, the epilogue did not fit the instruction
+        // cache and its warps spent most of their time waiting for instructions (ncu: stall_no_instruction 4.9 per
+        // issue, 3.4 x the run time of the plain dAct GEMM).
         const int n0 = t.n_block * BN;
         const int Hh = p.pz_h;
-        const float scale = p.scale;
-        const long long r = static_cast<long long>(row0) + lane;
-        const bool row_ok = r < p.pz_rows;
-        const bf16* prow = p.pz_pre + r * 2 * Hh;
-        uint32_t v[2][32];
-        uint4 qg[2][4], qu[2][4];
-        tmem_ld_32x32(taddr, v[0]);
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const bool okc = row_ok && n0 < p.n_cols;
-          qg[0][q] = okc ? __ldg(reinterpret_cast<const uint4*>(prow + n0) + q) : make_uint4(0, 0, 0, 0);
-          qu[0][q] = okc ? __ldg(reinterpret_cast<const uint4*>(prow + Hh + n0) + q) : make_uint4(0, 0, 0, 0);
-        }
-#pragma unroll
-        for (int c = 0; c < BN / 32; ++c) {
-          tmem_ld_wait();
-          if (c + 1 < BN / 32) {
-            tmem_ld_32x32(taddr + (c + 1) * 32, v[(c + 1) & 1]);
-            const int cn = n0 + (c + 1) * 32;
-            const bool okc = row_ok && cn < p.n_cols;
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              qg[(c + 1) & 1][q] = okc ? __ldg(reinterpret_cast<const uint4*>(prow + cn) + q) : make_uint4(0, 0, 0, 0);
-              qu[(c + 1) & 1][q] =
-                  okc ? __ldg(reinterpret_cast<const uint4*>(prow + Hh + cn) + q) : make_uint4(0, 0, 0, 0);
+        const int steps = (p.n_cols - n0 >= BN) ? BN / 64 : (p.n_cols - n0 + 63) / 64;  // 64-column steps of this tile
+#pragma unroll 1
+        for (int st = 0; st < steps; ++st) {
+          const uint32_t buf = stg + step_slot * STEP_BYTES;
+          // next step's boxes into the next buffer of the rotation (the store that last read it lies
+          // STEPS_BUFFERED - 1 groups back, so the wait leaves the latest STEPS_BUFFERED - 2 stores alone)
+          if (st + 1 < steps && !helper && lane == 0) {
+            bulk_wait_read<(S::STEPS_BUFFERED >= 2 ? S::STEPS_BUFFERED - 2 : 0)>();
+            const int nslot = (step_slot + 1 == S::STEPS_BUFFERED) ? 0 : step_slot + 1;
+            const uint32_t nbar = smem_u32(&ctrl->pre_bar[wi][nslot]);
+            const uint32_t nbuf = stg + nslot * STEP_BYTES;
+            mbar_expect_tx(nbar, STEP_BYTES);
+            tma_load_3d(nbuf, &tmB1, nbar, n0 + (st + 1) * 64, row0, 0);
+            tma_load_3d(nbuf + BOX_BYTES, &tmB1, nbar, Hh + n0 + (st + 1) * 64, row0, 0);
+          }
+          const uint32_t parity = (pre_phase >> step_slot) & 1u;
+          ok = mbar_wait_bounded(smem_u32(&ctrl->pre_bar[wi][step_slot]), parity, abort_flag, p.status,
+                                 FFM_STATUS_WAIT_EPILOGUE, p.wait_cycles);
+          ok = __all_sync(0xffffffffu, ok ? 1 : 0) != 0;
+          if (!ok) break;
+          pre_phase ^= 1u << step_slot;
+          const int qb = helper ? 4 : 0;  // first 16-byte column group of this warp's half of the step
+          switch (p.pz_act) {
+            case FFM_ACT_SWIGLU: glu_backward_step<FFM_ACT_SWIGLU>(taddr + st * 64, p.scale, buf, lane, qb); break;
+            case FFM_ACT_GEGLU_TANH: glu_backward_step<FFM_ACT_GEGLU_TANH>(taddr + st * 64, p.scale, buf, lane, qb); break;
+            case FFM_ACT_RELU2: glu_backward_step<FFM_ACT_RELU2>(taddr + st * 64, p.scale, buf, lane, qb); break;
+            default: glu_backward_step<FFM_ACT_GEGLU_ERF>(taddr + st * 64, p.scale, buf, lane, qb); break;
+          }
+          fence_proxy_async();
+          __syncwarp();
+          if (helper) {
+            // the step's buffer is reused only after warp wi has stored it and loaded the next boxes into it, and this
+            // warp sees those through pre_bar: no wait in this direction
+            if (lane == 0) mbar_arrive(smem_u32(&ctrl->help_bar[wi][step_slot]));
+          } else {
+            ok = mbar_wait_bounded(smem_u32(&ctrl->help_bar[wi][step_slot]), (help_phase >> step_slot) & 1u, abort_flag,
+                                   p.status, FFM_STATUS_WAIT_EPILOGUE, p.wait_cycles);
+            ok = __all_sync(0xffffffffu, ok ? 1 : 0) != 0;
+            if (!ok) break;
+            help_phase ^= 1u << step_slot;
+            if (lane == 0) {
+              tma_store_3d(&tmC, buf, n0 + st * 64, row0, 0);
+              tma_store_3d(&tmC, buf + BOX_BYTES, Hh + n0 + st * 64, row0, 0);
+              bulk_commit();
             }
           }
-          const int col = n0 + (c >> 1) * 64;  // first column of this step's boxes
-          if (col < p.n_cols) {
-            const uint32_t buf = stg + step_slot * STEP_BYTES;
-            if ((c & 1) == 0) {
-              if (lane == 0) bulk_wait_read<S::STEPS_BUFFERED - 1>();
-              __syncwarp();
-            }
-            if (n0 + c * 32 < p.n_cols) {
-              uint32_t og[16], ou[16];
-#pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                const uint32_t gw4[4] = {qg[c & 1][q].x, qg[c & 1][q].y, qg[c & 1][q].z, qg[c & 1][q].w};
-                const uint32_t uw4[4] = {qu[c & 1][q].x, qu[c & 1][q].y, qu[c & 1][q].z, qu[c & 1][q].w};
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  const int i = q * 4 + j;
-                  const float2 da = unpack_bf16x2(pack_bf16x2(__uint_as_float(v[c & 1][2 * i]) * scale,
-                                                              __uint_as_float(v[c & 1][2 * i + 1]) * scale));
-                  const float2 gf = unpack_bf16x2(gw4[j]);
-                  const float2 uf = unpack_bf16x2(uw4[j]);
-                  const float2 r0 = glu_bwd(p.pz_act, da.x, gf.x, uf.x);
-                  const float2 r1 = glu_bwd(p.pz_act, da.y, gf.y, uf.y);
-                  og[i] = pack_bf16x2(r0.x, r1.x);
-                  ou[i] = pack_bf16x2(r0.y, r1.y);
-                }
-              }
-#pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                const uint32_t o = box_offset(lane, (c & 1) * 4 + q);
-                st_shared_v4(buf + o, og[4 * q], og[4 * q + 1], og[4 * q + 2], og[4 * q + 3]);
-                st_shared_v4(buf + BOX_BYTES + o, ou[4 * q], ou[4 * q + 1], ou[4 * q + 2], ou[4 * q + 3]);
-              }
-            }
-            if (c & 1) {
-              fence_proxy_async();
-              __syncwarp();
-              if (lane == 0) {
-                tma_store_3d(&tmC, buf, col, row0, 0);
-                tma_store_3d(&tmC, buf + BOX_BYTES, Hh + col, row0, 0);
-                bulk_commit();
-              }
-              if (++step_slot == S::STEPS_BUFFERED) step_slot = 0;
-            }
-          }
+          if (++step_slot == S::STEPS_BUFFERED) step_slot = 0;
         }
+        if (!ok) break;
       } else {
         // four steps of 64 columns (one box each), two 32-column chunks per step, TMEM loads one chunk ahead
         const int n0 = t.n_block * BN;
@@ -965,7 +1039,7 @@ int launch_gemm_shape(const CUtensorMap& tmA, const CUtensorMap& tmB0, const CUt
                       const CUtensorMap& tmC2, const GemmParams& p, long long max_units, cudaStream_t stream) {
   static int max_ctas = 0;  // persistent grid size, found once per instantiation
   auto kernel = ffm_gemm_kernel<A_MN, B_MN, EPI, GROUPK, CTA2, PASS, FP8>;
-  constexpr int threads = GEMM_THREADS + PASS * PASSENGER_THREADS;
+  constexpr int threads = gemm_threads(EPI, PASS);
   constexpr int smem_bytes = Shape<CTA2, EPI>::SMEM_BYTES;
   if (max_ctas == 0) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess) {
@@ -1291,6 +1365,8 @@ extern "C" int ffm_grouped_gemm_dact_glu_backward(const void* gY, const void* Wd
   if ((rc = make_map_2d(&tmB, Wd, static_cast<long long>(groups) * K, H, 64, 64)) != FFM_OK) return rc;
   if ((rc = make_out_map(&tmC, gU, 1, rows, 2LL * H)) != FFM_OK) return rc;
   if ((rc = make_prefetch_map(&tmP, preact, rows, 2LL * H)) != FFM_OK) return rc;
+  CUtensorMap tmL;  // the epilogue's loads of the pre-activations: 64 x 32 boxes, same swizzle as the stores
+  if ((rc = make_out_map(&tmL, const_cast<void*>(preact), 1, rows, 2LL * H)) != FFM_OK) return rc;
   GemmParams p = {};
   p.tile_start = tile_start;
   p.groups = groups;
@@ -1306,6 +1382,6 @@ extern "C" int ffm_grouped_gemm_dact_glu_backward(const void* gY, const void* Wd
   p.pz_rows = rows;
   p.pz_h = H;
   p.pz_act = activation;
-  return launch_gemm<0, 1, EPI_GLUBWD, 0>(tmA, tmB, tmB, tmC, tmP, p, (rows + BM - 1) / BM, p.n_tiles,
+  return launch_gemm<0, 1, EPI_GLUBWD, 0>(tmA, tmB, tmL, tmC, tmP, p, (rows + BM - 1) / BM, p.n_tiles,
                                           static_cast<cudaStream_t>(stream), tile_rows);
 }

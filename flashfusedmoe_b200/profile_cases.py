@@ -4,7 +4,7 @@
 
 Cases: route_forward permute combine_forward combine_backward glu_backward route_backward
        gemm_up_glu gemm_down gemm_dact gemm_dx gemm_wgrad_down gemm_wgrad_up
-       quantize_rows gemm_up_glu_fp8 gemm_down_fp8
+       quantize_rows gemm_up_glu_fp8 gemm_down_fp8 gemm_dact_glu_bwd
 Shape: D = 1024, H = 2048, top_k = 2 (E * rows_per_expert routed rows). Every case touches far more than the
 126 MB L2 and holds about 1 GB on the device. Prints the CUDA-event time per launch.
 """
@@ -53,6 +53,8 @@ def main():
                         4.0 * T * D * H),
         "gemm_down": (lambda: ops.grouped_gemm(act, Wd, _lib.B_KMAJOR, E, ts, H, D), 2.0 * T * D * H),
         "gemm_dact": (lambda: ops.grouped_gemm(X, Wd, _lib.B_NMAJOR, E, ts, D, H), 2.0 * T * D * H),
+        "gemm_dact_glu_bwd": (lambda: ops.grouped_gemm_dact_glu_backward(X, Wd, E, ts, D, H, pre, "swiglu"),
+                              2.0 * T * D * H),
         "gemm_dx": (lambda: ops.grouped_gemm(gU, Wu, _lib.B_NMAJOR, E, ts, 2 * H, D), 4.0 * T * D * H),
         "gemm_wgrad_down": (lambda: ops.grouped_gemm_wgrad(X, act, E, ts), 2.0 * T * D * H),
         "gemm_wgrad_up": (lambda: ops.grouped_gemm_wgrad(gU, X, E, ts), 4.0 * T * D * H),
