@@ -802,9 +802,11 @@ def main():
         gemm_ms = sum(kt[n][1] for n in gemm_names if n in kt)
         gemm_launches = sum(kt[n][0] for n in gemm_names if n in kt)
         achieved = fl["gemm"] * K / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else None
-        # the same without the dW_down launches that carry the GLU backward as a passenger (their event time is the
-        # whole launch, their FLOPs are dW_down's alone): the rate of the GEMM kernel when it runs by itself
-        pass_ms = kt["gemm_wgrad_passenger"][1] if "gemm_wgrad_passenger" in kt else 0.0
+        # the same without the launches that also do the GLU backward (in the dAct GEMM's epilogue, or as a passenger
+        # of the dW_down GEMM with FFM_FUSED_GLU_BACKWARD=0): their event time is the whole launch, their FLOPs are the
+        # GEMM's alone (2 x rows x D x H in both schedules). What is left is the rate of the plain GEMM launches.
+        carriers = [n for n in ("gemm_dact_glu_backward", "gemm_wgrad_passenger") if n in kt]
+        pass_ms = sum(kt[n][1] for n in carriers)
         pass_flops = 2.0 * tokens * CFG["d_model"] * (CFG["top_k"] * CFG["ffn_dim"] // 2 + CFG["shared_ffn_dim"] // 2)
         alone = ((fl["gemm"] - pass_flops) * K / ((gemm_ms - pass_ms) * 1e-3) / 1e12
                  if pass_ms > 0 and gemm_ms > pass_ms else None)
@@ -847,7 +849,7 @@ def main():
                                                            + rows_ * 3 * H_),
                 "kernel": "ffm_gemm_kernel (tcgen05 grouped GEMM, all instantiations)",
                 "measured_in": "a second pass of the same K steps after the timed region, same streams and same "
-                               "kernels as the timed region (GLU backward riding in the dW_down launch), with a "
+                               "kernels as the timed region, with a "
                                "CUDA-event pair around every kernel launch of the library",
                 "peak_source": f"{peaks['source']} cuBLAS bf16 burst (sustained {peaks['tflops']})",
                 "frac_of_burst": (achieved / peaks["tflops_burst"]) if achieved else None,
@@ -855,13 +857,16 @@ def main():
                 "frac_of_nominal_2250": (achieved / 2250.0) if achieved else None,
                 "frac_of_hw_rate_at_sampled_clock": (achieved / hw_rate) if achieved and hw_rate else None,
                 "whole_step_tflops": fl["gemm"] * K / (ms * 1e-3) / 1e12,
-                "achieved_without_passenger_launches": alone,
-                "frac_without_passenger_launches": (alone / peaks["tflops_burst"]) if alone else None,
-                "passenger_launch_ms_per_step": pass_ms / K,
+                "glu_backward_schedule": ("epilogue of the dAct GEMM" if "gemm_dact_glu_backward" in carriers else
+                                          "passenger warps of the dW_down GEMM" if carriers else None),
+                "achieved_without_glu_backward_launches": alone,
+                "frac_without_glu_backward_launches": (alone / peaks["tflops_burst"]) if alone else None,
+                "glu_backward_launch_ms_per_step": pass_ms / K,
                 "gemm_launches": gemm_launches, "gemm_ms_per_step": gemm_ms / K,
                 "algorithmic_tflop_per_step": fl["gemm"] / 1e12,
                 "other_kernels_ms_per_step": {n: v[1] / K for n, v in kt.items()
-                                              if n not in gemm_names and n not in ("all_to_all", "exchange_rows", "gemm_wgrad_passenger")},
+                                              if n not in gemm_names and n not in ("all_to_all", "exchange_rows", "gemm_wgrad_passenger",
+                                                                                  "gemm_dact_glu_backward")},
             },
         }
         if eager is not None:

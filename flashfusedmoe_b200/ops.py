@@ -371,7 +371,7 @@ def grouped_gemm_dact_glu_backward(gY, Wd, groups, tile_start, K, H, preact, act
     _req(preact, torch.bfloat16, "preact")
     rows = gY.shape[0]
     gU = torch.empty(rows, 2 * H, dtype=torch.bfloat16, device=gY.device)
-    with _Launch("gemm", 1):
+    with _Launch("gemm", 1, also="gemm_dact_glu_backward"):
         rc = lib.ffm_grouped_gemm_dact_glu_backward(_ptr(gY), _ptr(Wd), groups, _ptr(tile_start), rows, K, H,
                                                     _lib.ACTIVATION[activation], _ptr(preact), _ptr(gU), 0,
                                                     _ptr(status_tensor(gY.device)), _stream())
