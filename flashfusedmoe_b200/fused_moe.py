@@ -144,6 +144,29 @@ def _get_side_stream(name, priority=0):
     return _side_streams[key]
 
 
+def _fork_small(like):
+    """(current stream, side stream for small kernels) with the side stream ordered after what the current one holds,
+    or (None, None) when overlap is off or the data is not on a GPU. Work issued on the side stream is a parallel
+    branch of a captured step and runs beside the GEMMs instead of between them; close with _join_small."""
+    if not _OVERLAP or not like.is_cuda:
+        return None, None
+    cur = torch.cuda.current_stream()
+    side = _get_side_stream("small")
+    fork = torch.cuda.Event()
+    fork.record(cur)
+    side.wait_event(fork)
+    return cur, side
+
+
+def _join_small(cur, side, *made_on_side):
+    """The current stream waits for the side stream; tensors allocated there are handed over to the current one."""
+    done = torch.cuda.Event()
+    done.record(side)
+    cur.wait_event(done)
+    for t in made_on_side:
+        t.record_stream(cur)
+
+
 def _get_compute_dtype(fallback_dtype):
     if torch.is_autocast_enabled("cuda"):
         return torch.get_autocast_dtype("cuda")
@@ -286,10 +309,23 @@ def _glu_ffn_backward(go, x, act, pre, w_gate, w_up, w_down, activation):
     else:
         gU = ops.glu_backward(d_act, pre, None, 1, activation)
         d_wdown = ops.grouped_gemm_wgrad(go, act, split, ts_down)
-    d_wdown = d_wdown.sum(dim=0) if split == 2 else d_wdown[0]
+    cur, side = _fork_small(go)
+    if side is None:
+        d_wdown = d_wdown.sum(dim=0) if split == 2 else d_wdown[0]
+        w_cat = torch.cat([w_gate, w_up], dim=0)
+        dx = ops.grouped_gemm(gU, w_cat, _lib.B_NMAJOR, 1, None, 2 * Hs, D)
+        d_wcat = ops.grouped_gemm_wgrad(gU, x, 1, ts)[0]
+        return dx, d_wcat[:Hs], d_wcat[Hs:], d_wdown
+    # the sum of the two partial products is needed only at the end: it runs as a side branch beside the next two
+    # GEMMs. The stacked [gate; up] weights of the dX GEMM are copied on the current stream (the GEMM needs them next).
+    parts = d_wdown
+    parts.record_stream(side)  # freed below while the side stream may still read it
+    with torch.cuda.stream(side):
+        d_wdown = parts.sum(dim=0) if split == 2 else parts[0]
     w_cat = torch.cat([w_gate, w_up], dim=0)
     dx = ops.grouped_gemm(gU, w_cat, _lib.B_NMAJOR, 1, None, 2 * Hs, D)
     d_wcat = ops.grouped_gemm_wgrad(gU, x, 1, ts)[0]
+    _join_small(cur, side, d_wdown)
     return dx, d_wcat[:Hs], d_wcat[Hs:], d_wdown
 
 
@@ -368,11 +404,18 @@ class _FusedMoEFunction(torch.autograd.Function):
         add = None if addend is None else _to(addend, dtype)
 
         routing = _route(h, g, cfg, hidden_states.requires_grad)
-        aux, z = _loss_tensors(routing, N, E, cfg)  # from the routing before any capacity dropping
-        if cfg.capacity is not None:
-            dropped = ops.route_apply_capacity(routing, cfg.capacity)
+        cur, branch = (None, None) if cfg.capacity is not None else _fork_small(h)
+        if branch is None:
+            aux, z = _loss_tensors(routing, N, E, cfg)  # from the routing before any capacity dropping
+            if cfg.capacity is not None:
+                dropped = ops.route_apply_capacity(routing, cfg.capacity)
+            else:
+                dropped = torch.zeros(1, dtype=torch.int32, device=h.device)
         else:
-            dropped = torch.zeros(1, dtype=torch.int32, device=h.device)
+            # three one-block kernels that nothing in the layer waits for: a side branch, joined before returning
+            with torch.cuda.stream(branch):
+                aux, z = _loss_tensors(routing, N, E, cfg)
+                dropped = torch.zeros(1, dtype=torch.int32, device=h.device)
         need_grad = cfg.wants_grad and any(ctx.needs_input_grad[:5])
         # Without a backward pass nothing sums over the padding rows, so they are not zeroed -- except with capacity
         # dropping: a dropped slot keeps its grouped row (now a padding row) with weight 0, and 0 * (whatever the
@@ -388,6 +431,8 @@ class _FusedMoEFunction(torch.autograd.Function):
             torch.cuda.current_stream().wait_event(cfg.addend_ready)
             add.record_stream(torch.cuda.current_stream())
         out = ops.combine_forward(Y, routing.pos, routing.topk_w, N, k, addend=add)
+        if branch is not None:
+            _join_small(cur, branch, aux, z, dropped)
 
         ctx.set_materialize_grads(False)
         ctx.cfg = cfg
