@@ -48,7 +48,8 @@ _EP_TRANSPORT = os.environ.get("FFM_EP_TRANSPORT", "p2p")
 # every other kernel of the step still runs; the difference against a normal step is the exposed exchange time.
 _EP_DRY_EXCHANGE = False
 # Overlap of HBM-bound kernels with the tensor-core GEMMs: the routing backward and the shared expert on side streams
-# (they fill the gaps and tails between GEMMs), the GLU backward as a passenger inside the dW_down GEMM's CTAs.
+# (they fill the gaps and tails between GEMMs), small kernels nothing waits for as side branches, and (without the
+# fused GLU-backward epilogue below) the GLU backward as a passenger inside the dW_down GEMM's CTAs.
 # FFM_OVERLAP=0 keeps one stream and separate kernels.
 _OVERLAP = os.environ.get("FFM_OVERLAP", "1") != "0"
 # GLU backward inside the dAct GEMM's epilogue (one launch, dAct never written, bit-identical to the two kernels): the

@@ -519,7 +519,7 @@ def test_wgrad_with_glu_backward_passenger(counts, M, Nout, H, activation):
     assert torch.equal(sentinel[:used], gU_ref[:used]) and (sentinel[used:] == 7.0).all()
 
 
-@pytest.mark.parametrize("activation", ["swiglu", "geglu", "relu_squared"])
+@pytest.mark.parametrize("activation", ["swiglu", "geglu", "relu_squared", "geglu_erf"])
 @pytest.mark.parametrize("counts,K,H", [([5, 0, 200, 128], 64, 64), ([300, 17, 129, 64, 1, 0, 77, 256], 128, 320),
                                         ([2048] * 8, 1024, 2048)])
 def test_dact_gemm_with_fused_glu_backward(counts, K, H, activation):
