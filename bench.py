@@ -441,6 +441,9 @@ def other_configs(group, rank, world, device):
         torch.cuda.empty_cache()
         out["configs[4]_graph"] = bench_decode.run(60, 10, 128, True, group, rank, world, device)
         torch.cuda.empty_cache()
+        if world == 1:
+            out["configs[1]_fp8_forward"] = fp8_forward_steps(device)
+            torch.cuda.empty_cache()
     except Exception as exc:   # the headline line must still be printed
         out["error"] = f"{type(exc).__name__}: {str(exc)[:300]}"
     if rank != 0:
@@ -448,6 +451,36 @@ def other_configs(group, rank, world, device):
     keep = ("value", "unit", "ms_per_step", "gemm_tflops_per_gpu_whole_step", "p50", "p99", "min", "mode",
             "weight_stream_bound_ms", "tokens_per_gpu", "iters", "steps", "config", "skipped", "grad_sync", "all_to_all_ms_per_iter")
     return {n: ({k: v for k, v in d.items() if k in keep} if isinstance(d, dict) else d) for n, d in out.items()}
+
+
+def fp8_forward_steps(device, steps=12, warmup=4):
+    """configs[1] on one GPU with the opt-in e4m3 forward projections of the routed experts (backward stays bf16):
+    the same step as the headline, captured and replayed, a few steps."""
+    import flashfusedmoe_b200 as ffm
+    layer = build_layer(device, None)
+    torch.manual_seed(1000)
+    x = torch.randn(CFG["batch"], CFG["seq"], CFG["d_model"], device=device).bfloat16().requires_grad_()
+    go = torch.randn_like(x)
+    step = make_step(layer, x, go)
+    ffm.set_expert_gemm_precision("fp8")
+    try:
+        graph, _ = capture_step(step)
+        for _ in range(warmup):
+            graph.replay()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(steps):
+            graph.replay()
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / steps
+    finally:
+        ffm.set_expert_gemm_precision("bf16")
+    tokens = CFG["batch"] * CFG["seq"]
+    return {"config": "BASELINE configs[1] with e4m3 operands in the routed experts' forward GEMMs (activations scaled "
+                      "per row, weights per expert; opt-in, not the headline precision), replayed graph",
+            "steps": steps, "value": tokens / (ms * 1e-3), "unit": UNIT, "ms_per_step": ms}
 
 
 def run_reference_arm(args, rank):

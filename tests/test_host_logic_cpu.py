@@ -245,6 +245,9 @@ def test_small_helpers_without_a_gpu():
     # run_beside: CPU tensors (or overlap switched off) call the function in place and return no event
     out, ev = fm.run_beside(lambda t: t * 2, torch.ones(3))
     assert ev is None and out.tolist() == [2.0, 2.0, 2.0]
+    # side branch for small kernels: none for CPU tensors, and the schedule defaults are on
+    assert fm._fork_small(torch.ones(3)) == (None, None)
+    assert fm._OVERLAP and fm._FUSED_GLU_BWD
     # inference shortcut arguments of the grouped GEMMs
     assert fm._small_m_kwargs(False, None) == {}
     kw = fm._small_m_kwargs(True, torch.tensor([3, 0, 7], dtype=torch.int64))
