@@ -59,12 +59,15 @@ constexpr int MAX_STAGES = 6;
 constexpr int SMEM_LIMIT = 232448;  // 227 KiB of dynamic shared memory per CTA
 
 enum { EPI_PLAIN = 0, EPI_GLU = 1, EPI_GLUBWD = 2 };
-// The GLU-backward epilogue does about 16 instructions and two MUFU operations per accumulator element, too much for
-// one warp per scheduler inside a tile's main loop: four helper warps (one more per TMEM lane quarter) take the upper
-// 32 columns of every 64-column step.
-constexpr int GLUBWD_HELPER_THREADS = 128;
+// The GLU epilogues get a second warp per TMEM lane quarter (helper warps 6..9, each taking the upper 32 columns of
+// every 64-column step). The GLU backward does about 16 instructions and two MUFU operations per accumulator element,
+// too much for one warp per scheduler inside a tile's main loop (0.174 -> 0.164 ms at 8 x 4096 rows, D 1024, H 2048);
+// the e4m3 up-projection has half the main loop of the bf16 one under the same epilogue (1382 -> 1626 TFLOP/s); the
+// bf16 up-projection gains 1 % (and needs 105 instead of 234 registers, since its loops are rolled).
+constexpr int HELPER_THREADS = 128;
+__host__ __device__ constexpr bool epilogue_helpers(int epi) { return epi == EPI_GLUBWD || epi == EPI_GLU; }
 __host__ __device__ constexpr int gemm_threads(int epi, int pass) {
-  return GEMM_THREADS + pass * PASSENGER_THREADS + (epi == EPI_GLUBWD ? GLUBWD_HELPER_THREADS : 0);
+  return GEMM_THREADS + pass * PASSENGER_THREADS + (epilogue_helpers(epi) ? HELPER_THREADS : 0);
 }
 
 // Ring depth against staging depth for CTA pairs. Measured at 8 x 4096 rows, D 1024, H 2048: every split from 4 to
@@ -153,6 +156,7 @@ struct Ctrl {
   int abort_flag;
   unsigned long long pre_bar[EPI_WARPS][3];  // GLU-backward epilogue: "pre-activation boxes have landed", per warp and buffer
   unsigned long long help_bar[EPI_WARPS][3];  // ... and "the helper warp has written its half of the step"
+  unsigned long long free_bar[EPI_WARPS][3];  // GLU epilogue with helpers: "the step's staging boxes may be overwritten"
   int tile_start[MAX_GROUPS + 1];
 };
 static_assert(sizeof(Ctrl) <= SMEM_CTRL_BYTES, "control block too large");
@@ -445,6 +449,70 @@ __device__ __forceinline__ void glu_backward_step(uint32_t tcol, float scale, ui
   }
 }
 
+// Eight GLU columns of the up-projection epilogue: gate and up accumulators g, u (scaled when they come from e4m3
+// operands) are rounded to bf16 (the stored pre-activations), the activation is computed from the rounded values, and
+// 16 bytes each go to this lane's row of the activation, gate and up boxes.
+template <int ACT, int FP8>
+__device__ __forceinline__ void glu_forward_8(const uint32_t (&g)[8], const uint32_t (&u)[8], float fp8_scale,
+                                              bool store_pre, uint32_t buf, uint32_t o) {
+  uint32_t pg[4], pu[4], pa[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    float g0 = __uint_as_float(g[2 * j]), g1 = __uint_as_float(g[2 * j + 1]);
+    float u0 = __uint_as_float(u[2 * j]), u1 = __uint_as_float(u[2 * j + 1]);
+    if (FP8) {
+      g0 *= fp8_scale;
+      g1 *= fp8_scale;
+      u0 *= fp8_scale;
+      u1 *= fp8_scale;
+    }
+    pg[j] = pack_bf16x2(g0, g1);
+    pu[j] = pack_bf16x2(u0, u1);
+    const float2 gf = unpack_bf16x2(pg[j]);
+    const float2 uf = unpack_bf16x2(pu[j]);
+    pa[j] = pack_bf16x2(glu_fwd(ACT, gf.x, uf.x), glu_fwd(ACT, gf.y, uf.y));
+  }
+  st_shared_v4(buf + o, pa[0], pa[1], pa[2], pa[3]);
+  if (store_pre) {
+    st_shared_v4(buf + BOX_BYTES + o, pg[0], pg[1], pg[2], pg[3]);
+    st_shared_v4(buf + 2 * BOX_BYTES + o, pu[0], pu[1], pu[2], pu[3]);
+  }
+}
+
+// 32 GLU columns (four 16-byte column groups from q_begin) of a 64-column step: gate at TMEM column tcol, up 128
+// columns further, read eight columns at a time one load ahead of the math in a rolled loop.
+template <int ACT, int FP8>
+__device__ __forceinline__ void glu_forward_half_step_act(uint32_t tcol, float fp8_scale, bool store_pre, uint32_t buf,
+                                                          int lane, int q_begin) {
+  uint32_t ga[8], ua[8], gb[8], ub[8];
+  tmem_ld_32x8(tcol, ga);
+  tmem_ld_32x8(tcol + 128, ua);
+#pragma unroll 1
+  for (int i = 0; i < 4; i += 2) {
+    tmem_ld_wait();
+    tmem_ld_32x8(tcol + (i + 1) * 8, gb);
+    tmem_ld_32x8(tcol + 128 + (i + 1) * 8, ub);
+    glu_forward_8<ACT, FP8>(ga, ua, fp8_scale, store_pre, buf, box_offset(lane, q_begin + i));
+    tmem_ld_wait();
+    if (i + 2 < 4) {
+      tmem_ld_32x8(tcol + (i + 2) * 8, ga);
+      tmem_ld_32x8(tcol + 128 + (i + 2) * 8, ua);
+    }
+    glu_forward_8<ACT, FP8>(gb, ub, fp8_scale, store_pre, buf, box_offset(lane, q_begin + i + 1));
+  }
+}
+
+template <int FP8>
+__device__ __forceinline__ void glu_forward_half_step(uint32_t tcol, int act, float fp8_scale, bool store_pre,
+                                                      uint32_t buf, int lane, int q_begin) {
+  switch (act) {
+    case FFM_ACT_SWIGLU: glu_forward_half_step_act<FFM_ACT_SWIGLU, FP8>(tcol, fp8_scale, store_pre, buf, lane, q_begin); break;
+    case FFM_ACT_GEGLU_TANH: glu_forward_half_step_act<FFM_ACT_GEGLU_TANH, FP8>(tcol, fp8_scale, store_pre, buf, lane, q_begin); break;
+    case FFM_ACT_RELU2: glu_forward_half_step_act<FFM_ACT_RELU2, FP8>(tcol, fp8_scale, store_pre, buf, lane, q_begin); break;
+    default: glu_forward_half_step_act<FFM_ACT_GEGLU_ERF, FP8>(tcol, fp8_scale, store_pre, buf, lane, q_begin); break;
+  }
+}
+
 // FP8 = 1: A and B hold e4m3 bytes, K-major only; a stage row is still 128 bytes, i.e. 128 K elements per block.
 template <int A_MN, int B_MN, int EPI, int GROUPK, int CTA2, int PASS = 0, int FP8 = 0>
 __global__ void __launch_bounds__(gemm_threads(EPI, PASS), 1)
@@ -454,6 +522,7 @@ ffm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   using S = Shape<CTA2, EPI>;
   constexpr int STAGES = S::STAGES;
   constexpr int STAGE_BYTES = S::STAGE_BYTES;
+  constexpr bool HELPERS = epilogue_helpers(EPI);
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
@@ -477,13 +546,14 @@ ffm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     for (int a = 0; a < NUM_ACC; ++a) {
       mbar_init(smem_u32(&ctrl->acc_full_bar[a]), 1);
       // one arrival per epilogue warp (helpers included)
-      mbar_init(smem_u32(&ctrl->acc_empty_bar[a]), (EPI == EPI_GLUBWD ? 2 : 1) * EPI_WARPS * (CTA2 ? 2 : 1));
+      mbar_init(smem_u32(&ctrl->acc_empty_bar[a]), (HELPERS ? 2 : 1) * EPI_WARPS * (CTA2 ? 2 : 1));
     }
-    if (EPI == EPI_GLUBWD) {
+    if (HELPERS) {
       for (int w = 0; w < EPI_WARPS; ++w) {
         for (int b = 0; b < 3; ++b) {
           mbar_init(smem_u32(&ctrl->pre_bar[w][b]), 1);
           mbar_init(smem_u32(&ctrl->help_bar[w][b]), 1);
+          mbar_init(smem_u32(&ctrl->free_bar[w][b]), 1);
         }
       }
     }
@@ -693,12 +763,13 @@ ffm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     // ================= epilogue (warps 2..5; with the GLU backward also helper warps 6..9) =================
     const int quarter = warp & 3;  // TMEM lanes [32 * quarter, 32 * quarter + 32) belong to this warp
     const int wi = (warp - 2) & 3;  // staging area and barriers; a helper shares those of the warp of its quarter
-    const bool helper = EPI == EPI_GLUBWD && warp >= 2 + EPI_WARPS;
+    const bool helper = HELPERS && warp >= 2 + EPI_WARPS;
     const uint32_t stg = stg_base + wi * S::STG_WARP_BYTES;
     constexpr int STEP_BYTES = S::BOXES_PER_STEP * BOX_BYTES;
     int step_slot = 0;  // staging slot of the next store step; advances per step actually stored
     uint32_t pre_phase = 0u;  // GLU-backward epilogue: bit b = parity to wait for on buffer b's load barrier
     uint32_t help_phase = 0u;  // the same for the helper's "half written" barriers (waited for by warps 2..5)
+    uint32_t free_phase = 0u;  // ... and for the "boxes may be overwritten" barriers (waited for by the helpers)
     TileWalker<GROUPK, CTA2> walker(p, ctrl->tile_start, rank);
     TileCoord t;
     int acc = 0;
@@ -734,70 +805,55 @@ ffm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       if (FP8) fp8_scale = __ldg(fp8_a_scale(p) + row0 + lane) * __ldg(fp8_b_scale(p) + t.group);
 
       if (EPI == EPI_GLU) {
-        // two steps of 64 GLU columns, each two 32-column chunks of gate and up; the TMEM loads of chunk c + 1 fly
-        // while chunk c is processed. A step fills three boxes (activation, gate, up) and stores them as one group.
+        // two steps of 64 GLU columns; warp wi takes the lower 32 columns of a step, its helper the upper 32, eight
+        // columns of gate and up per trip of a rolled loop. A step fills three boxes (activation, gate, up), stored as
+        // one group by warp wi once the helper has written its half.
         const int h0 = t.n_block * 128;
-        uint32_t g[2][32], u[2][32];
-        tmem_ld_32x32(taddr, g[0]);
-        tmem_ld_32x32(taddr + 128, u[0]);
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          tmem_ld_wait();
-          if (c + 1 < 4) {
-            tmem_ld_32x32(taddr + (c + 1) * 32, g[(c + 1) & 1]);
-            tmem_ld_32x32(taddr + 128 + (c + 1) * 32, u[(c + 1) & 1]);
+        const int qb = helper ? 4 : 0;
+#pragma unroll 1
+        for (int st = 0; st < 2 && h0 + st * 64 < p.n_cols; ++st) {
+          const uint32_t buf = stg + step_slot * STEP_BYTES;
+          const uint32_t slot_bit = 1u << step_slot;
+          if (!helper) {
+            // the slot is free once the step stored STEPS_BUFFERED steps ago has been read out
+            if (lane == 0) {
+              bulk_wait_read<S::STEPS_BUFFERED - 1>();
+              mbar_arrive(smem_u32(&ctrl->free_bar[wi][step_slot]));
+            }
+            __syncwarp();
+          } else {
+            ok = mbar_wait_bounded(smem_u32(&ctrl->free_bar[wi][step_slot]), (free_phase & slot_bit) ? 1u : 0u,
+                                   abort_flag, p.status, FFM_STATUS_WAIT_EPILOGUE, p.wait_cycles);
+            ok = __all_sync(0xffffffffu, ok ? 1 : 0) != 0;
+            if (!ok) break;
+            free_phase ^= slot_bit;
           }
-          const int col = h0 + (c >> 1) * 64;  // first GLU column of this step's boxes
-          if (col < p.n_cols) {
-            const uint32_t buf = stg + step_slot * STEP_BYTES;
-            if ((c & 1) == 0) {
-              // the slot is free once the step stored STEPS_BUFFERED steps ago has been read out
-              if (lane == 0) bulk_wait_read<S::STEPS_BUFFERED - 1>();
-              __syncwarp();
-            }
-            if (h0 + c * 32 < p.n_cols) {
-              uint32_t pg[16], pu[16], pa[16];
-#pragma unroll
-              for (int i = 0; i < 16; ++i) {
-                float g0 = __uint_as_float(g[c & 1][2 * i]), g1 = __uint_as_float(g[c & 1][2 * i + 1]);
-                float u0 = __uint_as_float(u[c & 1][2 * i]), u1 = __uint_as_float(u[c & 1][2 * i + 1]);
-                if (FP8) {
-                  g0 *= fp8_scale;
-                  g1 *= fp8_scale;
-                  u0 *= fp8_scale;
-                  u1 *= fp8_scale;
-                }
-                pg[i] = pack_bf16x2(g0, g1);
-                pu[i] = pack_bf16x2(u0, u1);
-                const float2 gf = unpack_bf16x2(pg[i]);
-                const float2 uf = unpack_bf16x2(pu[i]);
-                pa[i] = pack_bf16x2(glu_fwd(p.act, gf.x, uf.x), glu_fwd(p.act, gf.y, uf.y));
+          if (h0 + st * 64 + qb * 8 < p.n_cols) {
+            glu_forward_half_step<FP8>(taddr + st * 64 + qb * 8, p.act, fp8_scale, p.has_c2 != 0, buf, lane, qb);
+          }
+          fence_proxy_async();
+          __syncwarp();
+          if (helper) {
+            if (lane == 0) mbar_arrive(smem_u32(&ctrl->help_bar[wi][step_slot]));
+          } else {
+            ok = mbar_wait_bounded(smem_u32(&ctrl->help_bar[wi][step_slot]), (help_phase & slot_bit) ? 1u : 0u,
+                                   abort_flag, p.status, FFM_STATUS_WAIT_EPILOGUE, p.wait_cycles);
+            ok = __all_sync(0xffffffffu, ok ? 1 : 0) != 0;
+            if (!ok) break;
+            help_phase ^= slot_bit;
+            if (lane == 0) {
+              const int col = h0 + st * 64;
+              tma_store_3d(&tmC, buf, col, row0, 0);
+              if (p.has_c2) {
+                tma_store_3d(&tmC2, buf + BOX_BYTES, col, row0, 0);
+                tma_store_3d(&tmC2, buf + 2 * BOX_BYTES, p.glu_h + col, row0, 0);
               }
-#pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                const uint32_t o = box_offset(lane, (c & 1) * 4 + q);
-                st_shared_v4(buf + o, pa[4 * q], pa[4 * q + 1], pa[4 * q + 2], pa[4 * q + 3]);
-                if (p.has_c2) {
-                  st_shared_v4(buf + BOX_BYTES + o, pg[4 * q], pg[4 * q + 1], pg[4 * q + 2], pg[4 * q + 3]);
-                  st_shared_v4(buf + 2 * BOX_BYTES + o, pu[4 * q], pu[4 * q + 1], pu[4 * q + 2], pu[4 * q + 3]);
-                }
-              }
-            }
-            if (c & 1) {
-              fence_proxy_async();
-              __syncwarp();
-              if (lane == 0) {
-                tma_store_3d(&tmC, buf, col, row0, 0);
-                if (p.has_c2) {
-                  tma_store_3d(&tmC2, buf + BOX_BYTES, col, row0, 0);
-                  tma_store_3d(&tmC2, buf + 2 * BOX_BYTES, p.glu_h + col, row0, 0);
-                }
-                bulk_commit();
-              }
-              if (++step_slot == S::STEPS_BUFFERED) step_slot = 0;
+              bulk_commit();
             }
           }
+          if (++step_slot == S::STEPS_BUFFERED) step_slot = 0;
         }
+        if (!ok) break;
       } else if (EPI == EPI_GLUBWD) {
         // The accumulator is dAct (gradient of the GLU output). Rounded to bf16 as the stand-alone dAct GEMM would
         // store it, it goes through the GLU backward with the saved pre-activations of the same rows and columns, and

@@ -68,10 +68,10 @@ def test_product_path_has_no_cpu_fallback():
 
 
 def test_gemm_register_allocation_canary():
-    """ptxas figures of the build: no GEMM instantiation spills, and the GLU-epilogue GEMM keeps its wide register
-    allocation. (Growing the kernel's parameter struct by three fields once made ptxas pick 185 instead of 234
-    registers for it, with no spills reported and a 30 % slower kernel: two 32-column chunks of gate and up no longer
-    stayed in flight.)"""
+    """ptxas figures of the build: no GEMM instantiation spills, and the instantiations with helper epilogue warps
+    (320 threads: both GLU epilogues) stay far below the 204 registers that thread count allows. (The first GLU
+    epilogue kept 128 accumulator values in flight per lane, needed 234 registers, and ran 30 % slower when an unrelated
+    change to the parameter struct made ptxas pick 185; the rolled epilogues hold 32.)"""
     import re
     from flashfusedmoe_b200 import build
     build.build(force=not os.path.exists(build.PTXAS_LOG))
@@ -80,6 +80,6 @@ def test_gemm_register_allocation_canary():
     assert len(blocks) >= 10, "ptxas output of the GEMM instantiations not found"
     spills = re.findall(r"ffm_gemm_kernel\S*\n\s*(\d+) bytes stack frame, (\d+) bytes spill stores, (\d+) bytes spill loads", text)
     assert spills and all(int(a) == 0 and int(b) == 0 for _, a, b in spills), "a GEMM instantiation spills registers"
-    # <A K-major, B K-major, EPI_GLU, grouped-M, either tile shape, no passenger, bf16 operands>
-    glu = [int(r) for name, r in blocks if re.search(r"ILi0ELi0ELi1ELi0ELi\dELi0ELi0E", name)]
-    assert glu and min(glu) >= 200, f"GLU-epilogue GEMM register allocation changed: {glu}"
+    # <A, B, EPI_GLU = 1 or EPI_GLUBWD = 2, ...>
+    glu = [int(r) for name, r in blocks if re.search(r"ILi\dELi\dELi[12]ELi", name)]
+    assert glu and max(glu) <= 160, f"GLU-epilogue GEMM register allocation changed: {glu}"
