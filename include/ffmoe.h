@@ -198,7 +198,8 @@ int ffm_grouped_gemm_wgrad(const void* A, const void* B, int groups, const int32
 /* dAct GEMM with the GLU backward fused into its epilogue: gU [rows, 2H] = GLU backward of (gY Wd (N-major B, as
  * ffm_grouped_gemm with FFM_B_NMAJOR) rounded to bf16, preact [rows, 2H]), bit-identical to ffm_grouped_gemm followed by
  * ffm_glu_backward (reference: the bmm + activation_backward pair, fused_moe.py:520-531); dAct is never written. The
- * tile's pre-activations are prefetched into L2 when its main loop starts and read by the epilogue warps directly.
+ * epilogue warps pull the tile's pre-activations in by TMA, one 64-column step ahead, into the staging boxes that the
+ * gradients are then written over and stored from.
  * gY [rows, K], Wd [groups, K, H], K % 64 == 0, H % 64 == 0. */
 int ffm_grouped_gemm_dact_glu_backward(const void* gY, const void* Wd, int groups, const int32_t* tile_start,
                                        int64_t rows, int K, int H, int activation, const void* preact, void* gU,
