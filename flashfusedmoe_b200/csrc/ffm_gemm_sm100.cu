@@ -80,6 +80,9 @@ __host__ __device__ constexpr int gemm_threads(int epi, int pass) {
 #define FFM_TUNE_PP_STAGES 6
 #define FFM_TUNE_PP_STEPS 2
 #endif
+#ifndef FFM_TUNE_GB_STEPS
+#define FFM_TUNE_GB_STEPS 3
+#endif
 #ifndef FFM_TUNE_PG_STAGES
 #define FFM_TUNE_PG_STAGES 5
 #define FFM_TUNE_PG_STEPS 1
@@ -101,7 +104,7 @@ struct Shape {
   static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
   static constexpr int BOXES_PER_STEP = EPI == EPI_GLU ? 3 : (EPI == EPI_GLUBWD ? 2 : 1);
   static constexpr int STEPS_BUFFERED = EPI == EPI_GLU      ? (CTA2 ? FFM_TUNE_PG_STEPS : 1)
-                                        : EPI == EPI_GLUBWD ? (CTA2 ? 3 : 2)
+                                        : EPI == EPI_GLUBWD ? (CTA2 ? FFM_TUNE_GB_STEPS : 2)
                                                             : (CTA2 ? FFM_TUNE_PP_STEPS : 2);
   static constexpr int STG_WARP_BYTES = BOXES_PER_STEP * STEPS_BUFFERED * BOX_BYTES;
   static constexpr int STG_BYTES = EPI_WARPS * STG_WARP_BYTES;
