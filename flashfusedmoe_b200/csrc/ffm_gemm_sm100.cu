@@ -32,8 +32,8 @@
 //       K step of 16 rows = +2048 B on the start address
 // Output staging: every epilogue warp owns a few 32-row x 128-byte boxes (64 bf16 columns) with the 128-byte
 // swizzle (16-byte chunk index ^= row & 7), stored with box {64 columns, 32 rows, 1}; stores clip at the tensor
-// extents, so ragged row and column edges need no masking. A plain epilogue rotates two boxes per warp; the GLU
-// epilogue fills three (activation, gate, up) per 64-column step.
+// extents, so ragged row and column edges need no masking. A plain epilogue has one box per warp (two with one-CTA
+// tiles); the GLU epilogue fills three (activation, gate, up) per 64-column step.
 #include <stdlib.h>
 
 #include "ffm_common.cuh"
@@ -71,17 +71,22 @@ __host__ __device__ constexpr int gemm_threads(int epi, int pass) {
 }
 
 // Ring depth against staging depth for CTA pairs. Measured at 8 x 4096 rows, D 1024, H 2048: every split from 4 to
-// 6 stages runs within 3 % of the others alone (the GEMMs sit at the board's power limit, not at a pipeline limit).
-// A 4-stage ring leaves ~65 KiB of shared memory free on every SM, which is what lets blocks of an HBM-bound kernel
-// from another stream run beside the resident GEMM CTA (with 8 KiB free they do not); in the layer step the two
-// effects cancel to within run-to-run noise, so the deeper ring, which is the faster GEMM on its own, is the default
-// (-DFFM_TUNE_PP_STAGES=4 -DFFM_TUNE_PG_STAGES=4 builds the other one).
+// 6 stages runs within 3 % of the others alone (the GEMMs sit at the board's power limit, not at a pipeline limit),
+// and one, two or four staging steps per epilogue warp make no difference.
+// What the split decides is who can run beside the resident GEMM CTA. Every block needs 1 KiB of shared memory of
+// the SM even if it declares none, so a GEMM CTA that takes all 227 KiB shuts every other kernel out of its SM.
+// With one staging step (plain) and two staging buffers (GLU backward) every shape leaves 16-32 KiB: blocks of
+// kernels without shared memory of their own (the exchange's row and flag kernels, the row-wise HBM kernels) then
+// run on SMs that hold a GEMM CTA. Measured in the layer step: no change on one GPU (1.712-1.716 ms either way),
+// 1.650 -> 1.616 ms on two (expert parallel: the NVLink pushes no longer wait for a GEMM to drain).
+// A 4-stage ring (~65 KiB free) also admits kernels with shared memory of their own; the GEMMs are then 0-4 % slower
+// alone and the step does not gain (-DFFM_TUNE_PP_STAGES=4 -DFFM_TUNE_PG_STAGES=4 builds that one).
 #ifndef FFM_TUNE_PP_STAGES
 #define FFM_TUNE_PP_STAGES 6
-#define FFM_TUNE_PP_STEPS 2
+#define FFM_TUNE_PP_STEPS 1
 #endif
 #ifndef FFM_TUNE_GB_STEPS
-#define FFM_TUNE_GB_STEPS 3
+#define FFM_TUNE_GB_STEPS 2
 #endif
 #ifndef FFM_TUNE_PG_STAGES
 #define FFM_TUNE_PG_STAGES 5
@@ -89,9 +94,9 @@ __host__ __device__ constexpr int gemm_threads(int epi, int pass) {
 #endif
 
 // Shared-memory budget per tile shape and epilogue: ring stages against staging boxes per epilogue warp.
-//   CTA pair, plain: 6 stages x 32 KiB + 2 boxes    CTA pair, GLU: 5 stages x 32 KiB + 3 boxes
+//   CTA pair, plain: 6 stages x 32 KiB + 1 box      CTA pair, GLU: 5 stages x 32 KiB + 3 boxes
 //   one CTA,  plain: 4 stages x 48 KiB + 2 boxes    one CTA,  GLU: 3 stages x 48 KiB + 3 boxes
-//   GLU backward epilogue (EPI_GLUBWD): 4 stages + 3 x 2 boxes (one CTA: 3 stages + 2 x 2 boxes)
+//   GLU backward epilogue (EPI_GLUBWD): 4 stages + 2 x 2 boxes (one CTA: 3 stages + 2 x 2 boxes)
 // A GLU step stores three boxes (activation, gate, up) as one bulk group; a plain step stores one box; a GLU backward
 // step stores two (gate gradient, up gradient).
 template <int CTA2, int EPI>

@@ -139,7 +139,9 @@ __global__ void __launch_bounds__(256) p2p_plan_kernel(const int32_t* __restrict
   __shared__ long long s_R[PLAN_MAX_E];      // rows per expert over all sources
   __shared__ int s_overflow;
   __shared__ long long s_seg0[PLAN_MAX_E];   // first grouped row of expert e at its owner
-  __shared__ long long s_send0[FFM_P2P_MAX_PEERS][PLAN_MAX_E];  // first sender-order row of expert e at rank s
+  // first sender-order row of expert e at rank s, [ep][E]: sized by the launch, so that with few experts the block
+  // needs little shared memory and can run on an SM that a GEMM CTA occupies
+  extern __shared__ long long s_send0[];
   __shared__ long long s_rows_grouped;
   const int E = ep * e_local;
   const int t = threadIdx.x;
@@ -152,7 +154,7 @@ __global__ void __launch_bounds__(256) p2p_plan_kernel(const int32_t* __restrict
   if (t < ep) {  // sender-order prefix of rank t
     long long acc = 0;
     for (int e = 0; e < E; ++e) {
-      s_send0[t][e] = acc;
+      s_send0[t * E + e] = acc;
       acc += C[t * E + e];
     }
   }
@@ -205,11 +207,11 @@ __global__ void __launch_bounds__(256) p2p_plan_kernel(const int32_t* __restrict
     long long before = 0;
     for (int s = 0; s < rank; ++s) before += C[s * E + e];
     const long long rows = C[rank * E + e];
-    dispatch[4 * e + 0] = s_send0[rank][e];
+    dispatch[4 * e + 0] = s_send0[rank * E + e];
     dispatch[4 * e + 1] = s_seg0[e] + before;
     dispatch[4 * e + 2] = rows;
     dispatch[4 * e + 3] = e / e_local;
-    dispatch_end[e] = s_send0[rank][e] + rows;
+    dispatch_end[e] = s_send0[rank * E + e] + rows;
   }
   // combine: runs (expert, source) this rank holds, grouped layout -> the origin's sender order
   for (int i = t; i < e_local * ep; i += blockDim.x) {
@@ -220,7 +222,7 @@ __global__ void __launch_bounds__(256) p2p_plan_kernel(const int32_t* __restrict
     for (int el2 = 0; el2 < el; ++el2) prior += s_R[lo + el2];
     const long long rows = C[s * E + e];
     combine[4 * i + 0] = s_seg0[e] + before;
-    combine[4 * i + 1] = s_send0[s][e];
+    combine[4 * i + 1] = s_send0[s * E + e];
     combine[4 * i + 2] = rows;
     combine[4 * i + 3] = s;
     combine_end[i] = prior + before + rows;
@@ -390,7 +392,8 @@ extern "C" int ffm_p2p_plan(const int32_t* counts, int ep, int e_local, int rank
   if (ep < 1 || ep > FFM_P2P_MAX_PEERS || e_local < 1 || rank < 0 || rank >= ep) return FFM_ERR_BAD_ARG;
   if (ep * e_local > PLAN_MAX_E) return FFM_ERR_UNSUPPORTED;
   if (max_grouped_rows < 0 || (max_grouped_rows > 0 && status == nullptr)) return FFM_ERR_BAD_ARG;
-  p2p_plan_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  const size_t table_bytes = static_cast<size_t>(ep) * ep * e_local * sizeof(long long);  // [ep][E], at most 32 KiB
+  p2p_plan_kernel<<<1, 256, table_bytes, static_cast<cudaStream_t>(stream)>>>(
       counts, ep, e_local, rank, reinterpret_cast<long long*>(dispatch), reinterpret_cast<long long*>(dispatch_end),
       reinterpret_cast<long long*>(combine), reinterpret_cast<long long*>(combine_end),
       reinterpret_cast<long long*>(padding), reinterpret_cast<long long*>(padding_end), tile_start,
