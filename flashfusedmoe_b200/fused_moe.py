@@ -697,23 +697,41 @@ class _FusedMoEEPStaticFunction(torch.autograd.Function):
             px.push_rows_dev(None, None, 1, rb, t["padding"], t["padding_end"], tot[2:3], 256 * El, 0,
                              name="zero_padding")
         px.barrier_dev()
+        # The GEMMs and the combine read the received rows in place. The copies that the backward pass needs (the
+        # regions are overwritten by the next call) are side branches: the copy of the grouped rows must be complete
+        # before this rank signals the combine exchange (a peer that has passed that barrier may push the next call's
+        # rows into region 0), the copy of the returned rows before it signals the next dispatch, i.e. before the
+        # forward pass returns.
         Xg = px.region_view(0, cap_rows, D, h.dtype)
-        if need_grad:
-            Xg = px.keep_rows_dev(Xg, tot[3:4], cap_rows)   # saved for backward; the region is overwritten by the next call
+        Xg_saved = returned_saved = None
+        cur, copier = _fork_small(h) if need_grad else (None, None)
+        if need_grad and copier is None:
+            Xg = Xg_saved = px.keep_rows_dev(Xg, tot[3:4], cap_rows)
+        elif need_grad:
+            with torch.cuda.stream(copier):
+                Xg_saved = px.keep_rows_dev(Xg, tot[3:4], cap_rows)
         small = _small_m_kwargs(not need_grad and ep * _EP_STATIC_TOKENS * k < 128 * E, None)
         if small:
             small["valid_rows"] = C[:, px.rank * El:(px.rank + 1) * El].sum(0, dtype=torch.int32)
         act, pre = ops.grouped_gemm_glu(Xg, wu, wu.view(-1, D)[H:], 2 * H, El, t["tile_start"], D, H, cfg.activation,
                                         want_preact=need_grad, **small)
         Y = ops.grouped_gemm(act, wd, _lib.B_KMAJOR, El, t["tile_start"], H, D, **small)
+        if copier is not None:
+            _join_small(cur, copier, Xg_saved)
         px.push_rows_dev(Y, None, 1, rb, t["combine"], t["combine_end"], tot[1:2], cap_rows, 1)
         px.barrier_dev()
         returned = px.region_view(1, T, D, h.dtype)
-        if need_grad:
-            returned = returned.clone()
+        if need_grad and copier is None:
+            returned = returned_saved = returned.clone()
+        elif need_grad:
+            cur, copier = _fork_small(h)
+            with torch.cuda.stream(copier):
+                returned_saved = returned.clone()
         if has_shared:
             torch.cuda.current_stream().wait_event(shared_done)
         out = ops.combine_forward(returned, cpos, routing.topk_w, N, k, addend=shared[0] if has_shared else None)
+        if need_grad and copier is not None:
+            _join_small(cur, copier, returned_saved)
         aux, z = _loss_tensors(routing, N, E, cfg)
 
         ctx.set_materialize_grads(False)
@@ -727,7 +745,7 @@ class _FusedMoEEPStaticFunction(torch.autograd.Function):
         if need_grad:
             tensors = dict(h=h, g=g, wu=wu, wd=wd, topk_w=routing.topk_w, topk_idx=routing.topk_idx,
                            logits=routing.logits, lse=routing.lse, counts=routing.counts, src_c=src_c, cpos=cpos,
-                           returned=returned, Xg=Xg, act=act, pre=pre, ts_l=t["tile_start"], totals=tot,
+                           returned=returned_saved, Xg=Xg_saved, act=act, pre=pre, ts_l=t["tile_start"], totals=tot,
                            dispatch=t["dispatch"], dispatch_end=t["dispatch_end"], combine=t["combine"],
                            combine_end=t["combine_end"], padding=t["padding"], padding_end=t["padding_end"])
             if has_shared:
