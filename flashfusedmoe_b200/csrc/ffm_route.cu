@@ -684,7 +684,9 @@ void launch_route(int blocks, cudaStream_t s, const bf16* hidden, const bf16* ga
                   int32_t* topk_idx, float* lse, const RouteWorkspace& w) {
   auto kernel = route_gate_topk<GW, NG>;
   FFM_PREFER_MAX_SHARED(kernel);
-  // gate matrix in shared memory when a warp owns all experts and E x D bf16 fits in 64 KiB
+  // gate matrix in shared memory when a warp owns all experts, E x D bf16 fits in 64 KiB and E > 8: with up to eight
+  // experts staging gains nothing (the matrix stays hot in L1), and without it a block needs 2 KiB of shared memory
+  // and can run on an SM that holds a GEMM CTA (the shared expert's GEMMs run beside the routing kernels)
   constexpr size_t kGateSmemMax = 64 * 1024;
   const size_t gate_bytes = static_cast<size_t>(E) * D * sizeof(bf16);
   static bool smem_ok = false, smem_tried = false;
@@ -694,7 +696,8 @@ void launch_route(int blocks, cudaStream_t s, const bf16* hidden, const bf16* ga
                                    static_cast<int>(kGateSmemMax)) == cudaSuccess;
     if (!smem_ok) cudaGetLastError();
   }
-  const bool in_smem = NG == 1 && gate_bytes <= kGateSmemMax && (gate_bytes <= 48 * 1024 || smem_ok) && D % 8 == 0;
+  const bool in_smem =
+      NG == 1 && E > 8 && gate_bytes <= kGateSmemMax && (gate_bytes <= 48 * 1024 || smem_ok) && D % 8 == 0;
   route_gate_topk<GW, NG><<<blocks, ROUTE_THREADS, in_smem ? gate_bytes : 0, s>>>(
       hidden, gate_w, bias, N, D, E, top_k, opts, tpb, logits, topk_w, topk_idx, lse, w.block_hist, w.block_mass,
       w.block_z, in_smem ? 1 : 0);
