@@ -14,6 +14,8 @@
 //                       of every peer's flag array (release, system scope) and then waits until its own slots
 //                       show that epoch from every peer (acquire, system scope). Epochs only grow, so flags are
 //                       never reset. A wait that exceeds its cycle budget writes a status code and gives up.
+#include <stdlib.h>
+
 #include "ffm_common.cuh"
 
 namespace ffm {
@@ -261,6 +263,18 @@ __global__ void __launch_bounds__(256) p2p_plan_kernel(const int32_t* __restrict
 // payload of its exchanges while every kernel, barrier and local copy still runs. Results are then meaningless.
 int g_only_dst = -1;
 
+// Blocks of the row kernel per SM (FFM_P2P_BLOCKS_PER_SM, 1..8, default 8). The kernel runs on SMs that also hold a
+// GEMM CTA; fewer blocks leave those more issue slots, at some cost in NVLink rate.
+int rows_blocks_per_sm() {
+  static int v = 0;
+  if (v == 0) {
+    const char* e = getenv("FFM_P2P_BLOCKS_PER_SM");
+    const int x = e != nullptr ? atoi(e) : 8;
+    v = x < 1 ? 1 : (x > 8 ? 8 : x);
+  }
+  return v;
+}
+
 struct SignalArgs {
   uint32_t* flags[FFM_P2P_MAX_PEERS];  // flag array of every rank (index = rank); [my_rank] is local memory
 };
@@ -349,7 +363,7 @@ extern "C" int ffm_p2p_push_rows(const void* src, const int32_t* src_index, int 
     b.base[i] = static_cast<uint8_t*>(dst_bases[i]);
   }
   long long blocks = (total_rows + 8 * ROWS_PER_WARP - 1) / (8 * ROWS_PER_WARP);
-  if (blocks > 148LL * 8) blocks = 148LL * 8;
+  if (blocks > 148LL * rows_blocks_per_sm()) blocks = 148LL * rows_blocks_per_sm();
   p2p_rows_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint8_t*>(src), src_index, index_div, row_bytes, reinterpret_cast<const long long*>(segments),
       reinterpret_cast<const long long*>(seg_end), n_segments, total_rows, nullptr, b, g_only_dst);
@@ -373,7 +387,7 @@ extern "C" int ffm_p2p_push_rows_dev(const void* src, const int32_t* src_index, 
     b.base[i] = static_cast<uint8_t*>(dst_bases[i]);
   }
   long long blocks = (max_rows + 8 * ROWS_PER_WARP - 1) / (8 * ROWS_PER_WARP);
-  if (blocks > 148LL * 8) blocks = 148LL * 8;
+  if (blocks > 148LL * rows_blocks_per_sm()) blocks = 148LL * rows_blocks_per_sm();
   p2p_rows_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint8_t*>(src), src_index, index_div, row_bytes, reinterpret_cast<const long long*>(segments),
       reinterpret_cast<const long long*>(seg_end), n_segments, 0, reinterpret_cast<const long long*>(total_rows_dev), b,
