@@ -263,13 +263,15 @@ __global__ void __launch_bounds__(256) p2p_plan_kernel(const int32_t* __restrict
 // payload of its exchanges while every kernel, barrier and local copy still runs. Results are then meaningless.
 int g_only_dst = -1;
 
-// Blocks of the row kernel per SM (FFM_P2P_BLOCKS_PER_SM, 1..8, default 8). The kernel runs on SMs that also hold a
-// GEMM CTA; fewer blocks leave those more issue slots, at some cost in NVLink rate.
+// Blocks of the row kernel per SM (FFM_P2P_BLOCKS_PER_SM, 1..8, default 2). The kernel runs on SMs that also hold a
+// GEMM CTA, and NVLink, not the number of warps, bounds its rate: measured in the layer step (16,384 tokens per
+// rank, replayed) 8 / 4 / 2 / 1 blocks per SM give 1.630 / 1.613 / 1.614 / - ms on 2 GPUs and 1.748 / - / 1.693 /
+// 1.711 ms on 4, with the same 470-530 GB/s per direction inside the row kernels.
 int rows_blocks_per_sm() {
   static int v = 0;
   if (v == 0) {
     const char* e = getenv("FFM_P2P_BLOCKS_PER_SM");
-    const int x = e != nullptr ? atoi(e) : 8;
+    const int x = e != nullptr ? atoi(e) : 2;
     v = x < 1 ? 1 : (x > 8 ? 8 : x);
   }
   return v;
