@@ -832,17 +832,20 @@ def main():
         fl = algorithmic_flops(tokens, world)
         kt = timer.totals_ms()
         gemm_names = ("gemm_up_glu", "gemm", "gemm_wgrad")
-        gemm_ms = sum(kt[n][1] for n in gemm_names if n in kt)
+        # GEMM launches sit on several streams and two of them never share an SM: the merged intervals of their event
+        # pairs are the time the GEMM kernel had the GPU (the plain sum counts a launch queued behind another twice)
+        gemm_ms = timer.union_ms(gemm_names)
+        gemm_ms_sum = sum(kt[n][1] for n in gemm_names if n in kt)
         gemm_launches = sum(kt[n][0] for n in gemm_names if n in kt)
         achieved = fl["gemm"] * K / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else None
         # the same without the launches that also do the GLU backward (in the dAct GEMM's epilogue, or as a passenger
         # of the dW_down GEMM with FFM_FUSED_GLU_BACKWARD=0): their event time is the whole launch, their FLOPs are the
         # GEMM's alone (2 x rows x D x H in both schedules). What is left is the rate of the plain GEMM launches.
         carriers = [n for n in ("gemm_dact_glu_backward", "gemm_wgrad_passenger") if n in kt]
-        pass_ms = sum(kt[n][1] for n in carriers)
+        pass_ms = timer.union_ms(carriers)
+        rest_ms = timer.union_ms(gemm_names, exclude=carriers)
         pass_flops = 2.0 * tokens * CFG["d_model"] * (CFG["top_k"] * CFG["ffn_dim"] // 2 + CFG["shared_ffn_dim"] // 2)
-        alone = ((fl["gemm"] - pass_flops) * K / ((gemm_ms - pass_ms) * 1e-3) / 1e12
-                 if pass_ms > 0 and gemm_ms > pass_ms else None)
+        alone = (fl["gemm"] - pass_flops) * K / (rest_ms * 1e-3) / 1e12 if pass_ms > 0 and rest_ms > 0 else None
         value = tokens * world * K / (ms * 1e-3)
         sm_mhz = (clocks or {}).get("sm_mhz")
         sm_max = (clocks or {}).get("sm_max_mhz")
@@ -882,8 +885,9 @@ def main():
                                                            + rows_ * 3 * H_),
                 "kernel": "ffm_gemm_kernel (tcgen05 grouped GEMM, all instantiations)",
                 "measured_in": "a second pass of the same K steps after the timed region, same streams and same "
-                               "kernels as the timed region, with a "
-                               "CUDA-event pair around every kernel launch of the library",
+                               "kernels as the timed region, with a CUDA-event pair around every kernel launch of "
+                               "the library; GEMM time = merged intervals of the GEMM launches' event pairs (they sit "
+                               "on several streams and never share an SM)",
                 "peak_source": f"{peaks['source']} cuBLAS bf16 burst (sustained {peaks['tflops']})",
                 "frac_of_burst": (achieved / peaks["tflops_burst"]) if achieved else None,
                 "frac_of_sustained": (achieved / peaks["tflops"]) if achieved else None,
@@ -896,6 +900,7 @@ def main():
                 "frac_without_glu_backward_launches": (alone / peaks["tflops_burst"]) if alone else None,
                 "glu_backward_launch_ms_per_step": pass_ms / K,
                 "gemm_launches": gemm_launches, "gemm_ms_per_step": gemm_ms / K,
+                "gemm_event_pair_sum_ms_per_step": gemm_ms_sum / K,
                 "algorithmic_tflop_per_step": fl["gemm"] / 1e12,
                 "other_kernels_ms_per_step": {n: v[1] / K for n, v in kt.items()
                                               if n not in gemm_names and n not in ("all_to_all", "exchange_rows", "gemm_wgrad_passenger",

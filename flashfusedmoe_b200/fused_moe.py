@@ -390,10 +390,13 @@ def _require_bf16(dtype):
 # ----------------------------------------------------------------------------------------------
 
 class _FusedMoEFunction(torch.autograd.Function):
-    """Routed experts on one GPU. Outputs: (out [N, D], aux_loss, z_loss, tokens_per_expert)."""
+    """Routed experts on one GPU, optionally with the layer's shared expert (sw_*: its gate, up and down weights):
+    its forward GEMMs run on a side stream beside routing and permute and its output is added inside the combine
+    kernel; its backward GEMMs start with the backward pass, beside the row kernels that the routed GEMMs wait for.
+    Outputs: (out [N, D], aux_loss, z_loss, tokens_per_expert, dropped)."""
 
     @staticmethod
-    def forward(ctx, hidden_states, gate_weight, w_up, w_down, addend, cfg, dtype):
+    def forward(ctx, hidden_states, gate_weight, w_up, w_down, addend, sw_gate, sw_up, sw_down, cfg, dtype):
         N, D = hidden_states.shape
         E = gate_weight.shape[0]
         H = w_up.shape[1] // 2
@@ -403,6 +406,23 @@ class _FusedMoEFunction(torch.autograd.Function):
         wu = _to(w_up, dtype)
         wd = _to(w_down, dtype)
         add = None if addend is None else _to(addend, dtype)
+        need_grad = cfg.wants_grad and any(ctx.needs_input_grad[:8])
+        has_shared = sw_gate is not None
+        shared_ready = None
+        if has_shared:
+            assert add is None, "either an addend or shared expert weights"
+            swg, swu, swd = _to(sw_gate, dtype), _to(sw_up, dtype), _to(sw_down, dtype)
+            if _OVERLAP:
+                side = _get_side_stream("shared", priority=-1)
+                fork = torch.cuda.Event()
+                fork.record()
+                with torch.cuda.stream(side):
+                    side.wait_event(fork)
+                    add, s_act, s_pre = _glu_ffn_forward(h, swg, swu, swd, cfg.shared_activation, want_preact=need_grad)
+                    shared_ready = torch.cuda.Event()
+                    shared_ready.record(side)
+            else:
+                add, s_act, s_pre = _glu_ffn_forward(h, swg, swu, swd, cfg.shared_activation, want_preact=need_grad)
 
         routing = _route(h, g, cfg, hidden_states.requires_grad)
         cur, branch = (None, None) if cfg.capacity is not None else _fork_small(h)
@@ -417,7 +437,6 @@ class _FusedMoEFunction(torch.autograd.Function):
             with torch.cuda.stream(branch):
                 aux, z = _loss_tensors(routing, N, E, cfg)
                 dropped = torch.zeros(1, dtype=torch.int32, device=h.device)
-        need_grad = cfg.wants_grad and any(ctx.needs_input_grad[:5])
         # Without a backward pass nothing sums over the padding rows, so they are not zeroed -- except with capacity
         # dropping: a dropped slot keeps its grouped row (now a padding row) with weight 0, and 0 * (whatever the
         # GEMMs make of uninitialised memory, possibly NaN) would reach the output through the combine.
@@ -431,6 +450,9 @@ class _FusedMoEFunction(torch.autograd.Function):
         if add is not None and cfg.addend_ready is not None:
             torch.cuda.current_stream().wait_event(cfg.addend_ready)
             add.record_stream(torch.cuda.current_stream())
+        if shared_ready is not None:
+            torch.cuda.current_stream().wait_event(shared_ready)
+            add.record_stream(torch.cuda.current_stream())
         out = ops.combine_forward(Y, routing.pos, routing.topk_w, N, k, addend=add)
         if branch is not None:
             _join_small(cur, branch, aux, z, dropped)
@@ -440,12 +462,16 @@ class _FusedMoEFunction(torch.autograd.Function):
         ctx.shape = (N, D, E, H)
         ctx.rows_cap = routing.rows_cap
         ctx.in_dtypes = (hidden_states.dtype, gate_weight.dtype, w_up.dtype, w_down.dtype,
-                         None if addend is None else addend.dtype)
+                         None if addend is None else addend.dtype) + tuple(
+                             None if w is None else w.dtype for w in (sw_gate, sw_up, sw_down))
         saved = [h, g, wu, wd, routing.topk_w, routing.topk_idx, routing.logits, routing.lse, routing.counts,
                  routing.tile_start, routing.pos, routing.src, Xg]
         if keep:
             saved += [pre, act, Y]
         ctx.kept = keep
+        ctx.has_shared = has_shared and need_grad
+        if ctx.has_shared:
+            saved += [s_act, s_pre, swg, swu, swd]
         ctx.save_for_backward(*saved)
         counts = routing.counts
         ctx.mark_non_differentiable(counts, dropped)
@@ -469,6 +495,25 @@ class _FusedMoEFunction(torch.autograd.Function):
         if grad_out is None:
             grad_out = torch.zeros(N, D, dtype=h.dtype, device=h.device)
         go = _to(grad_out, h.dtype)  # also densifies expanded (stride-0) gradients
+
+        shared_done = None
+        if ctx.has_shared:
+            s_act, s_pre, swg, swu, swd = saved[-5:]
+            if _OVERLAP:
+                # the shared expert's backward depends on the output gradient alone: its GEMMs start now, beside
+                # combine_backward, and the routed GEMMs follow them
+                side = _get_side_stream("shared", priority=-1)
+                fork_s = torch.cuda.Event()
+                fork_s.record()
+                with torch.cuda.stream(side):
+                    side.wait_event(fork_s)
+                    s_dx, s_dwg, s_dwu, s_dwd = _glu_ffn_backward(go, h, s_act, s_pre, swg, swu, swd,
+                                                                  cfg.shared_activation)
+                    shared_done = torch.cuda.Event()
+                    shared_done.record(side)
+                go.record_stream(side)
+            else:
+                s_dx, s_dwg, s_dwu, s_dwd = _glu_ffn_backward(go, h, s_act, s_pre, swg, swu, swd, cfg.shared_activation)
 
         gYw, gw = ops.combine_backward(go, Y, topk_w, src, ctx.rows_cap, k)
         if _OVERLAP:
@@ -524,7 +569,16 @@ class _FusedMoEFunction(torch.autograd.Function):
         d_add = None
         if dt[4] is not None and ctx.needs_input_grad[4]:
             d_add = go.to(dt[4])
-        return (dH.to(dt[0]), d_gate.to(dt[1]), d_wu.to(dt[2]), d_wd.to(dt[3]), d_add, None, None)
+        s_grads = (None, None, None)
+        if ctx.has_shared:
+            if shared_done is not None:
+                cur_s = torch.cuda.current_stream()
+                cur_s.wait_event(shared_done)
+                for t_side in (s_dx, s_dwg, s_dwu, s_dwd):
+                    t_side.record_stream(cur_s)
+            dH = dH + s_dx
+            s_grads = (s_dwg.to(dt[5]), s_dwu.to(dt[6]), s_dwd.to(dt[7]))
+        return (dH.to(dt[0]), d_gate.to(dt[1]), d_wu.to(dt[2]), d_wd.to(dt[3]), d_add) + s_grads + (None, None)
 
 
 # ----------------------------------------------------------------------------------------------
@@ -1213,10 +1267,13 @@ def fused_moe(
     ep_full_input_grad=False,
     _addend=None,
     _addend_ready=None,
+    _shared=None,
 ):
     """Fused MoE forward; returns (output [N, D], losses dict). Arguments as in the reference
     (fused_moe.py:1073-1138). `_addend` is a private hook used by MoELayer to fold the shared expert's output
-    into the combine kernel."""
+    into the combine kernel; `_shared` = (gate, up, down weights, activation) is the private hook with which MoELayer
+    hands its shared expert to the single-GPU layer (the public `shared_expert_weights` keeps the reference's meaning:
+    expert parallel only)."""
     group = ep_group if ep_group is not None else (_EP_GROUP if _EP_ACTIVE else None)
     if not _EP_ACTIVE:
         _validate_inputs(hidden_states, gate_weight, w_up, w_down, top_k, activation, gating, ep_group=ep_group)
@@ -1250,7 +1307,8 @@ def fused_moe(
     lw_all = latent_weights if latent_weights is not None else ()
     cfg.wants_grad = torch.is_grad_enabled() and any(
         t is not None and t.requires_grad
-        for t in (hidden_states, gate_weight, w_up, w_down, _addend, *sw_all, *lw_all))
+        for t in (hidden_states, gate_weight, w_up, w_down, _addend, *sw_all, *lw_all,
+                  *(_shared[:3] if _shared is not None else ())))
 
     if group is not None:
         sw = shared_expert_weights if shared_expert_weights is not None else (None, None, None)
@@ -1263,8 +1321,12 @@ def fused_moe(
             out, aux, z, counts, dropped = _FusedMoEEPFunction.apply(hidden_states, gate_weight, w_up, w_down, sw[0],
                                                                      sw[1], sw[2], lw[0], lw[1], cfg, dtype)
     else:
-        out, aux, z, counts, dropped = _FusedMoEFunction.apply(hidden_states, gate_weight, w_up, w_down, _addend, cfg,
-                                                               dtype)
+        sh = (None, None, None)
+        if _shared is not None:
+            sh = tuple(_shared[:3])
+            cfg.shared_activation = _shared[3]
+        out, aux, z, counts, dropped = _FusedMoEFunction.apply(hidden_states, gate_weight, w_up, w_down, _addend,
+                                                               sh[0], sh[1], sh[2], cfg, dtype)
         if max_tokens_per_expert is not None and not allow_dropped_tokens and capacity is None:
             actual_max = int(counts.max().item())
             if actual_max > max_tokens_per_expert:

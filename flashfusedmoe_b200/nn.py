@@ -92,16 +92,20 @@ class MoELayer(nn.Module):
         x_flat = x.reshape(-1, D)
 
         shared_weights = None
-        addend = addend_ready = None
+        shared_local = None
         if self.shared_expert is not None:
             if self._ep_group is not None:
                 # EP: the shared expert runs inside fused_moe on a side stream (reference: nn.py:126-132)
                 shared_weights = (self.shared_expert.w_gate.weight, self.shared_expert.w_up.weight,
                                   self.shared_expert.w_down.weight)
             else:
-                # single GPU: runs on a side stream beside the routing kernels and is added to the routed output
-                # inside the combine kernel
-                addend, addend_ready = run_beside(self.shared_expert, x_flat)
+                # single GPU: fused_moe runs it on a side stream beside the routing kernels, adds its output inside the
+                # combine kernel and starts its backward GEMMs with the backward pass
+                se = self.shared_expert
+                if se.activation not in ("swiglu", "geglu", "relu_squared"):
+                    raise ValueError(f"Unknown activation: {se.activation}")
+                shared_local = (se.w_gate.weight, se.w_up.weight, se.w_down.weight,
+                                "geglu_erf" if se.activation == "geglu" else se.activation)
 
         latent_weights = None
         if self.latent_dim is not None:
@@ -114,7 +118,7 @@ class MoELayer(nn.Module):
             recompute_activations=self.recompute_activations,
             max_tokens_per_expert=self.max_tokens_per_expert, allow_dropped_tokens=self.allow_dropped_tokens,
             shared_expert_weights=shared_weights, latent_weights=latent_weights,
-            ep_full_input_grad=self.ep_full_input_grad, _addend=addend, _addend_ready=addend_ready)
+            ep_full_input_grad=self.ep_full_input_grad, _shared=shared_local)
         return out.reshape(*leading, D), losses
 
     def shard_experts(self, ep_group, ep_backend="nccl"):

@@ -31,6 +31,26 @@ class KernelTimer:
         """name -> (launches, total milliseconds); call after torch.cuda.synchronize()."""
         return {n: (len(ev), sum(a.elapsed_time(b) for a, b in ev)) for n, ev in self.events.items()}
 
+    def union_ms(self, names, exclude=()):
+        """Milliseconds during which at least one launch filed under `names` (and not under `exclude`) was between its
+        start and its end event. Launches on different streams overlap in time: a kernel whose start event has fired
+        may still wait for the SMs that a kernel of another stream holds, so the sum of the event pairs counts that
+        time twice and the merged intervals count it once. Call after torch.cuda.synchronize()."""
+        skip = {id(p) for n in exclude for p in self.events.get(n, ())}
+        pairs = {id(p): p for n in names for p in self.events.get(n, ()) if id(p) not in skip}
+        if not pairs:
+            return 0.0
+        base = next(iter(pairs.values()))[0]
+        spans = sorted((base.elapsed_time(a), base.elapsed_time(b)) for a, b in pairs.values())
+        total, lo, hi = 0.0, spans[0][0], spans[0][1]
+        for a, b in spans[1:]:
+            if a > hi:
+                total += hi - lo
+                lo, hi = a, b
+            else:
+                hi = max(hi, b)
+        return total + (hi - lo)
+
 
 def set_timer(timer):
     global _timer

@@ -549,3 +549,29 @@ def test_dact_gemm_with_fused_glu_backward(counts, K, H, activation):
                                                    activation)
     ops.check_status()
     assert torch.equal(dense_got, dense_want)
+
+
+def test_kernel_timer_merges_overlapping_launches():
+    """KernelTimer.union_ms counts the time two launches on different streams overlap once; the plain sum counts it
+    twice."""
+    timer = ops.KernelTimer()
+    side = torch.cuda.Stream()
+    x = torch.zeros(1 << 24, device=DEV)
+    ops.set_timer(timer)
+    try:
+        with ops._Launch("a", 0):
+            torch.cuda._sleep(2_000_000)
+        with torch.cuda.stream(side):
+            with ops._Launch("b", 0):
+                torch.cuda._sleep(2_000_000)
+        with ops._Launch("c", 0):
+            x.add_(1.0)
+    finally:
+        ops.set_timer(None)
+    torch.cuda.synchronize()
+    totals = timer.totals_ms()
+    both = timer.union_ms(("a", "b"))
+    assert max(totals["a"][1], totals["b"][1]) <= both + 1e-3
+    assert both < totals["a"][1] + totals["b"][1]          # the two sleeps ran at the same time
+    assert abs(timer.union_ms(("a", "b"), exclude=("b",)) - totals["a"][1]) < 1e-3
+    assert timer.union_ms(("missing",)) == 0.0
