@@ -838,14 +838,10 @@ def main():
         gemm_ms_sum = sum(kt[n][1] for n in gemm_names if n in kt)
         gemm_launches = sum(kt[n][0] for n in gemm_names if n in kt)
         achieved = fl["gemm"] * K / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else None
-        # the same without the launches that also do the GLU backward (in the dAct GEMM's epilogue, or as a passenger
-        # of the dW_down GEMM with FFM_FUSED_GLU_BACKWARD=0): their event time is the whole launch, their FLOPs are the
-        # GEMM's alone (2 x rows x D x H in both schedules). What is left is the rate of the plain GEMM launches.
+        # the launches that also do the GLU backward (in the dAct GEMM's epilogue, or as a passenger of the dW_down GEMM
+        # with FFM_FUSED_GLU_BACKWARD=0): their event time is the whole launch, their FLOPs are the GEMM's alone
         carriers = [n for n in ("gemm_dact_glu_backward", "gemm_wgrad_passenger") if n in kt]
         pass_ms = timer.union_ms(carriers)
-        rest_ms = timer.union_ms(gemm_names, exclude=carriers)
-        pass_flops = 2.0 * tokens * CFG["d_model"] * (CFG["top_k"] * CFG["ffn_dim"] // 2 + CFG["shared_ffn_dim"] // 2)
-        alone = (fl["gemm"] - pass_flops) * K / (rest_ms * 1e-3) / 1e12 if pass_ms > 0 and rest_ms > 0 else None
         value = tokens * world * K / (ms * 1e-3)
         sm_mhz = (clocks or {}).get("sm_mhz")
         sm_max = (clocks or {}).get("sm_max_mhz")
@@ -896,8 +892,7 @@ def main():
                 "whole_step_tflops": fl["gemm"] * K / (ms * 1e-3) / 1e12,
                 "glu_backward_schedule": ("epilogue of the dAct GEMM" if "gemm_dact_glu_backward" in carriers else
                                           "passenger warps of the dW_down GEMM" if carriers else None),
-                "achieved_without_glu_backward_launches": alone,
-                "frac_without_glu_backward_launches": (alone / peaks["tflops_burst"]) if alone else None,
+                # merged intervals of those launches' event pairs (includes time they wait behind another GEMM)
                 "glu_backward_launch_ms_per_step": pass_ms / K,
                 "gemm_launches": gemm_launches, "gemm_ms_per_step": gemm_ms / K,
                 "gemm_event_pair_sum_ms_per_step": gemm_ms_sum / K,
