@@ -10,7 +10,7 @@ import math
 import torch
 import torch.nn as nn
 
-from .fused_moe import fused_moe, glu_ffn, run_beside, set_ep_group
+from .fused_moe import fused_moe, glu_ffn, set_ep_group
 
 
 class _GLUFFN(nn.Module):
