@@ -497,14 +497,18 @@ class _FusedMoEFunction(torch.autograd.Function):
         go = _to(grad_out, h.dtype)  # also densifies expanded (stride-0) gradients
 
         shared_done = None
+        fork_s = None
+        if ctx.has_shared and _OVERLAP:
+            fork_s = torch.cuda.Event()
+            fork_s.record()
+        # first in launch order: the routed GEMMs wait for it, the shared expert's (launched next) do not
+        gYw, gw = ops.combine_backward(go, Y, topk_w, src, ctx.rows_cap, k)
         if ctx.has_shared:
             s_act, s_pre, swg, swu, swd = saved[-5:]
             if _OVERLAP:
-                # the shared expert's backward depends on the output gradient alone: its GEMMs start now, beside
-                # combine_backward, and the routed GEMMs follow them
+                # the shared expert's backward depends on the output gradient alone: its GEMMs start with the backward
+                # pass, beside combine_backward, and the routed GEMMs follow them
                 side = _get_side_stream("shared", priority=-1)
-                fork_s = torch.cuda.Event()
-                fork_s.record()
                 with torch.cuda.stream(side):
                     side.wait_event(fork_s)
                     s_dx, s_dwg, s_dwu, s_dwd = _glu_ffn_backward(go, h, s_act, s_pre, swg, swu, swd,
@@ -515,7 +519,6 @@ class _FusedMoEFunction(torch.autograd.Function):
             else:
                 s_dx, s_dwg, s_dwu, s_dwd = _glu_ffn_backward(go, h, s_act, s_pre, swg, swu, swd, cfg.shared_activation)
 
-        gYw, gw = ops.combine_backward(go, Y, topk_w, src, ctx.rows_cap, k)
         if _OVERLAP:
             # Two GEMMs never share an SM, so the GEMMs stay in one chain and each HBM-bound kernel is paired with
             # a GEMM that does not depend on it:
